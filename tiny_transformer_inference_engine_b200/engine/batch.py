@@ -1,0 +1,159 @@
+"""Packs a step's entries into one int32 buffer and one host-to-device copy.
+
+The reference builds ``input_ids / positions / query_start_loc / block_tables /
+seq_lens`` as Python lists per step (serving/batch.py:18-36) and turns them into
+tensors again inside every layer (serving/paged_mqa.py:80,87-96;
+serving/fake_paged_attn.py:52-100).  Here they are laid out once in pinned host
+memory, copied once, and every kernel of the step reads views of that buffer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..parts.base import StepContext
+
+
+@dataclass
+class StepEntry:
+    """A request's next tokens: ``tokens`` sit at positions ``start .. start+len-1``;
+    ``want`` lists indices into ``tokens`` whose logits are asked for."""
+    rid: Hashable
+    start: int
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)
+
+
+def _round4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class BatchPacker:
+    def __init__(self, manager, ops, dtype: torch.dtype, device, vocab_size: int, max_seq_len: int):
+        self.manager, self.ops, self.dtype = manager, ops, dtype
+        self.device = torch.device(device)
+        self.vocab_size, self.max_seq_len = vocab_size, max_seq_len
+        self._host = None
+        self._dev = None
+        self._cap = 0
+        self._copied = None            # event: the last host-to-device copy has read the host buffer
+
+    def _ensure(self, n: int):
+        if n > self._cap:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            pin = self.device.type == "cuda"
+            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._cap = cap
+
+    def validate(self, entries: List[StepEntry]) -> None:
+        """Host-side checks of everything a kernel will index with (cf. serving/kv_pool.py:41-53,
+        serving/fake_paged_attn.py:61-92, kernels/pagedattn/pagedattn.cu:867-895)."""
+        seen = set()
+        for en in entries:
+            if en.rid in seen:
+                raise ValueError(f"request {en.rid!r} appears twice in one step")
+            seen.add(en.rid)
+            n = len(en.tokens)
+            if n < 1:
+                raise ValueError(f"request {en.rid!r} brings no tokens")
+            if en.start < 0 or en.start + n > self.max_seq_len:
+                raise ValueError(f"request {en.rid!r}: positions {en.start}..{en.start + n - 1} exceed "
+                                 f"max_seq_len={self.max_seq_len}")
+            for t in en.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise ValueError(f"request {en.rid!r}: token id {t} outside [0, {self.vocab_size})")
+            for w in en.want:
+                if not 0 <= int(w) < n:
+                    raise ValueError(f"request {en.rid!r}: wanted place {w} outside its {n} tokens")
+            for gi, g in enumerate(self.manager.groups):
+                table = g.tables.get(en.rid)
+                if table is None:
+                    raise KeyError(f"request {en.rid!r} is not admitted")
+                first = g.first_needed_page(en.start)
+                last = -(-(en.start + n) // g.page_size)
+                if len(table) < last or any(p <= 0 or p >= g.num_pages for p in table[first:last]):
+                    raise ValueError(f"request {en.rid!r}: block table of group {gi} does not cover "
+                                     f"positions {en.start}..{en.start + n - 1}")
+
+    def pack(self, entries: List[StepEntry], pad_seqs: int = 0, pages_per_seq: Optional[Dict[int, int]] = None,
+             buffers=None) -> StepContext:
+        """``pad_seqs``/``pages_per_seq``/``buffers`` give a fixed layout (for a captured
+        graph): the batch is padded to ``pad_seqs`` one-token requests that sit on the
+        scratch page with length 1, and the tables get ``pages_per_seq[group]`` columns."""
+        self.validate(entries)
+        mgr = self.manager
+        N_real = len(entries)
+        N = max(N_real, pad_seqs)
+        q_lens = [len(e.tokens) for e in entries] + [1] * (N - N_real)
+        T = sum(q_lens)
+        tok, pos, tseq, qsl, seql, slots, rows = [], [], [], [0], [], [], []
+        for i, en in enumerate(entries):
+            n = len(en.tokens)
+            base = qsl[-1]
+            tok.extend(int(t) for t in en.tokens)
+            pos.extend(range(en.start, en.start + n))
+            tseq.extend([i] * n)
+            qsl.append(base + n)
+            seql.append(en.start + n)
+            slots.append(mgr.slot_of[en.rid])
+            rows.extend(base + int(w) for w in en.want)
+        for i in range(N_real, N):
+            tok.append(0); pos.append(0); tseq.append(i); rows.append(qsl[-1]); qsl.append(qsl[-1] + 1); seql.append(1); slots.append(0)
+        R = len(rows)
+        tables, widths = [], []
+        for gi, g in enumerate(mgr.groups):
+            width = max([len(g.tables[e.rid]) for e in entries] + [1])
+            if pages_per_seq is not None:
+                if width > pages_per_seq[gi]:
+                    raise ValueError("block table wider than the fixed layout")
+                width = pages_per_seq[gi]
+            arr = np.zeros((N, width), dtype=np.int32)
+            for i, en in enumerate(entries):
+                t = g.tables[en.rid]
+                arr[i, :len(t)] = t
+            tables.append(arr)
+            widths.append(width)
+
+        sizes = [T, T, T, N + 1, N, N, max(R, 1)] + [N * w for w in widths]
+        offs, total = [], 0
+        for s in sizes:
+            offs.append(total)
+            total += _round4(s)
+        if buffers is None:
+            self._ensure(total)
+            host, dev = self._host, self._dev
+        else:
+            host, dev = buffers
+            if total > host.numel():
+                raise ValueError("step does not fit the fixed buffers")
+        if self._copied is not None:
+            self._copied.synchronize()
+        hn = host.numpy()
+        for off, data in zip(offs[:7], (tok, pos, tseq, qsl, seql, slots, rows)):
+            hn[off:off + len(data)] = data
+        for off, arr in zip(offs[7:], tables):
+            hn[off:off + arr.size] = arr.reshape(-1)
+        dev[:total].copy_(host[:total], non_blocking=True)
+        if self.device.type == "cuda":
+            if self._copied is None:
+                self._copied = torch.cuda.Event()
+            self._copied.record()
+
+        def view(k, n):
+            return dev[offs[k]:offs[k] + n]
+
+        ctx = StepContext(
+            ops=self.ops, dtype=self.dtype, device=self.device,
+            num_tokens=T, num_seqs=N, max_q_len=max(q_lens), max_kv_len=max(seql),
+            token_ids=view(0, T), positions=view(1, T), token_seq=view(2, T),
+            query_start_loc=view(3, N + 1), seq_lens=view(4, N), slot_ids=view(5, N),
+            logit_rows=view(6, R), num_logit_rows=R,
+            block_tables={gi: dev[offs[7 + gi]:offs[7 + gi] + N * w].view(N, w) for gi, w in enumerate(widths)},
+            host={"q_lens": q_lens, "seq_lens": seql, "query_start_loc": qsl, "positions": pos,
+                  "num_real_seqs": N_real},
+        )
+        return ctx

@@ -1,0 +1,180 @@
+"""The Python entry point: load or make a model, generate.
+
+In the reference's manner (inference.py:68-152, serving/generation.py:11-69):
+``load_model(path)`` gives an engine, ``generate_ids(engine, prompt_ids, max_new_tokens,
+temperature=, top_k=, top_p=)`` gives the new token ids of one prompt with the same
+argument checks, ``Engine.generate`` does it for many prompts through the scheduler,
+and ``add_request`` / ``step`` expose the continuous loop (serving/scheduler.py:24,46).
+A generated EOS token is reported and ends the request, as in ``generate_ids``
+(inference.py:147-150).
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from .. import models as _models  # noqa: F401  (registers the architecture)
+from ..cache import CacheManager
+from ..config import ModelConfig, EngineConfig, CacheConfig, SchedulerConfig
+from ..models.model import Model
+from ..registry import model_spec
+from ..sampling import SamplingParams, Sampler
+from ..weights import load_folder, place, random_tensors
+from .batch import StepEntry
+from .scheduler import Scheduler
+from .step import Stepper
+
+_TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+class Engine:
+    def __init__(self, config: ModelConfig, tensors_or_folder, engine_config: Optional[EngineConfig] = None,
+                 ops=None):
+        self.config = config
+        self.engine_config = ec = engine_config or EngineConfig()
+        self.device = torch.device(ec.device)
+        self.dtype = _TORCH[ec.dtype]
+        if ops is None:
+            from ..ops import get_ops
+            ops = get_ops(self.device)
+        self.ops = ops
+        self.spec = model_spec(config)
+        self.model = Model(self.spec)
+        specs = self.model.param_specs()
+        # weights are checked against the configuration before anything large is allocated
+        if isinstance(tensors_or_folder, (str, os.PathLike)):
+            tensors = load_folder(str(tensors_or_folder), specs, self.dtype, self.device)
+        else:
+            tensors = place(tensors_or_folder, specs, self.dtype, self.device)
+        self.model.bind(ops, self.dtype, self.device)
+        self.model.load(tensors)
+        del tensors
+        needs = self.model.cache_needs()
+        self.manager = CacheManager(needs, self.model.run_order, ec.cache.block_size, ec.cache.num_gpu_blocks,
+                                    ec.sched.max_num_seqs, ec.kv_dtype, self.device,
+                                    kv_budget_bytes=ec.cache.kv_budget_bytes)
+        # models/model_config.py:101-102: the pool must hold one full-length sequence plus the scratch page
+        if self.manager.groups and self.manager.num_usable_pages * ec.cache.block_size < 1:
+            raise ValueError("the cache pool holds no page")
+        graphs = ec.sched.cudagraph_batch_sizes if (ec.use_cuda_graphs and self.device.type == "cuda") else []
+        self.stepper = Stepper(self.model, self.manager, ops, self.dtype, self.device, graphs)
+        self.sampler = Sampler(ops, ec.sched.max_num_seqs, config.vocab_size, self.device)
+        self.scheduler = Scheduler(self.manager, ec.sched, config.max_seq_len, config.eos_token_id)
+        self._requests: Dict[int, object] = {}
+
+    # ---------------------------------------------------------------- construction
+    @classmethod
+    def from_folder(cls, folder: str, engine_config: Optional[EngineConfig] = None, ops=None, **opts) -> "Engine":
+        return cls(ModelConfig.from_json(folder), folder, _engine_config(engine_config, opts), ops)
+
+    @classmethod
+    def from_random(cls, config: Union[ModelConfig, dict, str], seed: int = 0,
+                    engine_config: Optional[EngineConfig] = None, ops=None, **opts) -> "Engine":
+        if isinstance(config, str):
+            config = ModelConfig.from_json(config)
+        elif isinstance(config, dict):
+            config = ModelConfig.from_dict(config)
+        return cls(config, random_tensors(config, seed), _engine_config(engine_config, opts), ops)
+
+    # ---------------------------------------------------------------- continuous loop
+    def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        for t in prompt_ids:
+            if not 0 <= int(t) < self.config.vocab_size:
+                raise ValueError(f"token id {t} outside [0, {self.config.vocab_size})")
+        rid = self.scheduler.add_request(list(prompt_ids), params)
+        self._requests[rid] = self.scheduler.waiting[-1]
+        return rid
+
+    @torch.no_grad()
+    def step(self) -> List[Tuple[int, int, bool]]:
+        """One scheduler step: plan, run the batch, sample on the device, read the tokens."""
+        sched = self.scheduler
+        before = {r.rid for r in sched.running}
+        entries = sched.plan()
+        if not entries:
+            return []
+        for r in sched.running:
+            if r.rid not in before or r.num_cached == 0:
+                self.sampler.set_request(self.manager.slot_of[r.rid], r.params, draws_so_far=len(r.output))
+        logits = self.stepper.step(entries)
+        slots = [self.manager.slot_of[e.rid] for e in entries if e.want]
+        if slots:
+            slot_ids = torch.tensor(slots, dtype=torch.int32).to(self.device, non_blocking=True)
+            tokens = self.sampler.sample(logits[:len(slots)], slot_ids).tolist()       # one device-to-host read
+        else:
+            tokens = []
+        return sched.update(entries, tokens)
+
+    # ---------------------------------------------------------------- whole generations
+    def generate(self, prompts_ids: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None
+                 ) -> List[List[int]]:
+        """New token ids for every prompt (host lists in, host lists out)."""
+        if not prompts_ids:
+            return []
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts_ids)
+        if len(params) != len(prompts_ids):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        for ids, p in zip(prompts_ids, params):                                         # inference.py:126-135
+            if p.max_new_tokens and not len(ids):
+                raise ValueError("prompt must hold at least one token")
+            if len(ids) + p.max_new_tokens > self.config.max_seq_len:
+                raise ValueError("prompt plus requested generation exceeds max_seq_len")
+        outputs: Dict[int, List[int]] = {}
+        order = []
+        for ids, p in zip(prompts_ids, params):
+            if p.max_new_tokens == 0:
+                order.append(None)
+                continue
+            rid = self.add_request(ids, p)
+            order.append(rid)
+            outputs[rid] = []
+        while any(rid is not None and not self._requests[rid].finished for rid in order):
+            for rid, tok, _ in self.step():
+                if rid in outputs:
+                    outputs[rid].append(tok)
+        for rid in outputs:
+            self._requests.pop(rid, None)
+        return [outputs[rid] if rid is not None else [] for rid in order]
+
+    def stats(self) -> dict:
+        return {**self.scheduler.counters, **{f"step_{k}": v for k, v in self.stepper.counters.items()},
+                "pages_free": self.manager.num_free_pages, "pages_usable": self.manager.num_usable_pages}
+
+
+def _engine_config(engine_config: Optional[EngineConfig], opts: dict) -> EngineConfig:
+    if engine_config is not None:
+        if opts:
+            raise ValueError("give either an EngineConfig or keyword options")
+        return engine_config
+    cache_keys = {"block_size", "num_gpu_blocks", "kv_budget_bytes"}
+    sched_keys = {"max_num_seqs", "max_num_batched_tokens", "enable_chunked_prefill", "cudagraph_batch_sizes"}
+    cache = CacheConfig(**{k: opts.pop(k) for k in list(opts) if k in cache_keys})
+    sched = SchedulerConfig(**{k: opts.pop(k) for k in list(opts) if k in sched_keys})
+    return EngineConfig(cache=cache, sched=sched, **opts)
+
+
+# ------------------------------------------------------------------- the reference's names
+def load_model(path: str, device: str = "cuda:0", **opts) -> Engine:
+    """``inference.py:68`` takes a checkpoint file; this takes a model folder."""
+    return Engine.from_folder(path, device=device, **opts)
+
+
+def generate_ids(engine: Engine, prompt_ids: Sequence[int], max_new_tokens: int, *, temperature: float = 1.0,
+                 top_k: int = 0, top_p: float = 1.0, seed: int = 0, greedy: bool = False) -> List[int]:
+    """``inference.py:124-152`` with its checks: a negative count raises, zero tokens give
+    ``[]`` (and need no prompt), an empty or over-long prompt raises."""
+    if max_new_tokens < 0:
+        raise ValueError("max_new_tokens must be >= 0")
+    if max_new_tokens == 0:
+        return []
+    if not len(prompt_ids):
+        raise ValueError("prompt must encode to at least one token")
+    if len(prompt_ids) > engine.config.max_seq_len:
+        raise ValueError(f"prompt has {len(prompt_ids)} tokens; model limit is {engine.config.max_seq_len}")
+    params = SamplingParams(max_new_tokens=max_new_tokens, temperature=temperature, top_k=top_k, top_p=top_p,
+                            seed=seed, greedy=greedy)
+    return engine.generate([list(prompt_ids)], params)[0]

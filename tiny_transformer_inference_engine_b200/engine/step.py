@@ -1,0 +1,86 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted
+places out.
+
+It generalises the reference's ``PagedTransformer.forward_batch`` (serving/paged_model.py:50-67):
+any mix of prompt portions and single decoded tokens, cut anywhere, runs as ONE varlen
+batch from the cache that earlier steps left; it runs only the tokens it is given and
+returns 32-bit logits only where asked (the reference returns the last token of every
+span).  The cache must already cover the new positions (``CacheManager.extend``).
+
+Decode-only steps (one token per request, one wanted row each) can run from a captured
+CUDA graph per batch-size bucket: the metadata buffer keeps its address and layout, so a
+replay needs only the one host-to-device copy.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .batch import BatchPacker, StepEntry
+from ..cache import CacheManager
+from ..models.model import Model
+
+
+class _DecodeGraph:
+    def __init__(self, bucket, host, dev, graph, logits, ctx):
+        self.bucket, self.host, self.dev, self.graph, self.logits, self.ctx = bucket, host, dev, graph, logits, ctx
+
+
+class Stepper:
+    def __init__(self, model: Model, manager: CacheManager, ops, dtype: torch.dtype, device,
+                 graph_batch_sizes: Optional[List[int]] = None):
+        self.model, self.manager, self.ops, self.dtype = model, manager, ops, dtype
+        self.device = torch.device(device)
+        self.packer = BatchPacker(manager, ops, dtype, device, model.spec.vocab_size, model.spec.max_seq_len)
+        self.graph_batch_sizes = sorted(graph_batch_sizes or [])
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self.counters = {"steps": 0, "tokens": 0, "graph_replays": 0}
+
+    # ---------------------------------------------------------------- plain step
+    @torch.no_grad()
+    def step(self, entries: List[StepEntry]) -> torch.Tensor:
+        """Logits (float32, [sum of wants, vocab]) in the order of the entries and of ``want``."""
+        if not entries:
+            return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
+        self.counters["steps"] += 1
+        self.counters["tokens"] += sum(len(e.tokens) for e in entries)
+        if self.graph_batch_sizes and self._is_decode(entries):
+            bucket = next((b for b in self.graph_batch_sizes if b >= len(entries)), None)
+            if bucket is not None:
+                return self._step_graph(entries, bucket)
+        ctx = self.packer.pack(entries)
+        views = self.manager.views(ctx.block_tables)
+        return self.model.forward(ctx, views)
+
+    @staticmethod
+    def _is_decode(entries) -> bool:
+        return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
+    # ---------------------------------------------------------------- captured decode step
+    def _fixed_pages(self) -> Dict[int, int]:
+        return {gi: -(-self.model.spec.max_seq_len // g.page_size) for gi, g in enumerate(self.manager.groups)}
+
+    def _step_graph(self, entries, bucket: int) -> torch.Tensor:
+        n = len(entries)
+        g = self._graphs.get(bucket)
+        pages = self._fixed_pages()
+        if g is None:
+            words = 8 * (bucket + 4) + sum(bucket * w + 4 for w in pages.values()) + 64
+            host = torch.empty(words, dtype=torch.int32, pin_memory=True)
+            dev = torch.zeros(words, dtype=torch.int32, device=self.device)
+            ctx = self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(host, dev))
+            # the captured kernels must cover any context length: size them for the longest
+            ctx.max_kv_len = self.model.spec.max_seq_len
+            views = self.manager.views(ctx.block_tables)
+            self.model.forward(ctx, views)                       # warm-up outside the capture
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, views)
+            g = _DecodeGraph(bucket, host, dev, graph, logits, ctx)
+            self._graphs[bucket] = g
+        self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(g.host, g.dev))
+        g.graph.replay()
+        self.counters["graph_replays"] += 1
+        return g.logits[:n]

@@ -1,0 +1,99 @@
+"""Causal attention over a paged key/value cache (multi-query, grouped or multi-head).
+
+Order of the reference's serving path (serving/paged_mqa.py:64-113): project q, k, v;
+rotate q and k at the tokens' positions; store rotated k and raw v into the pages
+at ``table[pos // page] * page + pos % page``; attend over every key of the request
+read back from the pages (new ones included) with scale ``1/sqrt(head_dim)`` and a
+bottom-right aligned causal mask (kernels/pagedattn/pagedattn.cu:196-207,256);
+project the concatenated heads with ``out``.  Query head ``h`` uses kv head
+``h // (heads / kv_heads)`` (kernels/flashattn/flashattn.cu, same rule).
+
+The three projections are fused at load into one matrix ``[(Hq+2*Hkv)*D, d]`` so one
+product feeds the rotate-and-store kernel.  ``window`` (keys ``pos-window+1..pos``)
+is a parameter of the part; the reference's model has none.  A run entry that reads
+another entry's cache (``shares_kv``) has no k/v projection and stores nothing.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from .base import Mixer, ParamSpec, PartSpec, PagedKVNeed, PagedKVView, StepContext
+from ..registry import register_part, build_part
+
+
+@register_part("mixer", "attention")
+class PagedAttention(Mixer):
+    def __init__(self, prefix: str, d_model: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position: PartSpec, bias: bool = False, window: Optional[int] = None,
+                 scale: Optional[float] = None, shares_kv: bool = False,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(prefix)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        if window is not None and window < 1:
+            raise ValueError(f"window must be >= 1 or None, got {window}")
+        self.d_model, self.num_heads, self.num_kv_heads, self.head_dim = d_model, num_heads, num_kv_heads, head_dim
+        self.bias, self.window, self.shares_kv = bool(bias), window, bool(shares_kv)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.position = build_part("position", position)
+        self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "out"}
+        if names:
+            self.names.update(names)
+        self.w_in = self.b_in = self.w_out = self.b_out = None
+
+    def children(self):
+        return [self.position]
+
+    # ---------------------------------------------------------------- tensors
+    def param_specs(self):
+        n, d, D = self.names, self.d_model, self.head_dim
+        specs = {f"{n['q']}.weight": ParamSpec((self.num_heads * D, d)),
+                 f"{n['o']}.weight": ParamSpec((d, self.num_heads * D))}
+        if not self.shares_kv:
+            specs[f"{n['k']}.weight"] = ParamSpec((self.num_kv_heads * D, d))
+            specs[f"{n['v']}.weight"] = ParamSpec((self.num_kv_heads * D, d))
+        if self.bias:
+            for key in list(specs):
+                w = specs[key]
+                specs[key.replace(".weight", ".bias")] = ParamSpec((w.shape[0],), storage="matrix", init="normal")
+        return specs
+
+    def load(self, params):
+        n = self.names
+        keys = ["q"] if self.shares_kv else ["q", "k", "v"]
+        self.w_in = torch.cat([params[f"{n[k]}.weight"] for k in keys], dim=0).contiguous()
+        self.w_out = params[f"{n['o']}.weight"].contiguous()
+        if self.bias:
+            self.b_in = torch.cat([params[f"{n[k]}.bias"] for k in keys], dim=0).contiguous()
+            self.b_out = params[f"{n['o']}.bias"].contiguous()
+
+    # ---------------------------------------------------------------- cache
+    def cache_need(self):
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    # ---------------------------------------------------------------- step
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
+        ops = self.ops
+        Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        write = cache.writable and not self.shares_kv
+        kv_heads_in_buf = 0 if self.shares_kv else Hkv
+        qkv = ops.linear(x, self.w_in, self.b_in)                  # [T, (Hq + 2*Hkv) * D]
+        table = self.position.rotary_table()
+        if table is None:
+            T = qkv.shape[0]
+            q = qkv[:, :Hq * D].view(T, Hq, D)
+            k = None if self.shares_kv else qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+            self.position.apply(q, k, ctx.positions)
+            inv_freq, style = None, 0
+        else:
+            inv_freq, style = table
+        ops.rope_store(qkv, Hq, kv_heads_in_buf, D, ctx.positions, ctx.token_seq, inv_freq, style,
+                       cache.k_pages, cache.v_pages, cache.block_table, cache.page_size, write)
+        out = torch.empty((qkv.shape[0], Hq * D), dtype=qkv.dtype, device=qkv.device)
+        ops.paged_attention(qkv, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
+                            ctx.query_start_loc, ctx.seq_lens, ctx.num_seqs, ctx.max_q_len, ctx.max_kv_len,
+                            self.scale, self.window or 0, out)
+        return ops.linear(out, self.w_out, self.b_out)
