@@ -1,0 +1,52 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions, error reporting.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace ttie {
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// Every exported function returns 0 or a negative code and leaves a message for ttie_last_error().
+void set_error(const char* fmt, ...);
+#define TTIE_FAIL(...) do { ::ttie::set_error(__VA_ARGS__); return -1; } while (0)
+#define TTIE_CHECK_LAUNCH(what) do { cudaError_t e_ = cudaGetLastError(); \
+    if (e_ != cudaSuccess) { ::ttie::set_error("%s: launch failed: %s", what, cudaGetErrorString(e_)); return -2; } } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block in a fixed order (warp shuffles, then the warp sums by warp 0): the
+// result does not depend on timing.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (threadIdx.x < nwarps) ? scratch[threadIdx.x] : 0.f;
+    if (warp == 0) { t = warp_sum(t); if (lane == 0) scratch[0] = t; }
+    __syncthreads();
+    return scratch[0];
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace ttie
