@@ -20,10 +20,13 @@ _STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch
 
 
 def random_tensors(config: ModelConfig, seed: int, std: float = 0.02, perturb_norms: bool = False,
-                   store_dtype: str = "float32") -> Dict[str, torch.Tensor]:
+                   store_dtype: str = "float32", device="cpu") -> Dict[str, torch.Tensor]:
+    """``device="cpu"`` (the default) gives bits that depend only on (config, seed); another
+    device draws there with that device's generator - quicker for models of billions of
+    parameters, and different bits."""
     from ..models.model import Model
     model = Model(model_spec(config))
-    gen = torch.Generator(device="cpu")
+    gen = torch.Generator(device=device)
     gen.manual_seed(int(seed))
     dt = _STORE[store_dtype]
     out = {}
@@ -33,13 +36,13 @@ def random_tensors(config: ModelConfig, seed: int, std: float = 0.02, perturb_no
         if ps.storage == "table":
             raise ValueError(f"no random rule for integer table {name}")
         if ps.init == "normal":
-            t = torch.randn(ps.shape, generator=gen, dtype=torch.float32) * std
+            t = torch.randn(ps.shape, generator=gen, dtype=torch.float32, device=device) * std
         elif ps.init == "ones":
-            t = torch.ones(ps.shape, dtype=torch.float32)
+            t = torch.ones(ps.shape, dtype=torch.float32, device=device)
             if perturb_norms:
-                t = t + torch.randn(ps.shape, generator=gen, dtype=torch.float32) * std
+                t = t + torch.randn(ps.shape, generator=gen, dtype=torch.float32, device=device) * std
         else:
-            t = torch.zeros(ps.shape, dtype=torch.float32)
+            t = torch.zeros(ps.shape, dtype=torch.float32, device=device)
         # vectors keep 32-bit storage (they are few and their precision matters)
         out[name] = t.to(torch.float32 if ps.storage == "vector" else dt).contiguous()
     return out
