@@ -1,0 +1,336 @@
+"""Each kernel alone against its plain float32 stand-in, at sizes other than the engine's:
+widths and vocabularies that are no power of two, 3 / 5 / 71 heads, head sizes in steps of 16,
+page sizes 1..64, pools filled with garbage and shuffled block tables so that a stray read
+shows, and inputs made so that one far key, a window's edge or a page's edge decides the result."""
+import math
+import random
+import struct
+
+import pytest
+import torch
+
+from plain_ops import PlainOps, uniform_from_state
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+PLAIN = PlainOps()
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tiny_transformer_inference_engine_b200.ops import get_ops
+    return get_ops(DEV)
+
+
+def rel(a, b):
+    return ((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30)).item()
+
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 1.2e-2}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,d,V", [(1, 64, 100), (37, 1000, 515), (5, 4544, 77)])
+def test_embed(ops, dtype, T, d, V):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(V, d, generator=g).to(DT[dtype])
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    ids[0] = V - 1
+    out = torch.empty(T, d, dtype=torch.float32, device=DEV)
+    ops.embed(ids.to(DEV), table.to(DEV), out)
+    exp = torch.empty(T, d)
+    PLAIN.embed(ids, table, exp)
+    assert torch.equal(out.cpu(), exp)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,d,eps", [(1, 64, 1e-5), (19, 1000, 1e-6), (3, 4544, 1e-3), (2, 11008, 1e-5)])
+def test_add_rmsnorm(ops, dtype, wdtype, T, d, eps):
+    g = torch.Generator().manual_seed(1)
+    resid = torch.randn(T, d, generator=g) * 3
+    delta = (torch.randn(T, d, generator=g)).to(DT[dtype])
+    w = (1 + 0.1 * torch.randn(d, generator=g)).to(DT[wdtype])
+    for dl in (delta, None):
+        r_gpu, out = resid.clone().to(DEV), torch.empty(T, d, dtype=DT[dtype], device=DEV)
+        ops.add_rmsnorm(r_gpu, None if dl is None else dl.to(DEV), w.to(DEV), eps, out)
+        r_cpu, exp = resid.clone(), torch.empty(T, d, dtype=DT[dtype])
+        PLAIN.add_rmsnorm(r_cpu, dl, w, eps, exp)
+        assert rel(r_gpu.cpu(), r_cpu) < 1e-6                   # the 32-bit residual sum itself
+        assert rel(out.float().cpu(), exp.float()) < (1e-5 if dtype == "float32" else 8e-3)
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32)
+    out = torch.empty(2, d, dtype=DT[dtype], device=DEV)
+    r_gpu = resid.clone().to(DEV)
+    ops.rmsnorm_rows(r_gpu, delta.to(DEV), rows.to(DEV), 2, w.to(DEV), eps, out)
+    exp = torch.empty(2, d, dtype=DT[dtype])
+    PLAIN.rmsnorm_rows(resid, delta, rows, 2, w, eps, exp)
+    assert torch.equal(r_gpu.cpu(), resid)                        # gathering leaves the stream untouched
+    assert rel(out.float().cpu(), exp.float()) < (1e-5 if dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("M,N,K,bias", [(1, 7, 5, False), (33, 515, 96, True), (130, 64, 1000, False), (5, 200, 4544, True)])
+def test_gemm_f32_is_true_32_bit(ops, M, N, K, bias):
+    g = torch.Generator().manual_seed(2)
+    x, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    b = torch.randn(N, generator=g) if bias else None
+    out = ops.linear(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV))
+    exp = x.double() @ w.double().T + (b.double() if bias else 0)
+    # TF32 would leave ~1e-3; FFMA with 32-bit accumulation leaves ~1e-6
+    assert rel(out.cpu(), exp) < 3e-6
+    # a strided input (a column slice) works too
+    big = torch.randn(M, K + 8, generator=g).to(DEV)
+    out2 = ops.linear(big[:, 3:3 + K], w.to(DEV), None)
+    assert rel(out2.cpu(), big[:, 3:3 + K].cpu().double() @ w.double().T) < 3e-6
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 4352, 4096), (300, 352, 176)])
+def test_linear_bf16(ops, M, N, K):
+    g = torch.Generator().manual_seed(3)
+    x, w = torch.randn(M, K, generator=g).bfloat16(), (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    b = torch.randn(N, generator=g).bfloat16()
+    exp = x.double() @ w.double().T
+    assert rel(ops.linear(x.to(DEV), w.to(DEV), None).float().cpu(), exp) < 8e-3
+    assert rel(ops.linear(x.to(DEV), w.to(DEV), b.to(DEV)).float().cpu(), exp + b.double()) < 8e-3
+    out32 = ops.linear(x.to(DEV), w.to(DEV), None, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32 and rel(out32.cpu(), exp) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,F", [(1, 176), (9, 1000), (4, 11008)])
+def test_swiglu(ops, dtype, T, F):
+    g = torch.Generator().manual_seed(4)
+    gu = (torch.randn(T, 2 * F, generator=g) * 4).to(DT[dtype])
+    gu[0, 0], gu[0, 1] = -80.0, 80.0
+    out = torch.empty(T, F, dtype=DT[dtype], device=DEV)
+    ops.swiglu(gu.to(DEV), out)
+    exp = torch.empty(T, F, dtype=DT[dtype])
+    PLAIN.swiglu(gu, exp)
+    assert torch.isfinite(out).all()
+    assert rel(out.float().cpu(), exp.float()) < (2e-6 if dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("Hq,Hkv,D,page,style,base", [(4, 1, 16, 16, 0, 1e4), (3, 1, 32, 8, 0, 5e5), (71, 1, 64, 64, 0, 1e4),
+                                                      (6, 2, 48, 5, 1, 2e4), (8, 8, 128, 1, 0, 1e4)])
+def test_rope_store(ops, dtype, Hq, Hkv, D, page, style, base):
+    g = torch.Generator().manual_seed(5)
+    lens = [(0, 7), (30, 1), (4090, 3)]                           # (start, new tokens): far positions too
+    T = sum(n for _, n in lens)
+    positions = torch.tensor([s + i for s, n in lens for i in range(n)], dtype=torch.int32)
+    token_seq = torch.tensor([i for i, (_, n) in enumerate(lens) for _ in range(n)], dtype=torch.int32)
+    width = max(-(-(s + n) // page) for s, n in lens)
+    nb = 3 * width + 1
+    perm = torch.randperm(nb - 1, generator=g) + 1
+    table = perm[:3 * width].view(3, width).to(torch.int32)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g).to(DT[dtype])
+    inv_freq = 1.0 / (base ** (torch.arange(0, D, 2).float() / D))
+    kp = torch.full((nb, Hkv, page, D), 777.0).to(DT[dtype])
+    vp = kp.clone()
+    q_gpu, kp_gpu, vp_gpu = qkv.clone().to(DEV), kp.clone().to(DEV), vp.clone().to(DEV)
+    ops.rope_store(q_gpu, Hq, Hkv, D, positions.to(DEV), token_seq.to(DEV), inv_freq.to(DEV), style, kp_gpu, vp_gpu,
+                   table.to(DEV), page, True)
+    PLAIN.rope_store(qkv, Hq, Hkv, D, positions, token_seq, inv_freq, style, kp, vp, table, page, True)
+    tol = 3e-6 if dtype == "float32" else 8e-3
+    assert rel(q_gpu.float().cpu(), qkv.float()) < tol
+    assert rel(kp_gpu.float().cpu(), kp.float()) < tol and rel(vp_gpu.float().cpu(), vp.float()) < tol
+    assert torch.equal(kp_gpu.cpu()[0], kp[0])                    # the scratch page is untouched
+    untouched = (kp == 777.0)
+    assert torch.equal(kp_gpu.cpu()[untouched], kp[untouched])    # nothing else was written
+    # no rotation, no store
+    q2 = qkv.clone().to(DEV)
+    ops.rope_store(q2, Hq, Hkv, D, positions.to(DEV), token_seq.to(DEV), None, 0, kp_gpu, vp_gpu, table.to(DEV), page, False)
+    assert torch.equal(q2.cpu(), qkv)
+
+
+# ------------------------------------------------------------------------------------------ attention
+def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed=0, spike=None):
+    """seqs: list of (kv_len, q_len).  spike=(seq, query index, key position): that query and that
+    key are made parallel and large so the key decides the row's output."""
+    g = torch.Generator().manual_seed(seed)
+    dt = DT[dtype]
+    N = len(seqs)
+    T = sum(q for _, q in seqs)
+    width = max(-(-L // page) for L, _ in seqs) + 1
+    nb = sum(-(-L // page) for L, _ in seqs) + 1
+    order = (torch.randperm(nb - 1, generator=g) + 1).tolist()
+    kp = torch.full((nb, Hkv, page, D), 1000.0).to(dt)            # garbage everywhere first
+    vp = torch.full((nb, Hkv, page, D), -1000.0).to(dt)
+    table = torch.zeros(N, width, dtype=torch.int32)
+    qkv = (torch.randn(T, (Hq + 2 * Hkv) * D, generator=g) * 0.7).to(dt)
+    dense, qsl = [], [0]
+    for i, (L, n) in enumerate(seqs):
+        k = (torch.randn(L, Hkv, D, generator=g) * 0.7).to(dt)
+        v = torch.randn(L, Hkv, D, generator=g).to(dt)
+        if spike is not None and spike[0] == i:
+            _, qi, kpos = spike
+            u = torch.randn(D, generator=g)
+            u = u / u.norm()
+            qkv[qsl[-1] + qi, :Hq * D] = (u * 14.0).repeat(Hq).to(dt)
+            k[kpos, :, :] = (u * 14.0).to(dt)
+        for pg in range(-(-L // page)):
+            phys = order.pop()
+            table[i, pg] = phys
+            lo, hi = pg * page, min(L, (pg + 1) * page)
+            kp[phys, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            vp[phys, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+        dense.append((k.float(), v.float()))
+        qsl.append(qsl[-1] + n)
+    seq_lens = torch.tensor([L for L, _ in seqs], dtype=torch.int32)
+    qsl_t = torch.tensor(qsl, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    out = torch.full((T, Hq * D), 5.0, dtype=dt, device=DEV)
+    max_q, max_kv = max(n for _, n in seqs), max(L for L, _ in seqs)
+    ops.paged_attention(qkv.to(DEV), Hq, Hkv, D, kp.to(DEV), vp.to(DEV), table.to(DEV), page, qsl_t.to(DEV),
+                        seq_lens.to(DEV), N, max_q, max_kv, scale, window, out, plan=plan)
+    exp = torch.empty(T, Hq * D)
+    G = Hq // Hkv
+    for i, (L, n) in enumerate(seqs):
+        k, v = dense[i]
+        q = qkv[qsl[i]:qsl[i + 1], :Hq * D].float().view(n, Hq, D)
+        qpos, kpos = torch.arange(L - n, L)[:, None], torch.arange(L)[None, :]
+        vis = kpos <= qpos
+        if window:
+            vis = vis & (kpos > qpos - window)
+        for h in range(Hq):
+            s = (q[:, h] @ k[:, h // G].T) * scale
+            p = torch.softmax(s.masked_fill(~vis, float("-inf")), -1)
+            exp[qsl[i]:qsl[i + 1], h * D:(h + 1) * D] = p @ v[:, h // G]
+    return out.float().cpu(), exp, dense, qsl
+
+
+SCENARIOS = {                                                     # like tests/test.py:33-38 of the reference
+    "prefill": [(33, 33), (1, 1), (130, 130)],
+    "decode": [(200, 1), (64, 1), (65, 1), (1, 1), (513, 1)],
+    "chunked": [(100, 7), (64, 2), (130, 66), (300, 129)],
+    "mixed": [(77, 77), (300, 1), (129, 2), (64, 64), (1000, 1)],
+}
+SHAPES = [(4, 1, 16, 16), (3, 1, 32, 8), (6, 2, 48, 32), (71, 1, 64, 64), (32, 1, 128, 64), (5, 5, 80, 3), (8, 1, 256, 16),
+          (2, 2, 20, 7)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("scenario", list(SCENARIOS))
+@pytest.mark.parametrize("Hq,Hkv,D,page", SHAPES)
+def test_paged_attention(ops, dtype, scenario, Hq, Hkv, D, page):
+    out, exp, _, _ = attention_case(ops, dtype, Hq, Hkv, D, page, SCENARIOS[scenario])
+    assert torch.isfinite(out).all()
+    assert rel(out, exp) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype,kernel,unit", [("float32", "simt", 32), ("bfloat16", "simt", 32), ("bfloat16", "mma", 64)])
+@pytest.mark.parametrize("splits", [2, 3, 7])
+def test_split_keys_merge(ops, dtype, kernel, unit, splits):
+    seqs = [(700, 1), (64, 1), (129, 2), (1, 1)]
+    split_len = -(-(-(-700 // splits)) // unit) * unit
+    n = -(-700 // split_len)
+    out, exp, _, _ = attention_case(ops, dtype, 8, 2, 64, 16, seqs, plan=(kernel, n, split_len))
+    assert rel(out, exp) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype,kernel", [("float32", "simt"), ("bfloat16", "simt"), ("bfloat16", "mma")])
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_window(ops, dtype, kernel, window):
+    out, exp, _, _ = attention_case(ops, dtype, 4, 2, 32, 8, [(150, 150), (90, 1), (300, 40)], window=window,
+                                    plan=(kernel, 1, 0))
+    assert rel(out, exp) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype,kernel", [("float32", "simt"), ("bfloat16", "mma"), ("bfloat16", "simt")])
+@pytest.mark.parametrize("kpos,why", [(0, "the first key"), (63, "last key of a page"), (64, "first key of a page"),
+                                      (447, "far key among hundreds"), (599, "the query's own position")])
+def test_one_key_decides(ops, dtype, kernel, kpos, why):
+    """Random inputs give near-uniform attention, which hides a misplaced key; here one key's score
+    stands out, so the row's output must be that key's value."""
+    seqs = [(50, 1), (600, 1), (64, 3)]
+    for plan in ((kernel, 1, 0), (kernel, 3, 256)):
+        out, exp, dense, qsl = attention_case(ops, dtype, 4, 1, 64, 64, seqs, plan=plan, spike=(1, 0, kpos))
+        row = out[qsl[1]].view(4, 64)
+        v = dense[1][1][kpos, 0]
+        assert (row - v).abs().max() < 2e-2, why
+        assert rel(out, exp) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_edge_key(ops, dtype):
+    """The key just outside the window must not count although its score would dominate; the key
+    just inside must."""
+    W = 100
+    for kpos, inside in ((500 - W, False), (500 - W + 1, True)):
+        out, exp, dense, qsl = attention_case(ops, dtype, 2, 1, 32, 16, [(501, 1)], window=W, spike=(0, 0, kpos))
+        v = dense[0][1][kpos, 0]
+        close = (out[0].view(2, 32) - v).abs().max() < 2e-2
+        assert bool(close) == inside
+        assert rel(out, exp) < TOL[dtype]
+
+
+def test_refuses_sizes_it_cannot_take(ops):
+    from tiny_transformer_inference_engine_b200.ops import KernelError
+    with pytest.raises(KernelError, match="head size 18"):
+        attention_case(ops, "float32", 2, 1, 18, 4, [(5, 5)])
+    with pytest.raises(KernelError, match="head size 272"):
+        attention_case(ops, "bfloat16", 2, 1, 272, 4, [(5, 5)])
+    with pytest.raises(KernelError, match="not supported"):
+        ops.linear(torch.zeros(2, 2, dtype=torch.float16, device=DEV), torch.zeros(2, 2, dtype=torch.float16, device=DEV), None) \
+            if False else ops.embed(torch.zeros(1, dtype=torch.int32, device=DEV),
+                                    torch.zeros(2, 2, dtype=torch.float16, device=DEV),
+                                    torch.zeros(1, 2, dtype=torch.float32, device=DEV))
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def sampler_state(rows):
+    st = torch.zeros(len(rows), 8, dtype=torch.int32)
+    for i, (seed, draws, top_k, temp, top_p, greedy) in enumerate(rows):
+        st[i] = torch.tensor([seed & 0x7fffffff, seed >> 31, draws, top_k,
+                              struct.unpack("<i", struct.pack("<f", temp))[0],
+                              struct.unpack("<i", struct.pack("<f", top_p))[0], greedy, 0], dtype=torch.int32)
+    return st
+
+
+@pytest.mark.parametrize("V", [256, 1000, 32000, 65024])
+def test_sampling_distribution_and_draw(ops, V):
+    g = torch.Generator().manual_seed(V)
+    rows = [(1, 0, 0, 1.0, 1.0, 0), (2, 5, 32, 0.8, 1.0, 0), (3, 1, 0, 0.7, 0.9, 0), (4, 9, 50, 1.3, 0.5, 0),
+            (5, 2, 1, 1.0, 1.0, 0), (6, 0, 0, 1.0, 1.0, 1), (7, 3, V + 5, 2.0, 0.999, 0), (8, 4, 3, 0.1, 0.3, 0)]
+    R = len(rows)
+    logits = torch.randn(R, V, generator=g) * 3
+    logits[5, 17] = logits[5, 400 % V] = logits[5].max() + 1     # equal maxima: the lowest index wins
+    state = sampler_state(rows)
+    slot_ids = torch.arange(R, dtype=torch.int32)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    probs = torch.zeros(R, V, device=DEV)
+    st_gpu = state.clone().to(DEV)
+    ops.sample(logits.to(DEV), slot_ids.to(DEV), st_gpu, out, probs_out=probs)
+    out, probs, st_after = out.cpu(), probs.cpu(), st_gpu.cpu()
+    assert torch.equal(st_after[:, 2], state[:, 2] + 1)           # every draw counter advanced
+    for r, (seed, draws, top_k, temp, top_p, greedy) in enumerate(rows):
+        if greedy:
+            assert out[r] == min(17, 400 % V)
+            continue
+        exp = PLAIN.filtered_probs(logits[r], temp, top_k, top_p).float()
+        assert torch.equal(probs[r] > 0, exp > 0), f"row {r}: kept sets differ"
+        assert torch.allclose(probs[r], exp, atol=2e-6, rtol=1e-4)
+        u = uniform_from_state(seed & 0x7fffffff, seed >> 31, draws)
+        cdf = torch.cumsum(probs[r].double(), 0)
+        tok = int(out[r])
+        assert probs[r, tok] > 0
+        lo = cdf[tok - 1].item() if tok else 0.0
+        assert lo - 1e-5 <= u <= cdf[tok].item() + 1e-5, (r, u, lo, cdf[tok].item())
+    assert out[4] == int(torch.argmax(logits[4]))                 # top_k = 1 is argmax (tests/test_sampling.py:6-12)
+
+
+def test_sampling_frequencies(ops):
+    """Many draws of one row follow its probabilities."""
+    V, n = 50, 4000
+    logits = torch.randn(1, V, generator=torch.Generator().manual_seed(0)) * 2
+    state = sampler_state([(123, 0, 10, 0.9, 0.95, 0)]).to(DEV)
+    slot = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty(1, dtype=torch.int32, device=DEV)
+    lg, counts = logits.to(DEV), torch.zeros(V)
+    for _ in range(n):
+        ops.sample(lg, slot, state, out)
+        counts[int(out)] += 1
+    exp = PLAIN.filtered_probs(logits[0], 0.9, 10, 0.95).float()
+    assert int(state[0, 2]) == n
+    assert (counts[exp == 0] == 0).all()
+    assert (counts / n - exp).abs().max() < 0.03

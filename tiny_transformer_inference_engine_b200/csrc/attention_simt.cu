@@ -206,6 +206,17 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
     }
 }
 
+}  // namespace
+
+namespace ttie {
+int attn_merge_bf16(const float* ws_o, const float* ws_ml, void* out, int rows, int num_splits, int D, cudaStream_t s) {
+    attn_merge_kernel<__nv_bfloat16><<<rows, D >= 128 ? 128 : 64, 0, s>>>(ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    TTIE_CHECK_LAUNCH("attention merge");
+    return 0;
+}
+}  // namespace ttie
+
+namespace {
 template <typename T, int DPL>
 int launch(const AttnParams& p, int T_tokens, cudaStream_t s) {
     const size_t smem = ((size_t)ROWS * p.D + 2 * (size_t)BK * (p.D + 4)) * sizeof(float);

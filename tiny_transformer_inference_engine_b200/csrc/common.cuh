@@ -47,6 +47,9 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[0];
 }
 
+// merges split-KV partial results (attention_simt.cu)
+int attn_merge_bf16(const float* ws_o, const float* ws_ml, void* out, int rows, int num_splits, int D, cudaStream_t s);
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 }  // namespace ttie

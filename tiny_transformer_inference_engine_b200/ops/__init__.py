@@ -34,6 +34,9 @@ _SIGNATURES = {
     "ttie_paged_attention": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
                              _c_void, _c_int, _c_void],
+    "ttie_paged_attention_mma": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
+                                 _c_void, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
 }
 
@@ -67,7 +70,9 @@ class CudaOps:
             fn.argtypes, fn.restype = argtypes, _c_int
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
-        self.attn_target_ctas = 4 * NUM_SMS
+        self.attn_target_ctas = 2 * NUM_SMS
+        for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows"):
+            getattr(self.lib, name).restype = _c_int
 
     # ------------------------------------------------------------------ helpers
     def _check(self, rc: int, what: str):
@@ -140,31 +145,46 @@ class CudaOps:
                                              self._stream(qkv)), "rope_store")
         self.launches += 1
 
-    def attention_splits(self, num_seqs, num_heads, num_kv_heads, max_q_len, max_kv_len):
-        """How the key range is split: (num_splits, split_len).  A split is made only when the
-        query rows alone cannot fill the GPU; the split length is a multiple of 32 keys."""
+    def attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len):
+        """Which attention kernel runs and how the key range is split: (kernel, num_splits,
+        split_len).  bfloat16 with a head size that is a multiple of 16 up to 128 runs on
+        tensor cores; everything else runs the general float32-arithmetic kernel.  The key
+        range is split only when the query rows alone cannot fill the GPU."""
         G = num_heads // num_kv_heads
-        base = num_seqs * num_kv_heads * math.ceil(max_q_len * G / 32)
-        if base >= self.attn_target_ctas // 2 or max_kv_len <= 256:
-            return 1, 0
-        want = min(math.ceil(self.attn_target_ctas / base), math.ceil(max_kv_len / 128))
-        split_len = math.ceil(math.ceil(max_kv_len / want) / 32) * 32
-        return math.ceil(max_kv_len / split_len), split_len
+        rows = max_q_len * G
+        if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
+            kernel, tile_rows, unit, min_len = "mma", self.lib.ttie_attn_mma_tile_rows(max_q_len, num_heads, num_kv_heads), 64, 256
+        else:
+            kernel, tile_rows, unit, min_len = "simt", 32, 32, 128
+        base = num_seqs * num_kv_heads * math.ceil(rows / tile_rows)
+        if base >= NUM_SMS or max_kv_len <= min_len:
+            return kernel, 1, 0
+        want = min(math.ceil(self.attn_target_ctas / base), math.ceil(max_kv_len / min_len))
+        split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
+        num_splits = math.ceil(max_kv_len / split_len)
+        return (kernel, num_splits, split_len) if num_splits > 1 else (kernel, 1, 0)
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table, page_size,
                         query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out,
-                        splits=None):
+                        plan=None):
         T = qkv.shape[0]
-        num_splits, split_len = splits if splits is not None else self.attention_splits(
-            num_seqs, num_heads, num_kv_heads, max_q_len, max_kv_len)
+        kernel, num_splits, split_len = plan if plan is not None else self.attention_plan(
+            qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
         scratch = None
         if num_splits > 1:
             scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
-        self._check(self.lib.ttie_paged_attention(
-            _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
-            _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads, head_dim,
-            max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch), self._dt(qkv),
-            self._stream(qkv)), "paged_attention")
+        if kernel == "mma":
+            self._check(self.lib.ttie_paged_attention_mma(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
+                head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
+                self._stream(qkv)), "paged_attention_mma")
+        else:
+            self._check(self.lib.ttie_paged_attention(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
+                head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
+                self._dt(qkv), self._stream(qkv)), "paged_attention")
         self.launches += 2 if num_splits > 1 else 1
 
     def sample(self, logits, slot_ids, state, out, probs_out=None):
