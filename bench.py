@@ -105,7 +105,7 @@ def build_engine(cfg, layers, batch, ctx, graphs, seed=0):
     mc = ModelConfig.from_dict({**cfg, "num_layers": layers})
     w = random_tensors(mc, seed, store_dtype="bfloat16", device="cuda:0")
     page = 64
-    pages = batch * (-(-ctx // page)) + 2
+    pages = batch * (-(-ctx // page)) + 2 * batch + 2        # admission keeps a growth page per running request
     ec = EngineConfig(dtype="bfloat16", device="cuda:0", use_cuda_graphs=True,
                       cache=CacheConfig(block_size=page, num_gpu_blocks=pages),
                       sched=SchedulerConfig(max_num_seqs=batch, max_num_batched_tokens=max(2048, batch),
@@ -239,22 +239,36 @@ def main():
                 "of": pk["source"]}
 
     # ---- decode end to end through Engine.step(): host tokens in, host tokens out
-    prompts = torch.randint(0, vocab, (batch, start_len), generator=g).tolist()
+    # requests that finish their prompt early decode while the others still prefill, so each gets
+    # room for those extra tokens and none finishes inside the timed region
+    prefill_steps = -(-batch * start_len // 2048) + batch
+    room = W + K + prefill_steps + 2
+    e2e_prompt = ctx - room
+    prompts = torch.randint(0, vocab, (batch, e2e_prompt), generator=g).tolist()
     for p in prompts:
-        eng.add_request(p, SamplingParams(max_new_tokens=W + K, temperature=0.8, ignore_eos=True))
+        eng.add_request(p, SamplingParams(max_new_tokens=room, temperature=0.8, ignore_eos=True))
     while any(r.remaining > 1 for r in list(eng.scheduler.running) + list(eng.scheduler.waiting)) or eng.scheduler.waiting:
         eng.step()
-    for _ in range(W - 1):
+    for _ in range(W):
         eng.step()
-    n_e2e = min(K, W + K - W - 1)
+    n_e2e = K
     got = [0]
 
     def e2e_step(_):
         got[0] += len(eng.step())
 
+    if os.environ.get("TTIE_BENCH_PROFILE"):
+        import cProfile, pstats
+        pr = cProfile.Profile(); pr.enable()
     e_ms = timed(e2e_step, n_e2e)
-    while eng.scheduler.has_work:
-        eng.step()
+    if os.environ.get("TTIE_BENCH_PROFILE"):
+        pr.disable()
+        pstats.Stats(pr, stream=sys.stderr).sort_stats("tottime").print_stats(12)
+        print(eng.stats(), file=sys.stderr)
+    assert got[0] == batch * n_e2e, (got[0], batch, n_e2e)
+    for r in list(eng.scheduler.running):
+        eng.manager.release(r.rid)
+    eng.scheduler.running.clear()
     h2d = 4 * (8 * (batch + 4) + batch * (-(-ctx // 64)) + 64)          # the step's packed int32 metadata
     e2e = {"value": got[0] / (e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
            "steps": n_e2e}
@@ -281,7 +295,7 @@ def main():
                    "kv_heads": cfg["num_kv_heads"], "head_dim": nums["head_dim"], "ffn_hidden": cfg["hidden_size"],
                    "vocab": vocab, "page_size": 64, "prompt_len": start_len, "l2": "inputs larger than L2 (weights 11 GB per step)",
                    "cuda_graph": True, "sampling": "temperature 0.8 on device"},
-        "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points, "clocks": clock_rec,
+        "e2e": e2e, "gpu_launches": launches, "e2e_prompt_len": e2e_prompt, "prefill": prefill, "roofline": roofline, "points": points, "clocks": clock_rec,
         "impl": "ours",
     }
     print(json.dumps(out))
