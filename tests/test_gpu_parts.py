@@ -1,0 +1,228 @@
+"""Each part alone against the plain model's function, and the generality of the assembly:
+a toy mixer with state of its own, a toy architecture with a window in some layers, a layer
+that runs twice and a layer that reads another layer's cache - all registered from here,
+without a change to the framework's files."""
+import math
+
+import pytest
+import torch
+
+import plain_model as pm
+import trace_util as tu
+from gpu_util import TOL
+
+from tiny_transformer_inference_engine_b200 import Engine, ModelConfig, EngineConfig, CacheConfig, SchedulerConfig
+from tiny_transformer_inference_engine_b200 import register_model, register_part
+from tiny_transformer_inference_engine_b200.parts.base import (PartSpec, LayerSpec, RunEntry, ModelSpec, Mixer, ParamSpec,
+                                                                FixedStateNeed, StepContext, PagedKVView)
+from tiny_transformer_inference_engine_b200.registry import build_part, unregister_model, unregister_part
+from tiny_transformer_inference_engine_b200.weights import random_tensors
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tiny_transformer_inference_engine_b200.ops import get_ops
+    return get_ops(DEV)
+
+
+def rel(a, b):
+    return ((a.double() - b.double()).abs().max() / b.double().abs().max()).item()
+
+
+def ctx_for(ops, dtype, seqs, page, tables):
+    """A StepContext for requests given as (start, new tokens)."""
+    pos = [s + i for s, n in seqs for i in range(n)]
+    tseq = [i for i, (_, n) in enumerate(seqs) for _ in range(n)]
+    qsl = [0]
+    for _, n in seqs:
+        qsl.append(qsl[-1] + n)
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return StepContext(ops=ops, dtype=dtype, device=torch.device(DEV), num_tokens=len(pos), num_seqs=len(seqs),
+                       max_q_len=max(n for _, n in seqs), max_kv_len=max(s + n for s, n in seqs), token_ids=t([0] * len(pos)),
+                       positions=t(pos), token_seq=t(tseq), query_start_loc=t(qsl), seq_lens=t([s + n for s, n in seqs]),
+                       slot_ids=t(list(range(len(seqs)))), logit_rows=t([0]), num_logit_rows=0, block_tables={0: tables})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(ops, dtype):
+    part = build_part("norm", PartSpec("rmsnorm", "n", {"dim": 200, "eps": 3e-4}))
+    part.bind(ops, DT[dtype], torch.device(DEV))
+    w = 1 + 0.2 * torch.randn(200)
+    part.load({"weight": w.to(DEV)})
+    resid, delta = torch.randn(7, 200), torch.randn(7, 200).to(DT[dtype])
+    r = resid.clone().to(DEV)
+    out = part.add_norm(r, delta.to(DEV))
+    x = resid + delta.float()
+    assert rel(r.cpu(), x) < 1e-6
+    assert rel(out.float().cpu(), pm.plain_rmsnorm(x, w, 3e-4)) < (1e-5 if dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_ffn_part(ops, dtype):
+    part = build_part("ffn", PartSpec("swiglu", "mlp", {"d_model": 72, "hidden": 200, "bias": True}))
+    part.bind(ops, DT[dtype], torch.device(DEV))
+    g = torch.Generator().manual_seed(0)
+    w = {k: (torch.randn(ps.shape, generator=g) * 0.1).to(DT[dtype]) for k, ps in part.param_specs().items()}
+    part.load({k: v.to(DEV) for k, v in w.items()})
+    x = torch.randn(9, 72, generator=g).to(DT[dtype])
+    out = part.forward(x.to(DEV), None)
+    exp = pm.plain_swiglu(x.float(), {f"mlp.{k}": v.float() for k, v in w.items()}, "mlp")
+    assert rel(out.float().cpu(), exp) < (1e-5 if dtype == "float32" else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("style", ["interleaved", "half"])
+def test_attention_part_with_position_encoding(ops, dtype, style):
+    """The mixer alone: a whole sequence in one step, then the same in two portions from the cache."""
+    d, Hq, Hkv, D, page, S = 96, 6, 2, 16, 4, 23
+    cfg = {"d_model": d, "num_heads": Hq, "num_kv_heads": Hkv, "rope_theta": 777.0}
+    part = build_part("mixer", PartSpec("attention", "attn", {
+        "d_model": d, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D, "bias": True,
+        "position": PartSpec("rope", "", {"dim": D, "base": 777.0, "style": style})}))
+    part.bind(ops, DT[dtype], torch.device(DEV))
+    g = torch.Generator().manual_seed(1)
+    w = {k: (torch.randn(ps.shape, generator=g) * 0.1).to(DT[dtype]) for k, ps in part.param_specs().items()}
+    part.load({k: v.to(DEV) for k, v in w.items()})
+    x = torch.randn(S, d, generator=g).to(DT[dtype])
+    exp = pm.plain_mqa(x.float(), {f"attn.{k}": v.float() for k, v in w.items()}, "attn", cfg, torch.arange(S), style=style)
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    for cuts in ([S], [10, 13], [1, 2, 20]):
+        kp = torch.zeros(8, Hkv, page, D, dtype=DT[dtype], device=DEV)
+        vp = torch.zeros_like(kp)
+        table = torch.tensor([[5, 2, 7, 1, 3, 6]], dtype=torch.int32, device=DEV)
+        outs, start = [], 0
+        for n in cuts:
+            ctx = ctx_for(ops, DT[dtype], [(start, n)], page, table)
+            outs.append(part.forward(x[start:start + n].to(DEV), ctx, PagedKVView(kp, vp, table, page)))
+            start += n
+        assert rel(torch.cat(outs).float().cpu(), exp) < tol, cuts
+
+
+# ------------------------------------------------------------------------------------------ toy parts
+class ToyDecayMixer(Mixer):
+    """A mixer with state of its own and no pages: s_t = a * s_{t-1} + W x_t per request, y_t = s_t.
+    Its state lives in the state slot of the request; a portion advances it token by token."""
+
+    def __init__(self, prefix, dim, decay):
+        super().__init__(prefix)
+        self.dim, self.decay = dim, decay
+
+    def param_specs(self):
+        return {"mix.weight": ParamSpec((self.dim, self.dim))}
+
+    def load(self, params):
+        self.w = params["mix.weight"]
+
+    def cache_need(self):
+        return FixedStateNeed((self.dim,), "float32")
+
+    def forward(self, x, ctx, cache):
+        u = self.ops.linear(x, self.w, None).float()
+        y = torch.empty_like(u)
+        qsl, slots = ctx.host["query_start_loc"], ctx.slot_ids.tolist()
+        for i in range(ctx.num_seqs):
+            s = cache.state[slots[i]]
+            for t in range(qsl[i], qsl[i + 1]):
+                s = self.decay * s + u[t]
+                y[t] = s
+            cache.state[slots[i]] = s
+        return y.to(x.dtype)
+
+
+def toy_spec(config):
+    d, D = config.d_model, config.head_dim
+    norm = lambda p: PartSpec("rmsnorm", p, {"dim": d, "eps": config.rms_norm_eps})
+    ffn = lambda p: PartSpec("swiglu", p, {"d_model": d, "hidden": config.hidden_size, "bias": False})
+    rope = PartSpec("rope", "", {"dim": D, "base": config.rope_theta, "style": "interleaved"})
+
+    def attn(p, **kw):
+        return PartSpec("attention", p, {"d_model": d, "num_heads": config.num_heads, "num_kv_heads": config.num_kv_heads,
+                                         "head_dim": D, "position": rope, **kw})
+    mixers = [attn("layers.0.attn"), PartSpec("toy_decay", "layers.1.toy", {"dim": d, "decay": 0.5}),
+              attn("layers.2.attn", window=config.extra["window"]), attn("layers.3.attn", shares_kv=True)]
+    layers = [LayerSpec(PartSpec("pre_norm", f"layers.{i}", {"mixer_norm": norm(f"layers.{i}.n1"), "mixer": m,
+                                                              "ffn_norm": norm(f"layers.{i}.n2"), "ffn": ffn(f"layers.{i}.mlp")}))
+              for i, m in enumerate(mixers)]
+    # layer 0 runs twice (each run with a cache of its own); layer 3 reads the cache of the first run of layer 0
+    order = (RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(0), RunEntry(3, cache_from=0))
+    return ModelSpec(d_model=d, vocab_size=config.vocab_size, max_seq_len=config.max_seq_len,
+                     embedding=PartSpec("token", "emb", {"vocab_size": config.vocab_size, "dim": d}),
+                     layers=tuple(layers), run_order=order, final_norm=norm("final_norm"),
+                     head=PartSpec("linear", "lm_head", {"dim": d, "vocab_size": config.vocab_size}))
+
+
+def toy_plain_forward(cfg, w, tokens):
+    """The toy architecture written out plainly, whole sequence, no cache."""
+    w = {k: v.float() for k, v in w.items()}
+    S, d, Hq, Hkv = len(tokens), cfg["d_model"], cfg["num_heads"], cfg["num_kv_heads"]
+    D, eps = d // Hq, cfg["rms_norm_eps"]
+    x = w["emb.weight"][torch.tensor(tokens)]
+    cos, sin = pm.plain_rope_tables(D, torch.arange(S), cfg["rope_theta"])
+    kept = {}
+
+    def attn(h, p, window=None, kv=None, keep=None):
+        q = pm.plain_rope((h @ w[f"{p}.q_proj.weight"].T).view(S, Hq, D), cos, sin)
+        if kv is None:
+            k = pm.plain_rope((h @ w[f"{p}.k_proj.weight"].T).view(S, Hkv, D), cos, sin)
+            v = (h @ w[f"{p}.v_proj.weight"].T).view(S, Hkv, D)
+        else:
+            k, v = kv
+        if keep:
+            kept[keep] = (k, v)
+        return pm.plain_attention(q, k, v, 1 / math.sqrt(D), window).reshape(S, d) @ w[f"{p}.out.weight"].T
+
+    def toy(h, p):
+        u, s, ys = h @ w[f"{p}.mix.weight"].T, torch.zeros(d), []
+        for t in range(S):
+            s = 0.5 * s + u[t]
+            ys.append(s)
+        return torch.stack(ys)
+
+    def block(x, i, mixer):
+        x = x + mixer(pm.plain_rmsnorm(x, w[f"layers.{i}.n1.weight"], eps))
+        return x + pm.plain_swiglu(pm.plain_rmsnorm(x, w[f"layers.{i}.n2.weight"], eps), w, f"layers.{i}.mlp")
+
+    x = block(x, 0, lambda h: attn(h, "layers.0.attn", keep="first"))
+    x = block(x, 1, lambda h: toy(h, "layers.1.toy"))
+    x = block(x, 2, lambda h: attn(h, "layers.2.attn", window=cfg["window"]))
+    x = block(x, 0, lambda h: attn(h, "layers.0.attn"))
+    x = block(x, 3, lambda h: attn(h, "layers.3.attn", kv=kept["first"]))
+    return pm.plain_rmsnorm(x, w["final_norm.weight"], eps) @ w["lm_head.weight"].T
+
+
+@pytest.fixture
+def toy_registered():
+    register_part("mixer", "toy_decay")(ToyDecayMixer)
+    register_model("toy_mix")(toy_spec)
+    yield
+    unregister_model("toy_mix")
+    unregister_part("mixer", "toy_decay")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["whole", "decode", "portions", "mixed"])
+def test_toy_architecture_is_built_and_stepped(toy_registered, dtype, mode):
+    cfg = dict(architecture="toy_mix", vocab_size=300, d_model=80, num_layers=4, num_heads=5, num_kv_heads=1,
+               hidden_size=112, max_seq_len=256, rope_theta=3000.0, rms_norm_eps=1e-5, window=21)
+    mc = ModelConfig.from_dict(cfg)
+    assert mc.extra == {"window": 21}
+    w = random_tensors(mc, 3, perturb_norms=True)
+    assert "layers.1.toy.mix.weight" in w and "layers.3.attn.k_proj.weight" not in w
+    g = torch.Generator().manual_seed(8)
+    reqs = {f"r{i}": torch.randint(0, 300, (n,), generator=g).tolist() for i, n in enumerate((70, 150, 33, 256, 90))}
+    steps = {"whole": tu.whole, "decode": tu.prefill_then_decode, "portions": tu.portions, "mixed": tu.mixed}[mode](reqs)
+    page = 8
+    ec = EngineConfig(dtype=dtype, device=DEV, use_cuda_graphs=False,
+                      cache=CacheConfig(block_size=page, num_gpu_blocks=tu.max_live_tokens(steps) // page + 1),
+                      sched=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64))
+    eng = Engine(mc, w, ec)
+    # three runs own pages: two full-attention runs share a group, the windowed run has its own
+    assert [len(g_.entries) for g_ in eng.manager.groups] == [2, 1] and list(eng.manager.entry_state) == [1]
+    exp = {rid: toy_plain_forward(cfg, w, toks) for rid, toks in reqs.items()}
+    got = tu.run_steps(eng, steps)
+    bad = tu.first_wrong(got, exp, TOL[dtype])
+    assert bad is None, f"first wrong place {bad}"
