@@ -52,11 +52,16 @@ class PlainOps:
         y = x * torch.rsqrt(x.square().mean(dim=-1, keepdim=True) + eps) * weight.float()
         out.copy_(y.to(out.dtype))
 
-    def linear(self, x, w, bias, out_dtype=None):
+    def linear(self, x, w, bias, out_dtype=None, partial_ok=False):
         y = x.float() @ w.float().T
         if bias is not None:
             y = y + bias.float()
         return y.to(out_dtype or x.dtype)
+
+    def linear_swiglu(self, x, w_gu, b_gu, hidden):
+        act = torch.empty((x.shape[0], hidden), dtype=x.dtype)
+        self.swiglu(self.linear(x, w_gu, b_gu), act)
+        return act
 
     def swiglu(self, gate_up, out):
         F = out.shape[1]
@@ -64,7 +69,7 @@ class PlainOps:
         out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
 
     def rope_store(self, qkv, num_heads, num_kv_heads, head_dim, positions, token_seq, inv_freq, style,
-                   k_pages, v_pages, block_table, page_size, write_kv):
+                   k_pages, v_pages, block_table, page_size, write_kv, q_out=None, cs_table=None):
         T = qkv.shape[0]
         D = head_dim
         n_rot = num_heads + num_kv_heads

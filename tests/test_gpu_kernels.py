@@ -127,6 +127,7 @@ def test_rope_store(ops, dtype, Hq, Hkv, D, page, style, base):
     inv_freq = 1.0 / (base ** (torch.arange(0, D, 2).float() / D))
     kp = torch.full((nb, Hkv, page, D), 777.0).to(DT[dtype])
     vp = kp.clone()
+    qkv0, kp0, vp0 = qkv.clone(), kp.clone(), vp.clone()
     q_gpu, kp_gpu, vp_gpu = qkv.clone().to(DEV), kp.clone().to(DEV), vp.clone().to(DEV)
     ops.rope_store(q_gpu, Hq, Hkv, D, positions.to(DEV), token_seq.to(DEV), inv_freq.to(DEV), style, kp_gpu, vp_gpu,
                    table.to(DEV), page, True)
@@ -137,6 +138,17 @@ def test_rope_store(ops, dtype, Hq, Hkv, D, page, style, base):
     assert torch.equal(kp_gpu.cpu()[0], kp[0])                    # the scratch page is untouched
     untouched = (kp == 777.0)
     assert torch.equal(kp_gpu.cpu()[untouched], kp[untouched])    # nothing else was written
+    if style == 0 and D % 4 == 0:
+        # the vectorised kernel with the step's cos/sin table gives the same
+        cs = ops.rope_table(positions.to(DEV), inv_freq.to(DEV))
+        theta = positions.float()[:, None] * inv_freq[None, :]
+        assert rel(cs.cpu()[..., 0], theta.cos()) < 1e-6 and rel(cs.cpu()[..., 1], theta.sin()) < 1e-6
+        q3, kp3, vp3 = qkv0.clone().to(DEV), kp0.clone().to(DEV), vp0.clone().to(DEV)
+        ops.rope_store(q3, Hq, Hkv, D, positions.to(DEV), token_seq.to(DEV), inv_freq.to(DEV), 0, kp3, vp3, table.to(DEV),
+                       page, True, cs_table=cs)
+        assert rel(q3.float().cpu(), qkv.float()) < tol
+        assert rel(kp3.float().cpu(), kp.float()) < tol and rel(vp3.float().cpu(), vp.float()) < tol
+        assert torch.equal(kp3.cpu()[untouched], kp[untouched])
     # no rotation, no store
     q2 = qkv.clone().to(DEV)
     ops.rope_store(q2, Hq, Hkv, D, positions.to(DEV), token_seq.to(DEV), None, 0, kp_gpu, vp_gpu, table.to(DEV), page, False)
@@ -334,3 +346,75 @@ def test_sampling_frequencies(ops):
     assert int(state[0, 2]) == n
     assert (counts[exp == 0] == 0).all()
     assert (counts / n - exp).abs().max() < 0.03
+
+
+# ------------------------------------------------------------------------------------------ weight-streaming product
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 4352, 4096), (3, 515, 200), (16, 1000, 176), (9, 4096, 11008),
+                                   (5, 72, 8), (16, 33, 4544)])
+def test_skinny_gemm_all_epilogues(ops, M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    b = torch.randn(N, generator=g).bfloat16()
+    exp = x.double() @ w.double().T
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    assert ops._skinny_ok(xd, wd)
+    before = ops.launches
+    assert rel(ops.linear(xd, wd, None).float().cpu(), exp) < 8e-3
+    assert rel(ops.linear(xd, wd, bd).float().cpu(), exp + b.double()) < 8e-3
+    out32 = ops.linear(xd, wd, bd, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32 and rel(out32.cpu(), exp + b.double()) < 1e-5
+    assert ops.launches == before + 3                              # this package's kernel ran, not the library's
+    part = ops.linear(xd, wd, None, partial_ok=True)
+    if part.dim() == 3:
+        assert part.dtype == torch.float32 and rel(part.sum(0).cpu(), exp) < 1e-5
+    # forced K split: partial sums feed add_rmsnorm and rope_store
+    for kslice in (128, 256):
+        S = -(-K // kslice)
+        part = torch.empty(S, M, N, dtype=torch.float32, device=DEV)
+        rc = ops.lib.ttie_skinny_gemm(xd.data_ptr(), xd.stride(0), wd.data_ptr(), wd.stride(0), None, part.data_ptr(), N,
+                                      M, N, K, kslice, 1, 0, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        assert rel(part.sum(0).cpu(), exp) < 1e-5
+    if N % 2 == 0:
+        F = N // 2
+        act = ops.linear_swiglu(xd, wd, bd, F)
+        gu = exp + b.double()
+        ref = gu[:, :F] * torch.sigmoid(gu[:, :F]) * gu[:, F:]
+        assert rel(act.float().cpu(), ref) < 1.2e-2
+
+
+def test_partial_sums_feed_norm_and_rope(ops):
+    g = torch.Generator().manual_seed(7)
+    S, T, d = 3, 5, 200
+    part = torch.randn(S, T, d, generator=g)
+    resid = torch.randn(T, d, generator=g)
+    w = 1 + 0.1 * torch.randn(d, generator=g)
+    r_gpu, out = resid.clone().to(DEV), torch.empty(T, d, dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(r_gpu, part.to(DEV), w.to(DEV), 1e-5, out)
+    r_cpu, exp = resid.clone(), torch.empty(T, d, dtype=torch.bfloat16)
+    PLAIN.add_rmsnorm(r_cpu, part.sum(0), w, 1e-5, exp)
+    assert rel(r_gpu.cpu(), r_cpu) < 1e-6 and rel(out.float().cpu(), exp.float()) < 8e-3
+    rows = torch.tensor([4, 1], dtype=torch.int32)
+    out2 = torch.empty(2, d, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm_rows(resid.to(DEV), part.to(DEV), rows.to(DEV), 2, w.to(DEV), 1e-5, out2)
+    exp2 = torch.empty(2, d, dtype=torch.bfloat16)
+    PLAIN.rmsnorm_rows(resid, part.sum(0), rows, 2, w, 1e-5, exp2)
+    assert rel(out2.float().cpu(), exp2.float()) < 8e-3
+    # rope_store from partial sums == rope_store of their sum
+    Hq, Hkv, D, page = 5, 1, 32, 4
+    width = (Hq + 2 * Hkv) * D
+    part = torch.randn(S, T, width, generator=g)
+    positions = torch.tensor([0, 1, 2, 3, 9], dtype=torch.int32)
+    token_seq = torch.tensor([0, 0, 0, 0, 1], dtype=torch.int32)
+    table = torch.tensor([[2, 0, 0], [1, 3, 4]], dtype=torch.int32)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))
+    kp, vp = torch.zeros(5, Hkv, page, D, dtype=torch.bfloat16, device=DEV), torch.zeros(5, Hkv, page, D, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=DEV)
+    ops.rope_store(part.to(DEV), Hq, Hkv, D, positions.to(DEV), token_seq.to(DEV), inv_freq.to(DEV), 0, kp, vp, table.to(DEV),
+                   page, True, q_out=q_out)
+    summed = part.sum(0)
+    kp2, vp2 = torch.zeros(5, Hkv, page, D), torch.zeros(5, Hkv, page, D)
+    PLAIN.rope_store(summed, Hq, Hkv, D, positions, token_seq, inv_freq, 0, kp2, vp2, table, page, True)
+    assert rel(q_out.float().cpu(), summed[:, :Hq * D]) < 8e-3
+    assert rel(kp.float().cpu(), kp2) < 8e-3 and rel(vp.float().cpu(), vp2) < 8e-3

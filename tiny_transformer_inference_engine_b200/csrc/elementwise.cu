@@ -20,7 +20,7 @@ void set_error(const char* fmt, ...) {
 using namespace ttie;
 
 extern "C" const char* ttie_last_error() { return ttie::g_error; }
-extern "C" int ttie_abi_version() { return 3; }
+extern "C" int ttie_abi_version() { return 4; }
 
 // ------------------------------------------------------------------------------------------ embed
 template <typename T>
@@ -48,8 +48,11 @@ extern "C" int ttie_embed(const int* ids, const void* table, float* out, int T, 
 // ------------------------------------------------------------------------------------------ rmsnorm
 // One block per row.  resid (float32) += delta; out = rmsnorm(resid) * w.  `rows` (optional)
 // gathers rows and then leaves resid untouched.
+// `dpart` (optional, instead of delta): float32 partial sums [S][rows of resid][d] of a K-split matrix
+// product; they are added in the order s = 0..S-1.
 template <typename T, typename W>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const int* __restrict__ rows,
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart,
+                                   int S, long long part_stride, const int* __restrict__ rows,
                                    const W* __restrict__ weight, T* __restrict__ out, int d, float eps) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
@@ -62,8 +65,13 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = x[i];
         if (dl) v += to_f32<T>(dl[i]);
+        if (dpart) {
+            float a = 0.f;
+            for (int sp = 0; sp < S; ++sp) a += dpart[sp * part_stride + src + i];
+            v += a;
+        }
         row[i] = v;
-        if (!rows && dl) x[i] = v;
+        if (!rows && (dl || dpart)) x[i] = v;
         ss += v * v;
     }
     ss = block_sum(ss, scratch);
@@ -72,32 +80,112 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
         o[i] = from_f32<T>(row[i] * inv * to_f32<W>(weight[i]));
 }
 
+
+// Vectorised form for widths that are a multiple of 4 and fit 8 float4 per thread: the row stays
+// in registers between the sum of squares and the scaling, so memory is touched once.
+template <typename T> struct Vec4 {};
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u; u.x = *reinterpret_cast<unsigned*>(&a); u.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+template <typename T, typename W, int NT, int MAXC>
+__global__ void __launch_bounds__(NT)
+add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart,
+                       int S, long long part_stride, const int* __restrict__ rows,
+                       const W* __restrict__ weight, T* __restrict__ out, int d, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * d;
+    float4 v[MAXC];
+    float ss = 0.f;
+    const int nchunk = d >> 2;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+        const int i = (threadIdx.x + c * NT) * 4;
+        if (threadIdx.x + c * NT < nchunk) {
+            float4 a = *reinterpret_cast<const float4*>(resid + src + i);
+            if (delta) { const float4 b = Vec4<T>::load(delta + src + i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+            if (dpart) {
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp = 0; sp < S; ++sp) {
+                    const float4 b = *reinterpret_cast<const float4*>(dpart + sp * part_stride + src + i);
+                    t.x += b.x; t.y += b.y; t.z += b.z; t.w += b.w;
+                }
+                a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+            }
+            if (!rows && (delta || dpart)) *reinterpret_cast<float4*>(resid + src + i) = a;
+            v[c] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+        const int i = (threadIdx.x + c * NT) * 4;
+        if (threadIdx.x + c * NT < nchunk) {
+            const float4 w = Vec4<W>::load(weight + i);
+            Vec4<T>::store(out + (size_t)r * d + i, make_float4(v[c].x * inv * w.x, v[c].y * inv * w.y, v[c].z * inv * w.z, v[c].w * inv * w.w));
+        }
+    }
+}
+
 template <typename T>
-static int launch_rmsnorm(float* resid, const void* delta, const int* rows, const void* weight, int w_dtype, void* out,
+static int launch_rmsnorm(float* resid, const void* delta, const float* dpart, int S, long long part_stride,
+                          const int* rows, const void* weight, int w_dtype, void* out,
                           int R, int d, float eps, cudaStream_t s) {
+    const bool aligned = !(((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)dpart | (uintptr_t)weight | (uintptr_t)out) & 15)
+                         && (part_stride % 4 == 0);
+    if (d % 4 == 0 && d <= 8192 && aligned) {
+        if (w_dtype == kF32) {
+            if (d <= 2048) add_rmsnorm_vec_kernel<T, float, 128, 4><<<R, 128, 0, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
+            else add_rmsnorm_vec_kernel<T, float, 256, 8><<<R, 256, 0, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
+        } else if (w_dtype == kBF16) {
+            if (d <= 2048) add_rmsnorm_vec_kernel<T, __nv_bfloat16, 128, 4><<<R, 128, 0, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
+            else add_rmsnorm_vec_kernel<T, __nv_bfloat16, 256, 8><<<R, 256, 0, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
+        } else TTIE_FAIL("rmsnorm: unknown weight dtype %d", w_dtype);
+        TTIE_CHECK_LAUNCH("rmsnorm");
+        return 0;
+    }
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024) TTIE_FAIL("rmsnorm: width %d needs %zu bytes of shared memory (limit 204800)", d, smem);
     if (w_dtype == kF32) {
         auto k = add_rmsnorm_kernel<T, float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<R, threads, smem, s>>>(resid, (const T*)delta, rows, (const float*)weight, (T*)out, d, eps);
+        k<<<R, threads, smem, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
     } else if (w_dtype == kBF16) {
         auto k = add_rmsnorm_kernel<T, __nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<R, threads, smem, s>>>(resid, (const T*)delta, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
+        k<<<R, threads, smem, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
     } else TTIE_FAIL("rmsnorm: unknown weight dtype %d", w_dtype);
     TTIE_CHECK_LAUNCH("rmsnorm");
     return 0;
 }
 
 // rows == nullptr: all R rows in place (resid updated).  rows != nullptr: gather R rows.
-extern "C" int ttie_add_rmsnorm(float* resid, const void* delta, const int* rows, const void* weight, int w_dtype,
+// delta: [rows of resid][d] in the compute dtype, or nullptr.  dpart: float32 partial sums
+// [S][rows of resid][d] (part_stride = elements between two partial sums), or nullptr.
+extern "C" int ttie_add_rmsnorm(float* resid, const void* delta, const float* dpart, int S, long long part_stride,
+                                const int* rows, const void* weight, int w_dtype,
                                 void* out, int R, int d, float eps, int dtype, void* stream) {
     if (R <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == kF32) return launch_rmsnorm<float>(resid, delta, rows, weight, w_dtype, out, R, d, eps, s);
-    if (dtype == kBF16) return launch_rmsnorm<__nv_bfloat16>(resid, delta, rows, weight, w_dtype, out, R, d, eps, s);
+    if (dtype == kF32) return launch_rmsnorm<float>(resid, delta, dpart, S, part_stride, rows, weight, w_dtype, out, R, d, eps, s);
+    if (dtype == kBF16) return launch_rmsnorm<__nv_bfloat16>(resid, delta, dpart, S, part_stride, rows, weight, w_dtype, out, R, d, eps, s);
     TTIE_FAIL("rmsnorm: unknown dtype %d", dtype);
 }
 
@@ -195,5 +283,185 @@ extern "C" int ttie_rope_store(void* qkv, int row_stride, int T, int Hq, int Hkv
             page_size, num_pages, write_kv);
     else TTIE_FAIL("rope_store: unknown dtype %d", dtype);
     TTIE_CHECK_LAUNCH("rope_store");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------ rope + store from partial sums
+// The same as rope_store for a q/k/v row that arrives as float32 partial sums [S][T][width] of a
+// K-split product: the row is summed (s = 0..S-1) into shared memory, rotated there in 32-bit, q is
+// written to q_out [T][Hq*D] and k, v into the pages - the sum is rounded to the storage type once.
+template <typename T>
+__global__ void rope_store_partial_kernel(const float* __restrict__ part, int S, long long part_stride, int width,
+                                          int Hq, int Hkv, int D, const int* __restrict__ positions,
+                                          const int* __restrict__ token_seq, const float* __restrict__ inv_freq, int style,
+                                          T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                          const int* __restrict__ block_table, int table_width, int page_size,
+                                          int num_pages, int write_kv) {
+    extern __shared__ float sm[];
+    float* rowbuf = sm;                                             // [width]
+    float* cs = sm + width;                                         // cos[D/2], sin[D/2]
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = D >> 1;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float a = 0.f;
+        for (int sp = 0; sp < S; ++sp) a += part[sp * part_stride + (long long)t * width + i];
+        rowbuf[i] = a;
+    }
+    if (inv_freq)
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            float sn, c;
+            sincosf((float)pos * inv_freq[j], &sn, &c);
+            cs[j] = c; cs[half + j] = sn;
+        }
+    __syncthreads();
+    if (inv_freq) {
+        const int n_rot = (Hq + Hkv) * half;
+        for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+            const int h = i / half, j = i - h * half;
+            float* x = rowbuf + h * D;
+            const int a = style == 0 ? 2 * j : j, b = style == 0 ? 2 * j + 1 : j + half;
+            const float xa = x[a], xb = x[b], c = cs[j], sn = cs[half + j];
+            x[a] = xa * c - xb * sn;
+            x[b] = xa * sn + xb * c;
+        }
+        __syncthreads();
+    }
+    T* qo = q_out + (size_t)t * Hq * D;
+    for (int i = threadIdx.x; i < Hq * D; i += blockDim.x) qo[i] = from_f32<T>(rowbuf[i]);
+    if (write_kv && Hkv > 0) {
+        const int seq = token_seq[t];
+        int page = block_table[(size_t)seq * table_width + pos / page_size];
+        if (page < 0 || page >= num_pages) page = 0;
+        const int off = pos % page_size;
+        const float* k = rowbuf + Hq * D;
+        const float* v = rowbuf + (Hq + Hkv) * D;
+        for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
+            const int h = i / D, dd = i - h * D;
+            const size_t dst = (((size_t)page * Hkv + h) * page_size + off) * D + dd;
+            k_pages[dst] = from_f32<T>(k[i]);
+            v_pages[dst] = from_f32<T>(v[i]);
+        }
+    }
+}
+
+extern "C" int ttie_rope_store_partial(const float* part, int S, long long part_stride, int T, int Hq, int Hkv, int D,
+                                       const int* positions, const int* token_seq, const float* inv_freq, int style,
+                                       void* q_out, void* k_pages, void* v_pages, const int* block_table, int table_width,
+                                       int page_size, int num_pages, int write_kv, int dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (D % 2) TTIE_FAIL("rope_store: head size %d must be even", D);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int width = (Hq + 2 * Hkv) * D;
+    const size_t smem = ((size_t)width + D) * sizeof(float);
+    if (smem > 200 * 1024) TTIE_FAIL("rope_store_partial: row of %d values needs %zu bytes of shared memory", width, smem);
+    const int threads = 256;
+    if (dtype == kF32) {
+        auto k = rope_store_partial_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<T, threads, smem, s>>>(part, S, part_stride, width, Hq, Hkv, D, positions, token_seq, inv_freq, style, (float*)q_out,
+                                   (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, num_pages, write_kv);
+    } else if (dtype == kBF16) {
+        auto k = rope_store_partial_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<T, threads, smem, s>>>(part, S, part_stride, width, Hq, Hkv, D, positions, token_seq, inv_freq, style,
+                                   (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
+                                   table_width, page_size, num_pages, write_kv);
+    } else TTIE_FAIL("rope_store_partial: unknown dtype %d", dtype);
+    TTIE_CHECK_LAUNCH("rope_store_partial");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------ rope + store, vectorised
+// Per step (not per layer): cos and sin of pos * inv_freq[j] for every token, [T][D/2] float2.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, float2* __restrict__ cs,
+                                  int half, int total) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int t = i / half, j = i - t * half;
+    float sn, c;
+    sincosf((float)positions[t] * inv_freq[j], &sn, &c);
+    cs[i] = make_float2(c, sn);
+}
+
+extern "C" int ttie_rope_table(const int* positions, const float* inv_freq, void* cs, int T, int half, void* stream) {
+    if (T <= 0) return 0;
+    const int total = T * half;
+    rope_table_kernel<<<ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, (float2*)cs, half, total);
+    TTIE_CHECK_LAUNCH("rope_table");
+    return 0;
+}
+
+// Interleaved pairs, four values per thread, no shared memory: the input row is either the
+// packed q/k/v row in the compute dtype (then q and k are also written back in place) or float32
+// partial sums [S][T][width].  cos/sin come from the step's table.
+template <typename T, bool PARTIAL>
+__global__ void __launch_bounds__(256)
+rope_store_vec_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ part, int S, long long part_stride,
+                      int Hq, int Hkv, int D, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                      const float2* __restrict__ cs, T* __restrict__ q_out, long long q_stride,
+                      T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
+                      int page_size, int num_pages, int write_kv) {
+    const int t = blockIdx.x;
+    const int width = (Hq + 2 * Hkv) * D, half = D >> 1;
+    const int pos = positions[t];
+    long long page_base = 0;
+    if (write_kv && Hkv > 0) {
+        int page = block_table[(size_t)token_seq[t] * table_width + pos / page_size];
+        if (page < 0 || page >= num_pages) page = 0;
+        page_base = (long long)page * Hkv * page_size + pos % page_size;      // + h * page_size, all times D
+    }
+    for (int c = threadIdx.x; c < (width >> 2); c += blockDim.x) {
+        const int col = c << 2;
+        const int h = col / D, i = col - h * D;
+        float4 v;
+        if (PARTIAL) {
+            v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sp = 0; sp < S; ++sp) {
+                const float4 b = *reinterpret_cast<const float4*>(part + sp * part_stride + (long long)t * width + col);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
+        } else {
+            v = Vec4<T>::load(qkv + (long long)t * row_stride + col);
+        }
+        if (h < Hq + Hkv && cs) {
+            const float4 t2 = *reinterpret_cast<const float4*>(cs + (size_t)t * half + (i >> 1));   // cos0 sin0 cos1 sin1
+            v = make_float4(v.x * t2.x - v.y * t2.y, v.x * t2.y + v.y * t2.x, v.z * t2.z - v.w * t2.w, v.z * t2.w + v.w * t2.z);
+        }
+        if (h < Hq) {
+            Vec4<T>::store(q_out + (long long)t * q_stride + col, v);
+        } else {
+            if (!PARTIAL && h < Hq + Hkv) Vec4<T>::store(qkv + (long long)t * row_stride + col, v);
+            if (write_kv) {
+                const int hk = h < Hq + Hkv ? h - Hq : h - Hq - Hkv;
+                T* dst = (h < Hq + Hkv ? k_pages : v_pages) + (page_base + (long long)hk * page_size) * D + i;
+                Vec4<T>::store(dst, v);
+            }
+        }
+    }
+}
+
+// qkv != nullptr: packed rows in the compute dtype, rotated in place (q_out may be qkv itself).
+// part != nullptr: float32 partial sums; q goes to q_out [T][q_stride].  cs: table from ttie_rope_table or
+// nullptr for no rotation.  Head size must be a multiple of 4.
+extern "C" int ttie_rope_store_vec(void* qkv, long long row_stride, const float* part, int S, long long part_stride, int T,
+                                   int Hq, int Hkv, int D, const int* positions, const int* token_seq, const void* cs,
+                                   void* q_out, long long q_stride, void* k_pages, void* v_pages, const int* block_table,
+                                   int table_width, int page_size, int num_pages, int write_kv, int dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (D % 4) TTIE_FAIL("rope_store_vec: head size %d must be a multiple of 4", D);
+    if ((qkv == nullptr) == (part == nullptr)) TTIE_FAIL("rope_store_vec: give exactly one of qkv and part");
+    if (((uintptr_t)qkv | (uintptr_t)part | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)cs) & 15)
+        TTIE_FAIL("rope_store_vec: pointers must be 16-byte aligned");
+    if (row_stride % 4 || q_stride % 4 || part_stride % 4) TTIE_FAIL("rope_store_vec: strides must be multiples of 4");
+    cudaStream_t s = (cudaStream_t)stream;
+#define TTIE_ROPE_VEC(TT, P) rope_store_vec_kernel<TT, P><<<T, 256, 0, s>>>((TT*)qkv, row_stride, part, S, part_stride, Hq, Hkv, D, \
+        positions, token_seq, (const float2*)cs, (TT*)q_out, q_stride, (TT*)k_pages, (TT*)v_pages, block_table, table_width, \
+        page_size, num_pages, write_kv)
+    if (dtype == kF32) { if (part) TTIE_ROPE_VEC(float, true); else TTIE_ROPE_VEC(float, false); }
+    else if (dtype == kBF16) { if (part) TTIE_ROPE_VEC(__nv_bfloat16, true); else TTIE_ROPE_VEC(__nv_bfloat16, false); }
+    else TTIE_FAIL("rope_store_vec: unknown dtype %d", dtype);
+#undef TTIE_ROPE_VEC
+    TTIE_CHECK_LAUNCH("rope_store_vec");
     return 0;
 }

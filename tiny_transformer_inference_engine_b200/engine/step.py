@@ -75,6 +75,7 @@ class Stepper:
             views = self.manager.views(ctx.block_tables)
             self.model.forward(ctx, views)                       # warm-up outside the capture
             torch.cuda.synchronize(self.device)
+            ctx.step_cache.clear()                              # what parts computed once per step is computed again inside the graph
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx, views)

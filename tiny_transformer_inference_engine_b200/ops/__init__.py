@@ -26,7 +26,15 @@ _c_int, _c_ll, _c_float, _c_void = ctypes.c_int, ctypes.c_longlong, ctypes.c_flo
 
 _SIGNATURES = {
     "ttie_embed": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
-    "ttie_add_rmsnorm": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ttie_add_rmsnorm": [_c_void, _c_void, _c_void, _c_int, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int,
+                         _c_float, _c_int, _c_void],
+    "ttie_rope_store_partial": [_c_void, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int,
+                                _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ttie_rope_table": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
+    "ttie_rope_store_vec": [_c_void, _c_ll, _c_void, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void,
+                            _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ttie_skinny_gemm": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_void],
     "ttie_swiglu": [_c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
     "ttie_rope_store": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void,
                         _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
@@ -71,6 +79,7 @@ class CudaOps:
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
         self.attn_target_ctas = 2 * NUM_SMS
+        self.skinny_max_rows = 16               # rows up to which the weight-streaming product replaces the library's
         for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows"):
             getattr(self.lib, name).restype = _c_int
 
@@ -97,21 +106,58 @@ class CudaOps:
                                         self._dt(table), self._stream(out)), "embed")
         self.launches += 1
 
+    @staticmethod
+    def _delta_args(delta):
+        """(delta pointer, partial pointer, S, stride) for a delta that is None, [T, d] in the compute
+        dtype, or float32 partial sums [S, T, d]."""
+        if delta is None:
+            return None, None, 0, 0
+        if delta.dim() == 3:
+            return None, delta.data_ptr(), delta.shape[0], delta.stride(0)
+        return delta.data_ptr(), None, 0, 0
+
     def add_rmsnorm(self, resid, delta, weight, eps, out):
         R, d = resid.shape
-        self._check(self.lib.ttie_add_rmsnorm(_ptr(resid), _ptr(delta), None, _ptr(weight), self._dt(weight),
+        dp, pp, S, stride = self._delta_args(delta)
+        self._check(self.lib.ttie_add_rmsnorm(_ptr(resid), dp, pp, S, stride, None, _ptr(weight), self._dt(weight),
                                               _ptr(out), R, d, float(eps), self._dt(out), self._stream(out)), "add_rmsnorm")
         self.launches += 1
 
     def rmsnorm_rows(self, resid, delta, rows, num_rows, weight, eps, out):
         d = resid.shape[1]
-        self._check(self.lib.ttie_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(rows), _ptr(weight), self._dt(weight),
+        dp, pp, S, stride = self._delta_args(delta)
+        self._check(self.lib.ttie_add_rmsnorm(_ptr(resid), dp, pp, S, stride, _ptr(rows), _ptr(weight), self._dt(weight),
                                               _ptr(out), num_rows, d, float(eps), self._dt(out), self._stream(out)),
                     "rmsnorm_rows")
         self.launches += 1
 
-    def linear(self, x, w, bias, out_dtype=None):
-        """y = x @ w.T (+ bias); x [M, K], w [N, K] -> [M, N]."""
+    # ---- matrix products
+    def _skinny_ok(self, x, w):
+        return (x.dtype == torch.bfloat16 and x.shape[0] <= self.skinny_max_rows and x.shape[1] % 8 == 0
+                and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+    def _kslice(self, N, K, may_split):
+        """K range per CTA of the weight-streaming kernel.  K is split over CTAs (partial sums) when the
+        16-row tiles alone are too few to balance the SMs."""
+        tiles = math.ceil(N / 16)
+        full = math.ceil(K / 128) * 128
+        if not may_split or tiles >= 4 * NUM_SMS:
+            return full
+        best, best_eff = full, 0.0
+        for S in (1, 2, 3, 4, 6, 8):
+            ks = math.ceil(math.ceil(K / S) / 128) * 128
+            if ks < 256:
+                break
+            ctas = tiles * math.ceil(K / ks)
+            eff = (ctas / NUM_SMS) / math.ceil(ctas / NUM_SMS)
+            if eff > best_eff + 0.02:
+                best, best_eff = ks, eff
+        return best
+
+    def linear(self, x, w, bias, out_dtype=None, partial_ok=False):
+        """y = x @ w.T (+ bias); x [M, K], w [N, K] -> [M, N].  With ``partial_ok`` the result may
+        instead be float32 partial sums [S, M, N] of a K-split product, which ``add_rmsnorm``,
+        ``rmsnorm_rows`` and ``rope_store`` accept and add up."""
         M, K = x.shape
         N = w.shape[0]
         if x.dtype == torch.float32:
@@ -120,7 +166,20 @@ class CudaOps:
                                                w.stride(0), N, self._stream(x)), "gemm_f32")
             self.launches += 1
             return out
-        # bfloat16: the library product, 32-bit accumulation inside
+        if self._skinny_ok(x, w):
+            kslice = self._kslice(N, K, partial_ok and bias is None and out_dtype is None)
+            S = math.ceil(K / kslice)
+            if S > 1:
+                out, epi = torch.empty((S, M, N), dtype=torch.float32, device=x.device), 1
+            elif out_dtype == torch.float32:
+                out, epi = torch.empty((M, N), dtype=torch.float32, device=x.device), 3
+            else:
+                out, epi = torch.empty((M, N), dtype=torch.bfloat16, device=x.device), 0
+            self._check(self.lib.ttie_skinny_gemm(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), N,
+                                                  M, N, K, kslice, epi, 0, self._stream(x)), "skinny_gemm")
+            self.launches += 1
+            return out
+        # bfloat16, many rows: the library product, 32-bit accumulation inside
         if out_dtype == torch.float32:
             out = torch.mm(x, w.t(), out_dtype=torch.float32)
             if bias is not None:
@@ -130,19 +189,62 @@ class CudaOps:
             return torch.addmm(bias, x, w.t())
         return torch.mm(x, w.t())
 
+    def linear_swiglu(self, x, w_gu, b_gu, hidden):
+        """silu(x @ Wg.T) * (x @ Wu.T) with w_gu = [Wg; Wu] ([2*hidden, K]) -> [M, hidden]."""
+        M, K = x.shape
+        act = torch.empty((M, hidden), dtype=x.dtype, device=x.device)
+        if self._skinny_ok(x, w_gu):
+            self._check(self.lib.ttie_skinny_gemm(_ptr(x), x.stride(0), _ptr(w_gu), w_gu.stride(0), _ptr(b_gu), _ptr(act),
+                                                  hidden, M, hidden, K, math.ceil(K / 128) * 128, 2, hidden,
+                                                  self._stream(x)), "skinny_gemm_swiglu")
+            self.launches += 1
+            return act
+        self.swiglu(self.linear(x, w_gu, b_gu), act)
+        return act
+
     def swiglu(self, gate_up, out):
         T, F = out.shape
         self._check(self.lib.ttie_swiglu(_ptr(gate_up), _ptr(out), T, F, self._dt(out), self._stream(out)), "swiglu")
         self.launches += 1
 
+    def rope_table(self, positions, inv_freq):
+        """cos and sin of pos * inv_freq for every token of the step: float32 [T, D/2, 2]."""
+        T, half = positions.shape[0], inv_freq.shape[0]
+        cs = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
+        self._check(self.lib.ttie_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(cs), T, half, self._stream(cs)), "rope_table")
+        self.launches += 1
+        return cs
+
     def rope_store(self, qkv, num_heads, num_kv_heads, head_dim, positions, token_seq, inv_freq, style,
-                   k_pages, v_pages, block_table, page_size, write_kv):
-        T = qkv.shape[0]
-        self._check(self.lib.ttie_rope_store(_ptr(qkv), qkv.stride(0), T, num_heads, num_kv_heads, head_dim,
-                                             _ptr(positions), _ptr(token_seq), _ptr(inv_freq), int(style),
-                                             _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
-                                             page_size, k_pages.shape[0], 1 if write_kv else 0, self._dt(qkv),
-                                             self._stream(qkv)), "rope_store")
+                   k_pages, v_pages, block_table, page_size, write_kv, q_out=None, cs_table=None):
+        """Rotates q and k and stores k, v into the pages.  qkv [T, width] is rotated in place; qkv given
+        as float32 partial sums [S, T, width] is summed, rotated, and q written to ``q_out`` [T, Hq*D].
+        ``cs_table`` (from ``rope_table``) replaces the per-layer sine/cosine evaluation."""
+        partial = qkv.dim() == 3
+        T = qkv.shape[-2]
+        stream = self._stream(qkv)
+        vec_ok = head_dim % 4 == 0 and (inv_freq is None or (style == 0 and cs_table is not None)) and \
+            (partial or (qkv.stride(0) % 4 == 0 and qkv.stride(1) == 1))
+        if vec_ok:
+            dst = q_out if partial else qkv
+            self._check(self.lib.ttie_rope_store_vec(
+                None if partial else _ptr(qkv), 0 if partial else qkv.stride(0), _ptr(qkv) if partial else None,
+                qkv.shape[0] if partial else 0, qkv.stride(0) if partial else 0, T, num_heads, num_kv_heads, head_dim,
+                _ptr(positions), _ptr(token_seq), None if inv_freq is None else _ptr(cs_table), _ptr(dst), dst.stride(0),
+                _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size, k_pages.shape[0],
+                1 if write_kv else 0, self._dt(dst), stream), "rope_store_vec")
+        elif partial:
+            self._check(self.lib.ttie_rope_store_partial(
+                _ptr(qkv), qkv.shape[0], qkv.stride(0), T, num_heads, num_kv_heads, head_dim, _ptr(positions), _ptr(token_seq),
+                _ptr(inv_freq), int(style), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                block_table.shape[1], page_size, k_pages.shape[0], 1 if write_kv else 0, self._dt(q_out),
+                stream), "rope_store_partial")
+        else:
+            self._check(self.lib.ttie_rope_store(_ptr(qkv), qkv.stride(0), T, num_heads, num_kv_heads, head_dim,
+                                                 _ptr(positions), _ptr(token_seq), _ptr(inv_freq), int(style),
+                                                 _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                                                 page_size, k_pages.shape[0], 1 if write_kv else 0, self._dt(qkv),
+                                                 stream), "rope_store")
         self.launches += 1
 
     def attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len):

@@ -80,20 +80,28 @@ class PagedAttention(Mixer):
         Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         write = cache.writable and not self.shares_kv
         kv_heads_in_buf = 0 if self.shares_kv else Hkv
-        qkv = ops.linear(x, self.w_in, self.b_in)                  # [T, (Hq + 2*Hkv) * D]
+        qkv = ops.linear(x, self.w_in, self.b_in, partial_ok=True)   # [T, (Hq + 2*Hkv) * D], or partial sums of it
+        T = qkv.shape[-2]
         table = self.position.rotary_table()
         if table is None:
-            T = qkv.shape[0]
+            if qkv.dim() == 3:
+                qkv = qkv.sum(0).to(x.dtype)
             q = qkv[:, :Hq * D].view(T, Hq, D)
             k = None if self.shares_kv else qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
             self.position.apply(q, k, ctx.positions)
             inv_freq, style = None, 0
+            cs_table = None
         else:
             inv_freq, style = table
+            cs_table = self.position.step_table(ctx) if inv_freq is not None else None
+        q = qkv
+        if qkv.dim() == 3:
+            q = torch.empty((T, Hq * D), dtype=x.dtype, device=x.device)
         ops.rope_store(qkv, Hq, kv_heads_in_buf, D, ctx.positions, ctx.token_seq, inv_freq, style,
-                       cache.k_pages, cache.v_pages, cache.block_table, cache.page_size, write)
-        out = torch.empty((qkv.shape[0], Hq * D), dtype=qkv.dtype, device=qkv.device)
-        ops.paged_attention(qkv, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
+                       cache.k_pages, cache.v_pages, cache.block_table, cache.page_size, write,
+                       q_out=q if qkv.dim() == 3 else None, cs_table=cs_table)
+        out = torch.empty((T, Hq * D), dtype=x.dtype, device=x.device)
+        ops.paged_attention(q, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
                             ctx.query_start_loc, ctx.seq_lens, ctx.num_seqs, ctx.max_q_len, ctx.max_kv_len,
                             self.scale, self.window or 0, out)
-        return ops.linear(out, self.w_out, self.b_out)
+        return ops.linear(out, self.w_out, self.b_out, partial_ok=True)

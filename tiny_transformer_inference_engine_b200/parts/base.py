@@ -132,6 +132,7 @@ class StepContext:
     num_logit_rows: int
     block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)   # cache group -> [N, max_pages]
     host: Dict[str, Any] = field(default_factory=dict)                    # the same numbers as Python lists
+    step_cache: Dict[Any, Any] = field(default_factory=dict)              # device values parts compute once per step
 
 
 class ResidualStream:
@@ -191,6 +192,11 @@ class PositionEncoding(Part):
     def rotary_table(self):
         """(inv_freq float32 [rotary_dim/2], style) if the encoding is a rotation of pairs
         by ``pos * inv_freq`` that the fused rotate-and-store kernel can do, else None."""
+        return None
+
+    def step_table(self, ctx):
+        """Optional: sines and cosines of the step's positions (float32 [T, D/2, 2]), computed once
+        per step, for encodings whose rotary_table() is not None."""
         return None
 
     def apply(self, q: torch.Tensor, k: Optional[torch.Tensor], positions: torch.Tensor) -> None:

@@ -38,7 +38,5 @@ class SwiGLU(FeedForward):
             self.b_down = params["down_proj.bias"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gu = self.ops.linear(x, self.w_gu, self.b_gu)              # [T, 2F]
-        act = torch.empty((x.shape[0], self.hidden), dtype=x.dtype, device=x.device)
-        self.ops.swiglu(gu, act)
-        return self.ops.linear(act, self.w_down, self.b_down)
+        act = self.ops.linear_swiglu(x, self.w_gu, self.b_gu, self.hidden)        # [T, F]
+        return self.ops.linear(act, self.w_down, self.b_down, partial_ok=True)

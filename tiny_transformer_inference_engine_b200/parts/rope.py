@@ -42,6 +42,17 @@ class RotaryEncoding(PositionEncoding):
     def rotary_table(self):
         return self._inv_freq, ROTARY_STYLES[self.style]
 
+    def step_table(self, ctx):
+        """cos/sin of every token of the step, computed once per step and shared by all layers whose
+        encoding has the same dimension and base (kept in the step's context)."""
+        if not hasattr(self.ops, "rope_table"):
+            return None
+        tables = ctx.step_cache
+        key = ("rope_table", self.dim, self.base)
+        if key not in tables:
+            tables[key] = self.ops.rope_table(ctx.positions, self._inv_freq)
+        return tables[key]
+
     def apply(self, q, k, positions):
         raise NotImplementedError("rotary encoding runs inside the fused rotate-and-store kernel")
 
@@ -55,6 +66,9 @@ class NoPosition(PositionEncoding):
 
     def rotary_table(self):
         return None, 0
+
+    def step_table(self, ctx):
+        return None
 
     def apply(self, q, k, positions):
         return None
