@@ -350,7 +350,7 @@ def test_sampling_frequencies(ops):
 
 # ------------------------------------------------------------------------------------------ weight-streaming product
 @pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 4352, 4096), (3, 515, 200), (16, 1000, 176), (9, 4096, 11008),
-                                   (5, 72, 8), (16, 33, 4544)])
+                                   (5, 72, 8), (16, 33, 4544), (33, 200, 512), (64, 96, 4096), (2, 32000, 4096)])
 def test_skinny_gemm_all_epilogues(ops, M, N, K):
     g = torch.Generator().manual_seed(M * 1000 + N)
     x = torch.randn(M, K, generator=g).bfloat16()
@@ -358,6 +358,7 @@ def test_skinny_gemm_all_epilogues(ops, M, N, K):
     b = torch.randn(N, generator=g).bfloat16()
     exp = x.double() @ w.double().T
     xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    ops.skinny_max_rows = 64
     assert ops._skinny_ok(xd, wd)
     before = ops.launches
     assert rel(ops.linear(xd, wd, None).float().cpu(), exp) < 8e-3
@@ -382,6 +383,7 @@ def test_skinny_gemm_all_epilogues(ops, M, N, K):
         gu = exp + b.double()
         ref = gu[:, :F] * torch.sigmoid(gu[:, :F]) * gu[:, F:]
         assert rel(act.float().cpu(), ref) < 1.2e-2
+    ops.skinny_max_rows = 8
 
 
 def test_partial_sums_feed_norm_and_rope(ops):
@@ -418,3 +420,25 @@ def test_partial_sums_feed_norm_and_rope(ops):
     PLAIN.rope_store(summed, Hq, Hkv, D, positions, token_seq, inv_freq, 0, kp2, vp2, table, page, True)
     assert rel(q_out.float().cpu(), summed[:, :Hq * D]) < 8e-3
     assert rel(kp.float().cpu(), kp2) < 8e-3 and rel(vp.float().cpu(), vp2) < 8e-3
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page", [(32, 1, 128, 64), (71, 1, 64, 16), (6, 2, 48, 32), (3, 1, 32, 8), (4, 4, 16, 5), (128, 1, 64, 64)])
+@pytest.mark.parametrize("seqs", [[(200, 1), (64, 1), (65, 1), (1, 1), (513, 1)], [(130, 2), (128, 1), (129, 1)], [(4096, 1)] * 2])
+def test_decode_form_attention(ops, Hq, Hkv, D, page, seqs):
+    max_kv = max(L for L, _ in seqs)
+    n = -(-max_kv // 128)
+    plan = ("mma_decode", n, 128) if n > 1 else ("mma_decode", 1, 0)
+    if max(q for _, q in seqs) * (Hq // Hkv) > 128:
+        pytest.skip("more query rows than the decode form takes")
+    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=plan)
+    assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
+    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=plan, window=70)
+    assert rel(out, exp) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("kpos", [0, 127, 128, 447, 599])
+def test_decode_form_one_key_decides(ops, kpos):
+    seqs = [(50, 1), (600, 1), (64, 1)]
+    out, exp, dense, qsl = attention_case(ops, "bfloat16", 4, 1, 64, 64, seqs, plan=("mma_decode", 5, 128), spike=(1, 0, kpos))
+    assert (out[qsl[1]].view(4, 64) - dense[1][1][kpos, 0]).abs().max() < 2e-2
+    assert rel(out, exp) < TOL["bfloat16"]

@@ -280,6 +280,212 @@ paged_attn_mma_kernel(const MmaParams p) {
     }
 }
 
+// ------------------------------------------------------------------------------------------ decode form
+// Few query rows per request (one decoded token times the heads of a kv head's group, or a short
+// portion): there is too little work per key tile for the tile loop above to hide latency, so the
+// key range is cut finer.  A CTA takes DEC_KEYS keys of one (request, kv head); each of its four
+// warps loads its own 32 keys (cp.async, no CTA-wide barrier) and computes all query rows against
+// them, 16 rows at a time; the four partial results of a 16-row tile are merged in shared memory
+// and leave as one partial result per CTA (or as the final output if the request has one split).
+constexpr int DEC_WARPS = 4, DEC_WKEYS = 32, DEC_KEYS = DEC_WARPS * DEC_WKEYS, DEC_MAX_ROWS = 128;
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+paged_attn_decode_kernel(const MmaParams p) {
+    constexpr int LDS = D + 8, CH = D / 8, NT = DEC_WARPS * 32;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int G = p.Hq / p.Hkv;
+    const int kvh = blockIdx.x % p.Hkv, seq = blockIdx.x / p.Hkv, split = blockIdx.y;
+    const int q0 = p.qsl[seq], q_len = p.qsl[seq + 1] - q0, kv_len = p.seq_lens[seq];
+    const int nrows = q_len * G;
+    if (nrows <= 0) return;
+    const int nmt = (nrows + 15) / 16;
+    const int rows_pad = nmt * 16;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [rows_pad][LDS]
+    __nv_bfloat16* Ks = Qs + p.row_tiles * LDS;                                     // [4 warps][32][LDS]; row_tiles holds the padded row capacity here
+    __nv_bfloat16* Vs = Ks + DEC_WARPS * DEC_WKEYS * LDS;
+    float* Op = reinterpret_cast<float*>(Vs + DEC_WARPS * DEC_WKEYS * LDS);         // [4 warps][16][D] partial outputs
+    float* MLp = Op + DEC_WARPS * 16 * D;                                           // [4 warps][16][2]
+    const int ctx = kv_len - q_len;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kbase = split * DEC_KEYS;
+    const bool cta_has_keys = kbase < kv_len;
+
+    if (cta_has_keys) {
+        for (int c = tid; c < rows_pad * CH; c += NT) {
+            const int r = c / CH, part = c - r * CH;
+            const bool ok = r < nrows;
+            const int tok = ok ? r / G : 0, g = ok ? r - tok * G : 0;
+            const __nv_bfloat16* src = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)(kvh * G + g) * D + part * 8;
+            cp_async16(Qs + r * LDS + part * 8, ok ? src : p.q, ok);
+        }
+        // this warp's 32 keys
+        const int key = kbase + warp * DEC_WKEYS + lane;
+        long long off = -1;
+        if (key < kv_len) {
+            const int pg = key / p.page_size;
+            const int page = p.block_table[(size_t)seq * p.table_width + pg];
+            off = (((long long)page * p.Hkv + kvh) * p.page_size + (key - pg * p.page_size)) * D;
+        }
+        __nv_bfloat16* kd = Ks + warp * DEC_WKEYS * LDS;
+        __nv_bfloat16* vd = Vs + warp * DEC_WKEYS * LDS;
+#pragma unroll
+        for (int i = 0; i < DEC_WKEYS * CH / 32; ++i) {
+            const int c = lane + 32 * i;
+            const int j = c / CH, part = c - j * CH;
+            const long long o = __shfl_sync(0xffffffffu, off, j);
+            const bool ok = o >= 0;
+            const long long src = ok ? o + part * 8 : 0;
+            cp_async16(kd + j * LDS + part * 8, p.k_pages + src, ok);
+            cp_async16(vd + j * LDS + part * 8, p.v_pages + src, ok);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    const int wkey0 = kbase + warp * DEC_WKEYS;
+    const __nv_bfloat16* kb = Ks + warp * DEC_WKEYS * LDS;
+    const __nv_bfloat16* vb = Vs + warp * DEC_WKEYS * LDS;
+    for (int mt = 0; mt < nmt; ++mt) {
+        float o[D / 8][4];
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+        float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+        int rpos[2], rlo[2]; bool rvalid[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = mt * 16 + (lane >> 2) + 8 * h;
+            rvalid[h] = row < nrows;
+            rpos[h] = rvalid[h] ? ctx + row / G : -1;
+            rlo[h] = p.window > 0 ? max(0, rpos[h] - p.window + 1) : 0;
+        }
+        const int mt_pos_hi = ctx + (min(nrows, mt * 16 + 16) - 1) / G;
+        const int mt_key_lo = p.window > 0 ? max(0, ctx + (mt * 16) / G - p.window + 1) : 0;
+        const bool needed = cta_has_keys && wkey0 < kv_len && wkey0 <= mt_pos_hi && wkey0 + DEC_WKEYS > mt_key_lo;
+        if (needed) {
+            float s[DEC_WKEYS / 8][4];
+#pragma unroll
+            for (int i = 0; i < DEC_WKEYS / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                unsigned qf[4];
+                ldmatrix_x4(qf, Qs + (mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
+#pragma unroll
+                for (int np = 0; np < DEC_WKEYS / 16; ++np) {
+                    unsigned b[4];
+                    ldmatrix_x4(b, kb + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
+                    mma_bf16(s[2 * np], qf, b[0], b[1]);
+                    mma_bf16(s[2 * np + 1], qf, b[2], b[3]);
+                }
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < DEC_WKEYS / 8; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int h = e >> 1;
+                    const int key = wkey0 + i * 8 + 2 * (lane & 3) + (e & 1);
+                    float v = s[i][e] * p.scale_log2;
+                    if (!(rvalid[h] && key <= rpos[h] && key >= rlo[h] && key < kv_len)) v = -INFINITY;
+                    s[i][e] = v;
+                    mx[h] = fmaxf(mx[h], v);
+                }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                mrow[h] = mx[h];
+            }
+            const float msub[2] = {mrow[0] == -INFINITY ? 0.f : mrow[0], mrow[1] == -INFINITY ? 0.f : mrow[1]};
+#pragma unroll
+            for (int i = 0; i < DEC_WKEYS / 8; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = exp2f(s[i][e] - msub[e >> 1]);
+                    s[i][e] = pv;
+                    lrow[e >> 1] += pv;
+                }
+#pragma unroll
+            for (int kk = 0; kk < DEC_WKEYS / 16; ++kk) {
+                unsigned pf[4];
+                pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < D / 16; ++dp) {
+                    unsigned b[4];
+                    ldmatrix_x4_trans(b, vb + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+                    mma_bf16(o[2 * dp], pf, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+                }
+            }
+        }
+        // this warp's partial result of the 16 rows -> shared memory
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float l = lrow[h];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const int r = (lane >> 2) + 8 * h;
+            float* op = Op + (warp * 16 + r) * D + 2 * (lane & 3);
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(op + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+            if ((lane & 3) == 0) { MLp[(warp * 16 + r) * 2] = mrow[h]; MLp[(warp * 16 + r) * 2 + 1] = l; }
+        }
+        __syncthreads();
+        // merge the four warps' partial results (maxima are in log2 units)
+        for (int e = tid; e < 16 * D; e += NT) {
+            const int r = e / D, d = e - r * D;
+            const int row = mt * 16 + r;
+            if (row >= nrows) continue;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) if (MLp[(w * 16 + r) * 2 + 1] > 0.f) M = fmaxf(M, MLp[(w * 16 + r) * 2]);
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) {
+                const float lw = MLp[(w * 16 + r) * 2 + 1];
+                if (lw > 0.f) {
+                    const float f = exp2f(MLp[(w * 16 + r) * 2] - M);
+                    acc += f * Op[(w * 16 + r) * D + d];
+                    L += f * lw;
+                }
+            }
+            const int tok = row / G, g = row - tok * G;
+            const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
+            if (p.num_splits == 1) {
+                p.out[grow * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            } else {
+                p.ws_o[(grow * p.num_splits + split) * D + d] = acc;
+                if (d == 0) {
+                    float* ml = p.ws_ml + (grow * p.num_splits + split) * 2;
+                    ml[0] = M * 0.6931471805599453f;                // natural-log units for the merge kernel
+                    ml[1] = L;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int D>
+int launch_decode(const MmaParams& p, cudaStream_t s) {
+    constexpr int LDS = D + 8;
+    const size_t smem = ((size_t)p.row_tiles * LDS + 2 * (size_t)DEC_KEYS * LDS) * sizeof(__nv_bfloat16)
+                        + (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
+    auto k = paged_attn_decode_kernel<D>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) TTIE_FAIL("paged_attention_decode: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    }
+    dim3 grid(p.num_seqs * p.Hkv, p.num_splits);
+    k<<<grid, DEC_WARPS * 32, smem, s>>>(p);
+    TTIE_CHECK_LAUNCH("paged_attention_decode");
+    return 0;
+}
+
 template <int D, int NWARPS>
 int launch(const MmaParams& p, cudaStream_t s) {
     constexpr int BM = NWARPS * 16, LDS = D + 8;
@@ -311,11 +517,32 @@ extern "C" int ttie_attn_mma_tile_rows(int max_q_len, int Hq, int Hkv) {
 
 extern "C" int ttie_attn_mma_supported(int D) { return D % 16 == 0 && D >= 16 && D <= 128; }
 
+// The decode form takes requests that bring at most this many query rows (tokens x heads per kv head)
+// and splits keys in pieces of ttie_attn_decode_split_len().
+extern "C" int ttie_attn_decode_max_rows() { return DEC_MAX_ROWS; }
+extern "C" int ttie_attn_decode_split_len() { return DEC_KEYS; }
+
+// form 0: tile loop (prompt portions; decode with caller-chosen splits).  form 1: decode form.
+extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                             const int* block_table, int table_width, int page_size, const int* qsl,
+                                             const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                             int max_q_len, float scale, int window, int num_splits, int split_len,
+                                             float* scratch, int form, void* stream);
+
 extern "C" int ttie_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                         const int* block_table, int table_width, int page_size, const int* qsl,
                                         const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
                                         int max_q_len, float scale, int window, int num_splits, int split_len,
                                         float* scratch, void* stream) {
+    return ttie_paged_attention_mma_form(q, q_stride, k_pages, v_pages, block_table, table_width, page_size, qsl, seq_lens, out,
+                                         T, num_seqs, Hq, Hkv, D, max_q_len, scale, window, num_splits, split_len, scratch, 0, stream);
+}
+
+extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                             const int* block_table, int table_width, int page_size, const int* qsl,
+                                             const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                             int max_q_len, float scale, int window, int num_splits, int split_len,
+                                             float* scratch, int form, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (!ttie_attn_mma_supported(D)) TTIE_FAIL("paged_attention_mma: head size %d not supported (multiples of 16 up to 128)", D);
     if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("paged_attention_mma: %d heads are not a multiple of %d kv heads", Hq, Hkv);
@@ -335,6 +562,26 @@ extern "C" int ttie_paged_attention_mma(const void* q, long long q_stride, const
     p.num_splits = num_splits; p.split_len = split_len;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     const int rows = max_q_len * (Hq / Hkv);
+    if (form == 1) {
+        if (rows > DEC_MAX_ROWS) TTIE_FAIL("paged_attention_mma: the decode form takes at most %d query rows per request, got %d", DEC_MAX_ROWS, rows);
+        if (num_splits > 1 && split_len != DEC_KEYS) TTIE_FAIL("paged_attention_mma: the decode form splits keys by %d", DEC_KEYS);
+        p.row_tiles = ceil_div(rows, 16) * 16;                  // padded query-row capacity of the CTA's shared memory
+        int rc;
+        switch (D) {
+            case 16: rc = launch_decode<16>(p, (cudaStream_t)stream); break;
+            case 32: rc = launch_decode<32>(p, (cudaStream_t)stream); break;
+            case 48: rc = launch_decode<48>(p, (cudaStream_t)stream); break;
+            case 64: rc = launch_decode<64>(p, (cudaStream_t)stream); break;
+            case 80: rc = launch_decode<80>(p, (cudaStream_t)stream); break;
+            case 96: rc = launch_decode<96>(p, (cudaStream_t)stream); break;
+            case 112: rc = launch_decode<112>(p, (cudaStream_t)stream); break;
+            case 128: rc = launch_decode<128>(p, (cudaStream_t)stream); break;
+            default: TTIE_FAIL("paged_attention_mma: head size %d", D);
+        }
+        if (rc) return rc;
+        if (num_splits > 1) return attn_merge_bf16(p.ws_o, p.ws_ml, out, T * Hq, num_splits, D, (cudaStream_t)stream);
+        return 0;
+    }
     const int bm = ttie_attn_mma_tile_rows(max_q_len, Hq, Hkv);
     p.row_tiles = ceil_div(rows, bm);
     if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("paged_attention_mma: grid too large");

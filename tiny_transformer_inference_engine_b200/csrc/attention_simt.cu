@@ -188,21 +188,41 @@ paged_attn_simt_kernel(const AttnParams p) {
 }
 
 // out[row] = sum_s exp(m_s - M) O_s / sum_s exp(m_s - M) l_s over the splits of the row.
+// One block per row: the first warp turns the (max, sum) pairs into one weight per split (kept in
+// shared memory), then every thread owns output columns and adds the splits' partial outputs with
+// independent loads.  The order of the additions is fixed.
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, T* __restrict__ out,
                                   int num_splits, int D) {
+    extern __shared__ float wgt[];                                  // [num_splits]
     const size_t row = blockIdx.x;
     const float* ml = ws_ml + row * num_splits * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < num_splits; ++s) if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
-    float denom = 0.f;
-    for (int s = 0; s < num_splits; ++s) if (ml[2 * s + 1] > 0.f) denom += expf(ml[2 * s] - M) * ml[2 * s + 1];
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int s = lane; s < num_splits; s += 32) {
+            const float2 v = *reinterpret_cast<const float2*>(ml + 2 * s);
+            if (v.y > 0.f) M = fmaxf(M, v.x);
+        }
+        M = warp_max(M);
+        float den = 0.f;
+        for (int s = lane; s < num_splits; s += 32) {
+            const float2 v = *reinterpret_cast<const float2*>(ml + 2 * s);
+            const float e = v.y > 0.f ? expf(v.x - M) : 0.f;
+            wgt[s] = e;
+            den += e * v.y;
+        }
+        den = warp_sum(den);
+        const float inv = den > 0.f ? 1.f / den : 0.f;
+        for (int s = lane; s < num_splits; s += 32) wgt[s] *= inv;
+    }
+    __syncthreads();
+    const float* o = ws_o + row * num_splits * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < num_splits; ++s)
-            if (ml[2 * s + 1] > 0.f) acc += expf(ml[2 * s] - M) * ws_o[(row * num_splits + s) * D + d];
-        out[row * D + d] = from_f32<T>(acc * inv);
+#pragma unroll 8
+        for (int s = 0; s < num_splits; ++s) acc = fmaf(wgt[s], o[(size_t)s * D + d], acc);
+        out[row * D + d] = from_f32<T>(acc);
     }
 }
 
@@ -210,7 +230,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
 
 namespace ttie {
 int attn_merge_bf16(const float* ws_o, const float* ws_ml, void* out, int rows, int num_splits, int D, cudaStream_t s) {
-    attn_merge_kernel<__nv_bfloat16><<<rows, D >= 128 ? 128 : 64, 0, s>>>(ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    attn_merge_kernel<__nv_bfloat16><<<rows, D >= 128 ? 128 : 64, num_splits * sizeof(float), s>>>(ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
     TTIE_CHECK_LAUNCH("attention merge");
     return 0;
 }
@@ -226,7 +246,7 @@ int launch(const AttnParams& p, int T_tokens, cudaStream_t s) {
     k<<<grid, WARPS * 32, smem, s>>>(p);
     TTIE_CHECK_LAUNCH("paged_attention");
     if (p.num_splits > 1) {
-        attn_merge_kernel<T><<<T_tokens * p.Hq, p.D >= 128 ? 128 : 64, 0, s>>>(p.ws_o, p.ws_ml, (T*)p.out, p.num_splits, p.D);
+        attn_merge_kernel<T><<<T_tokens * p.Hq, p.D >= 128 ? 128 : 64, p.num_splits * sizeof(float), s>>>(p.ws_o, p.ws_ml, (T*)p.out, p.num_splits, p.D);
         TTIE_CHECK_LAUNCH("attention merge");
     }
     return 0;

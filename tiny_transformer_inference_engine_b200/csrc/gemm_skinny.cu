@@ -69,8 +69,10 @@ skinny_gemm_kernel(const SkinnyParams p) {
     }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    for (int k0 = k_begin; k0 < k_end; k0 += 32 * U) {
-        uint4 wv[U][NSET][2], xv[U][MT];
+    // Two register buffers: the loads of the next 32*U keys are in flight while the current ones
+    // feed the tensor core, so every warp always has weight bytes on their way from HBM.
+    uint4 wA[U][NSET][2], xA[U][MT], wB[U][NSET][2], xB[U][MT];
+    auto load = [&](int k0, uint4 (&wv)[U][NSET][2], uint4 (&xv)[U][MT]) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int kk = k0 + 32 * u + 8 * q;
@@ -86,6 +88,8 @@ skinny_gemm_kernel(const SkinnyParams p) {
                 xv[u][j] = (ok && m < p.M) ? __ldg(reinterpret_cast<const uint4*>(p.x + (long long)m * p.ldx + kk)) : zero;
             }
         }
+    };
+    auto compute = [&](const uint4 (&wv)[U][NSET][2], const uint4 (&xv)[U][MT]) {
 #pragma unroll
         for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -95,6 +99,15 @@ skinny_gemm_kernel(const SkinnyParams p) {
                     mma_bf16(acc[s][j], wv[u][s][0].x, wv[u][s][1].x, wv[u][s][0].y, wv[u][s][1].y, xv[u][j].x, xv[u][j].y);
                     mma_bf16(acc[s][j], wv[u][s][0].z, wv[u][s][1].z, wv[u][s][0].w, wv[u][s][1].w, xv[u][j].z, xv[u][j].w);
                 }
+    };
+    if (k_begin < k_end) load(k_begin, wA, xA);
+    for (int k0 = k_begin; k0 < k_end; k0 += 64 * U) {
+        if (k0 + 32 * U < k_end) load(k0 + 32 * U, wB, xB);
+        compute(wA, xA);
+        if (k0 + 32 * U < k_end) {
+            if (k0 + 64 * U < k_end) load(k0 + 64 * U, wA, xA);
+            compute(wB, xB);
+        }
     }
 
     // sum the four warps' K ranges in a fixed order
@@ -142,10 +155,12 @@ int launch(const SkinnyParams& p, int splits, cudaStream_t s) {
 template <int EPI>
 int dispatch(const SkinnyParams& p, int splits, cudaStream_t s) {
     const int mt = ceil_div(p.M, 8);
-    if (mt <= 1) return launch<1, EPI, 4>(p, splits, s);
-    if (mt <= 2) return launch<2, EPI, 4>(p, splits, s);
-    if (mt <= 4) return launch<4, EPI, 2>(p, splits, s);
-    return launch<8, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
+    // long K ranges per warp stream best with deep unrolling, short ones with more CTAs per SM
+    const bool deep = EPI != 2 && p.kslice / 4 >= 512;
+    if (mt <= 1) return deep ? launch<1, EPI, 4>(p, splits, s) : launch<1, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
+    if (mt <= 2) return launch<2, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
+    if (mt <= 4) return launch<4, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
+    return launch<8, EPI, 1>(p, splits, s);
 }
 }  // namespace
 

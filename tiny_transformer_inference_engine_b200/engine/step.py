@@ -23,8 +23,9 @@ from ..models.model import Model
 
 
 class _DecodeGraph:
-    def __init__(self, bucket, host, dev, graph, logits, ctx):
+    def __init__(self, bucket, host, dev, graph, logits, ctx, launches):
         self.bucket, self.host, self.dev, self.graph, self.logits, self.ctx = bucket, host, dev, graph, logits, ctx
+        self.launches = launches            # kernels of this package inside the graph (counted while capturing)
 
 
 class Stepper:
@@ -77,11 +78,14 @@ class Stepper:
             torch.cuda.synchronize(self.device)
             ctx.step_cache.clear()                              # what parts computed once per step is computed again inside the graph
             graph = torch.cuda.CUDAGraph()
+            before = getattr(self.ops, "launches", 0)
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx, views)
-            g = _DecodeGraph(bucket, host, dev, graph, logits, ctx)
+            g = _DecodeGraph(bucket, host, dev, graph, logits, ctx, getattr(self.ops, "launches", 0) - before)
             self._graphs[bucket] = g
         self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(g.host, g.dev))
         g.graph.replay()
+        if hasattr(self.ops, "launches"):
+            self.ops.launches += g.launches
         self.counters["graph_replays"] += 1
         return g.logits[:n]

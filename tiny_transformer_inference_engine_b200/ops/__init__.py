@@ -45,6 +45,9 @@ _SIGNATURES = {
     "ttie_paged_attention_mma": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
                                  _c_void, _c_void],
+    "ttie_paged_attention_mma_form": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
+                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
+                                      _c_void, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
 }
 
@@ -79,8 +82,8 @@ class CudaOps:
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
         self.attn_target_ctas = 2 * NUM_SMS
-        self.skinny_max_rows = 16               # rows up to which the weight-streaming product replaces the library's
-        for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows"):
+        self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
+        for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows", "ttie_attn_decode_max_rows", "ttie_attn_decode_split_len"):
             getattr(self.lib, name).restype = _c_int
 
     # ------------------------------------------------------------------ helpers
@@ -255,13 +258,14 @@ class CudaOps:
         G = num_heads // num_kv_heads
         rows = max_q_len * G
         if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
-            kernel, tile_rows, unit, min_len = "mma", self.lib.ttie_attn_mma_tile_rows(max_q_len, num_heads, num_kv_heads), 64, 256
+            kernel, tile_rows, unit, min_len = "mma", self.lib.ttie_attn_mma_tile_rows(max_q_len, num_heads, num_kv_heads), 64, 128
         else:
             kernel, tile_rows, unit, min_len = "simt", 32, 32, 128
         base = num_seqs * num_kv_heads * math.ceil(rows / tile_rows)
         if base >= NUM_SMS or max_kv_len <= min_len:
             return kernel, 1, 0
-        want = min(math.ceil(self.attn_target_ctas / base), math.ceil(max_kv_len / min_len))
+        # as many splits as fit one wave of resident CTAs (two per SM), none shorter than min_len keys
+        want = max(1, min(self.attn_target_ctas // base, math.ceil(max_kv_len / min_len)))
         split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
         num_splits = math.ceil(max_kv_len / split_len)
         return (kernel, num_splits, split_len) if num_splits > 1 else (kernel, 1, 0)
@@ -275,12 +279,12 @@ class CudaOps:
         scratch = None
         if num_splits > 1:
             scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
-        if kernel == "mma":
-            self._check(self.lib.ttie_paged_attention_mma(
+        if kernel in ("mma", "mma_decode"):
+            self._check(self.lib.ttie_paged_attention_mma_form(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
                 head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
-                self._stream(qkv)), "paged_attention_mma")
+                1 if kernel == "mma_decode" else 0, self._stream(qkv)), "paged_attention_mma")
         else:
             self._check(self.lib.ttie_paged_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
