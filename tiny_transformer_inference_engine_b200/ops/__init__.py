@@ -48,6 +48,7 @@ _SIGNATURES = {
     "ttie_paged_attention_mma_form": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
                                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
                                       _c_void, _c_int, _c_void],
+    "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
 }
 
@@ -191,6 +192,20 @@ class CudaOps:
         if bias is not None:
             return torch.addmm(bias, x, w.t())
         return torch.mm(x, w.t())
+
+    def linear_tc(self, x, w, bias, out_dtype=None, tile_n=256):
+        """The tcgen05 / TMA / TMEM product: y = x @ w.T (+ bias) for bfloat16 operands."""
+        M, K = x.shape
+        N = w.shape[0]
+        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
+        self._check(self.lib.ttie_gemm_tc(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(0),
+                                          M, N, K, 1 if out.dtype == torch.float32 else 0, tile_n, self._stream(x)), "gemm_tc")
+        self.launches += 1
+        return out
+
+    def tc_error(self) -> int:
+        """Error word of the tensor-core kernels (0 = none); synchronises the device."""
+        return int(self.lib.ttie_tc_error())
 
     def linear_swiglu(self, x, w_gu, b_gu, hidden):
         """silu(x @ Wg.T) * (x @ Wu.T) with w_gu = [Wg; Wu] ([2*hidden, K]) -> [M, hidden]."""
