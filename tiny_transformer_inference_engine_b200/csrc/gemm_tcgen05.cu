@@ -1,7 +1,8 @@
 // bfloat16 matrix product for prompt portions on Blackwell's 5th-generation tensor cores:
 // C[M,N] = A[M,K] * W[N,K]^T (+ bias), float32 accumulation in tensor memory.
 //
-// Structure (one CTA per 128 x BN output tile, warp-specialised, no tracing compiler, no CUTLASS):
+// Structure (persistent: one CTA per SM walks over 128 x BN output tiles; warp-specialised; the
+// accumulator is double-buffered in tensor memory so a tile's epilogue overlaps the next tile's products):
 //   warp 0   one elected thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the
 //            A and W tiles of each 64-wide K block into a ring of shared-memory stages; the warp also
 //            allocates and frees the CTA's tensor-memory columns
@@ -89,77 +90,98 @@ template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int NACC = (2 * BN <= 512) ? 2 : 1;               // accumulator buffers in tensor memory
+    constexpr uint32_t TMEM_COLS = NACC * BN;
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 2 * NACC];
     __shared__ uint32_t tmem_slot;
-    __shared__ int failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN, num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + BK - 1) / BK;
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accbar = smem_u32(&bars[2 * STAGES]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t accfull0 = smem_u32(&bars[2 * STAGES]), accempty0 = smem_u32(&bars[2 * STAGES + NACC]);
 
     if (threadIdx.x == 0) {
-        failed = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(accbar, 1);
+        for (int a = 0; a < NACC; ++a) { mbar_init(accfull0 + 8 * a, 1); mbar_init(accempty0 + 8 * a, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_acc = tmem_slot;
+    const uint32_t tmem_base = tmem_slot;
 
+    // Tiles are dealt round-robin to the resident CTAs; M tiles are the fast index, so CTAs that run
+    // together share a W tile (read from HBM once) and the activations stay in L2.
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
-                if (!mbar_wait(empty0 + 8 * s, parity, 1)) { failed = 1; break; }
-                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                const uint32_t a_dst = smem_u32(smem + (size_t)s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                tma_load_2d(a_dst, &tmA, full0 + 8 * s, kb * BK, m0);
-                tma_load_2d(b_dst, &tmB, full0 + 8 * s, kb * BK, n0);
+            int kc = 0;                                          // K blocks loaded so far, over all tiles
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                bool ok = true;
+                for (int kb = 0; kb < num_kb; ++kb, ++kc) {
+                    const int s = kc % STAGES;
+                    const uint32_t parity = ((kc / STAGES) & 1) ^ 1;
+                    if (!mbar_wait(empty0 + 8 * s, parity, 1)) { ok = false; break; }
+                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    const uint32_t a_dst = smem_u32(smem + (size_t)s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+                    tma_load_2d(a_dst, &tmA, full0 + 8 * s, kb * BK, m0);
+                    tma_load_2d(b_dst, &tmB, full0 + 8 * s, kb * BK, n0);
+                }
+                if (!ok) break;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            int kc = 0, lt = 0;                                  // K blocks consumed; tiles done by this CTA
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t parity = (kb / STAGES) & 1;
-                if (!mbar_wait(full0 + 8 * s, parity, 2)) { failed = 1; ok = false; break; }
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+                const int ab = lt % NACC;
+                const uint32_t use = lt / NACC;
+                if (!mbar_wait(accempty0 + 8 * ab, (use & 1) ^ 1, 4)) { ok = false; break; }   // the epilogue has drained this buffer
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
-                const uint64_t da = umma_desc(a_addr), db = umma_desc(b_addr);
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(ab * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++kc) {
+                    const int s = kc % STAGES;
+                    if (!mbar_wait(full0 + 8 * s, (kc / STAGES) & 1, 2)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                    const uint64_t da = umma_desc(a_addr), db = umma_desc(b_addr);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    umma_bf16(tmem_acc, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, (kb | k) != 0);
-                umma_commit(empty0 + 8 * s);                   // the stage may be refilled once these products have read it
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(tmem_acc, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, (kb | k) != 0);
+                    umma_commit(empty0 + 8 * s);               // the stage may be refilled once these products have read it
+                }
+                if (ok) umma_commit(accfull0 + 8 * ab);        // the tile is complete once all products have finished
             }
-            if (ok) umma_commit(accbar);                       // the tile is complete once all products have finished
         }
     } else {
         // epilogue warps 2..5: warp w may touch TMEM lanes 32*(w%4) .. +31
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        bool ok = mbar_wait(accbar, 0, 3);
-        if (!ok) failed = 1;
-        ok = __all_sync(0xffffffffu, ok);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        int lt = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            const int ab = lt % NACC;
+            const uint32_t use = lt / NACC;
+            const int row = m0 + quarter * 32 + lane;
+            bool ok = mbar_wait(accfull0 + 8 * ab, use & 1, 3);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_acc = tmem_base + (uint32_t)(ab * BN) + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+                tmem_ld32(tmem_acc + (uint32_t)(c * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int col0 = n0 + c * 32;
                 if (row < p.M && col0 < p.N) {
@@ -200,12 +222,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                 }
             }
+            // hand the accumulator buffer back to the issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(accempty0 + 8 * ab) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -239,14 +264,24 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
     return 0;
 }
 
+int num_sms() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <int BN, int STAGES, typename OutT>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const TcParams& p, cudaStream_t s) {
     const size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
     auto k = gemm_tc_kernel<BN, STAGES, OutT>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TTIE_FAIL("gemm_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-    dim3 grid(ceil_div(p.N, BN), ceil_div(p.M, BM));
-    k<<<grid, 192, smem, s>>>(a, b, p);
+    const int tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN);
+    k<<<tiles < num_sms() ? tiles : num_sms(), 192, smem, s>>>(a, b, p);
     TTIE_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
