@@ -442,3 +442,23 @@ def test_decode_form_one_key_decides(ops, kpos):
     out, exp, dense, qsl = attention_case(ops, "bfloat16", 4, 1, 64, 64, seqs, plan=("mma_decode", 5, 128), spike=(1, 0, kpos))
     assert (out[qsl[1]].view(4, 64) - dense[1][1][kpos, 0]).abs().max() < 2e-2
     assert rel(out, exp) < TOL["bfloat16"]
+
+
+# ------------------------------------------------------------------------------------------ tcgen05 product
+@pytest.mark.parametrize("M,N,K,tile_n", [(128, 256, 64, 256), (2048, 4352, 4096, 256), (300, 520, 200, 256), (1, 1000, 64, 128),
+                                          (129, 72, 4544, 128), (700, 515 * 8, 176 * 8, 256), (260, 33000, 64, 256)])
+def test_gemm_tcgen05(ops, M, N, K, tile_n):
+    """TMA + tcgen05.mma + TMEM product against float64; tiles that hang over every edge, many tiles per
+    CTA (the persistent loop and both accumulator buffers), bias, float32 output."""
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    b = torch.randn(N, generator=g).bfloat16().to(DEV)
+    ref = x.double() @ w.double().T
+    assert rel(ops.linear_tc(x, w, None, None, tile_n).double(), ref) < 8e-3
+    assert rel(ops.linear_tc(x, w, b, torch.float32, tile_n).double(), ref + b.double()) < 1e-5
+    # a strided activation (column slice of a wider buffer)
+    wide = torch.randn(M, K + 64, generator=g).bfloat16().to(DEV)
+    xs = wide[:, 8:8 + K]
+    assert rel(ops.linear_tc(xs, w, None, torch.float32, tile_n).double(), xs.double() @ w.double().T) < 1e-5
+    assert ops.tc_error() == 0

@@ -1,0 +1,194 @@
+"""Per-kernel timings against their rooflines, at the sizes of a model configuration.
+
+    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|all]
+                                                                    [--batch 8] [--ctx 4096] [--tokens 2048]
+
+Every kernel is timed alone inside a captured CUDA graph of ``--iters`` launches (so the host's launch
+cost is not in the number), over inputs that rotate through more than the L2's 126 MB where the
+kernel streams weights.  Printed: microseconds per launch, the bytes or flops the kernel has to move,
+and the fraction of the peak (``MEASURED_PEAKS.json`` beside the repository root if present, else
+6.65 TB/s and 1.59 PFLOP/s).  The defaults are the Llama-2-7B layer sizes with one kv head.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from . import get_ops
+
+DEV = "cuda:0"
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    hbm, tf, src = 6650.0, 1590.0, "fallback"
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+
+        def find(d, key):
+            if isinstance(d, dict):
+                if isinstance(d.get(key), (int, float)):
+                    return float(d[key])
+                for v in d.values():
+                    r = find(v, key)
+                    if r:
+                        return r
+            return None
+        hbm, tf, src = find(m, "hbm_gbs") or hbm, find(m, "bf16_tflops") or tf, "measured"
+    except (OSError, ValueError):
+        pass
+    return hbm, tf, src
+
+
+def timeit(fn, iters=24, warm=3):
+    """Microseconds per call of ``fn(i)``, measured as one replay of a graph of ``iters`` calls."""
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e3
+
+
+def line(name, us, bytes_=None, flops=None):
+    hbm, tf, src = peaks()
+    parts = [f"{name:42s} {us:9.1f} us"]
+    if bytes_ is not None:
+        gbs = bytes_ / us / 1e3
+        parts.append(f"{bytes_ / 1e6:9.1f} MB {gbs:8.0f} GB/s = {gbs / hbm:5.2f} of {src} HBM peak")
+    if flops is not None:
+        t = flops / us / 1e6
+        parts.append(f"{flops / 1e9:9.1f} GF {t:7.0f} TF/s = {t / tf:5.2f} of {src} bf16 peak")
+    print("  ".join(parts), flush=True)
+
+
+def decode(ops, a):
+    d, F, V, Hq, Hkv, D = a.d_model, a.hidden, a.vocab, a.heads, a.kv_heads, a.d_model // a.heads
+    B, ctx, page = a.batch, a.ctx, 64
+    print(f"== decode step kernels, batch {B}, context {ctx}")
+
+    def weights(N, K):
+        n = max(2, int(400e6 // (N * K * 2)))
+        return [torch.randn(N, K, device=DEV).bfloat16() * 0.02 for _ in range(n)]
+
+    x = torch.randn(B, d, device=DEV).bfloat16()
+    for name, N, K in (("qkv projection", (Hq + 2 * Hkv) * D, d), ("output projection", d, Hq * D), ("down projection", d, F),
+                       ("lm_head", V, d)):
+        ws = weights(N, K)
+        xin = torch.randn(B, K, device=DEV).bfloat16()
+        f32 = torch.float32 if name == "lm_head" else None
+        line(f"{name} (weight streaming)", timeit(lambda i: ops.linear(xin, ws[i % len(ws)], None, out_dtype=f32, partial_ok=f32 is None)),
+             bytes_=N * K * 2)
+    ws = weights(2 * F, d)
+    line("gate/up projection + SwiGLU", timeit(lambda i: ops.linear_swiglu(x, ws[i % len(ws)], None, F)), bytes_=2 * F * d * 2)
+    resid, part, w = torch.randn(B, d, device=DEV), torch.randn(4, B, d, device=DEV), torch.ones(d, device=DEV)
+    out = torch.empty(B, d, device=DEV, dtype=torch.bfloat16)
+    line("residual add (4 partial sums) + RMSNorm", timeit(lambda i: ops.add_rmsnorm(resid, part, w, 1e-5, out)), bytes_=B * d * (4 * 5 + 4 + 2))
+    nb = B * (ctx // page) + 1
+    kp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
+    vp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
+    table = (torch.arange(B * (ctx // page), device=DEV, dtype=torch.int32) + 1).view(B, -1)
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
+    tseq = torch.arange(B, dtype=torch.int32, device=DEV)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))).to(DEV)
+    qkvp = torch.randn(4, B, (Hq + 2 * Hkv) * D, device=DEV)
+    q = torch.empty(B, Hq * D, device=DEV, dtype=torch.bfloat16)
+    cs = ops.rope_table(pos, inv)
+    line("rotate + store k/v (from 4 partial sums)", timeit(lambda i: ops.rope_store(qkvp, Hq, Hkv, D, pos, tseq, inv, 0, kp, vp, table, page, True, q_out=q, cs_table=cs)),
+         bytes_=B * (Hq + 2 * Hkv) * D * (4 * 4 + 2))
+    qsl = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    sl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+    o = torch.empty(B, Hq * D, device=DEV, dtype=torch.bfloat16)
+    plan = ops.attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx)
+    line(f"paged attention {plan} + merge", timeit(lambda i: ops.paged_attention(q, Hq, Hkv, D, kp, vp, table, page, qsl, sl, B, 1, ctx, 1 / math.sqrt(D), 0, o)),
+         bytes_=B * ctx * Hkv * D * 2 * 2)
+    logits = torch.randn(B, V, device=DEV)
+    st = torch.zeros(max(B, 1), 8, dtype=torch.int32, device=DEV)
+    st[:, 4] = 0x3f800000
+    st[:, 5] = 0x3f800000
+    tok = torch.empty(B, dtype=torch.int32, device=DEV)
+    line("sampling (temperature)", timeit(lambda i: ops.sample(logits, tseq, st, tok)), bytes_=B * V * 4)
+
+
+def prefill(ops, a):
+    d, F, Hq, Hkv, D = a.d_model, a.hidden, a.heads, a.kv_heads, a.d_model // a.heads
+    T, page = a.tokens, 64
+    print(f"== prefill kernels, one prompt of {T} tokens")
+    resid, delta, w = torch.randn(T, d, device=DEV), torch.randn(T, d, device=DEV).bfloat16(), torch.ones(d, device=DEV)
+    out = torch.empty(T, d, device=DEV, dtype=torch.bfloat16)
+    line("residual add + RMSNorm", timeit(lambda i: ops.add_rmsnorm(resid, delta, w, 1e-5, out), iters=8), bytes_=T * d * (4 + 4 + 2 + 2))
+    gu = torch.randn(T, 2 * F, device=DEV).bfloat16()
+    act = torch.empty(T, F, device=DEV, dtype=torch.bfloat16)
+    line("SwiGLU activation", timeit(lambda i: ops.swiglu(gu, act), iters=8), bytes_=T * F * 2 * 3)
+    nb = T // page + 2
+    kp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
+    vp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
+    table = (torch.arange(nb - 1, device=DEV, dtype=torch.int32) + 1).view(1, -1)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    tseq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))).to(DEV)
+    cs = ops.rope_table(pos, inv)
+    line("rotate + store k/v", timeit(lambda i: ops.rope_store(qkv, Hq, Hkv, D, pos, tseq, inv, 0, kp, vp, table, page, True, cs_table=cs), iters=8),
+         bytes_=T * (Hq + 2 * Hkv) * D * 2 * 2)
+    qsl = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    sl = torch.tensor([T], dtype=torch.int32, device=DEV)
+    o = torch.empty(T, Hq * D, device=DEV, dtype=torch.bfloat16)
+    plan = ops.attention_plan(torch.bfloat16, 1, Hq, Hkv, D, T, T)
+    line(f"causal paged attention {plan}", timeit(lambda i: ops.paged_attention(qkv, Hq, Hkv, D, kp, vp, table, page, qsl, sl, 1, T, T, 1 / math.sqrt(D), 0, o), iters=4),
+         flops=4 * Hq * D * T * (T + 1) // 2)
+
+
+def gemm_tc(ops, a):
+    d, F, Hq, Hkv, D = a.d_model, a.hidden, a.heads, a.kv_heads, a.d_model // a.heads
+    M = a.tokens
+    print(f"== matrix products of a {M}-token portion: library product and the tcgen05 kernel of this package")
+    for name, N, K in (("qkv", (Hq + 2 * Hkv) * D, d), ("out", d, Hq * D), ("gate_up", 2 * F, d), ("down", d, F)):
+        x = torch.randn(M, K, device=DEV).bfloat16()
+        w = (torch.randn(N, K, device=DEV) * 0.02).bfloat16()
+        flops = 2 * M * N * K
+        line(f"{name} [{M}x{K}]x[{K}x{N}] library (cuBLAS)", timeit(lambda i: torch.mm(x, w.t()), iters=8), flops=flops)
+        line(f"{name} [{M}x{K}]x[{K}x{N}] tcgen05 128x256", timeit(lambda i: ops.linear_tc(x, w, None, None, 256), iters=8), flops=flops)
+    err = ops.tc_error()
+    if err:
+        raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "all"))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--d-model", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=1)
+    ap.add_argument("--hidden", type=int, default=11008)
+    ap.add_argument("--vocab", type=int, default=32000)
+    a = ap.parse_args(argv)
+    ops = get_ops(DEV)
+    if a.what in ("decode", "all"):
+        decode(ops, a)
+    if a.what in ("prefill", "all"):
+        prefill(ops, a)
+    if a.what in ("gemm_tc", "all"):
+        gemm_tc(ops, a)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
