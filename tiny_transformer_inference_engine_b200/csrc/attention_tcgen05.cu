@@ -1,0 +1,449 @@
+// Causal paged attention for prompt portions on tcgen05 tensor cores (bfloat16, head size 64 or 128).
+//
+// A CTA owns 128 query rows - (token, head of a kv head's group) pairs, so with multi-query attention
+// 4 tokens x 32 heads share every key/value tile - and walks over 128-key tiles:
+//   warp 0      TMA: key and value tiles straight from the pages (one box per page and 64-column
+//               block, 128-byte swizzle) into a two-stage ring
+//   warp 1      one thread issues  S = Q K^T  (tcgen05.mma, both operands K-major in shared memory,
+//               S in tensor memory, two buffers) and  O_tile = P V  (P from shared memory, V as an
+//               MN-major operand, O_tile in tensor memory, two buffers)
+//   warps 2-5   softmax, one thread per row: tcgen05.ld the row of S, scale, mask, running maximum and
+//               sum in float32, P rounded to bfloat16 into shared memory in the operand layout; one
+//               iteration later the same thread takes O_tile out of tensor memory and adds it to its
+//               row of the output, rescaled - the running output lives in registers, so nothing in
+//               tensor memory is ever rescaled.
+// Mask, scale and table lookup are those of kernels/pagedattn/pagedattn.cu:196-207,256 of the reference.
+// Every mbarrier wait is bounded; a wait that runs out records a code and the CTA winds down.
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+using namespace ttie;
+
+namespace {
+constexpr int BM = 128, BN = 128;
+constexpr long long WAIT_CYCLES = 2000000000LL;
+
+__device__ int g_attn_tc_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const long long deadline = clock64() + WAIT_CYCLES;
+    while (!mbar_try(bar, parity)) {
+        if (clock64() > deadline) { atomicCAS(&g_attn_tc_error, 0, code); return false; }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// K-major operand: rows of 64 bfloat16 (128 bytes), 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (value tile as B: N = head dimension contiguous, K = keys are the 128-byte rows):
+// 8-key groups 1024 bytes apart (stride offset), 64-column blocks `lbo_bytes` apart (leading offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo_bytes) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+
+struct AttnTcParams {
+    const __nv_bfloat16* q; long long q_stride;
+    const int* block_table; int table_width; int page_size;
+    const int* qsl; const int* seq_lens;
+    __nv_bfloat16* out;
+    int num_seqs, Hq, Hkv;
+    float scale_log2; int window;
+    int row_tiles;
+};
+
+// Barrier slots
+enum { KF = 0, KE = 2, VF = 4, VE = 6, SF = 8, SE = 10, OF = 12, OE = 14, PF = 16, PE = 17, NBARS = 18 };
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
+    constexpr int CB = D / 64;                                   // 64-column blocks of the head dimension
+    constexpr uint32_t QBLK = BM * 128, KVBLK = BN * 128;        // bytes of one 64-column block
+    constexpr uint32_t Q_BYTES = CB * QBLK, P_BYTES = (BN / 64) * QBLK, KV_BYTES = CB * KVBLK;
+    constexpr uint32_t TMEM_COLS = 512;                          // 2 x 128 (S) + 2 x D (O_tile), rounded to a power of two
+    constexpr uint32_t S_COL = 0, O_COL = 256;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = smem;
+    unsigned char* Ps = Qs + Q_BYTES;
+    unsigned char* Ks = Ps + P_BYTES;                            // [2 stages]
+    unsigned char* Vs = Ks + 2 * KV_BYTES;                       // [2 stages]
+    __shared__ __align__(8) unsigned long long bars[NBARS];
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.Hq / p.Hkv;
+    int tile = blockIdx.x;
+    const int rt = p.row_tiles - 1 - tile % p.row_tiles;         // long (late) tiles first
+    tile /= p.row_tiles;
+    const int kvh = tile % p.Hkv, seq = tile / p.Hkv;
+    const int q0 = p.qsl[seq], q_len = p.qsl[seq + 1] - q0, kv_len = p.seq_lens[seq];
+    const int nrows = q_len * G, row0 = rt * BM;
+    if (row0 >= nrows) return;                                   // uniform over the CTA, before anything is allocated
+    const int ctx = kv_len - q_len;
+    const int tok_lo = row0 / G, tok_hi = (min(nrows, row0 + BM) - 1) / G;
+    const int key_hi = ctx + tok_hi + 1;                         // exclusive
+    const int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    const int t_begin = key_lo / BN, t_end = (key_hi + BN - 1) / BN;
+    const int ntiles = t_end - t_begin;
+    const uint32_t bar0 = smem_u32(&bars[0]);
+#define BAR(i) (bar0 + 8u * (uint32_t)(i))
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NBARS; ++i) {
+            const bool many = (i >= SE && i < SE + 2) || (i >= OE && i < OE + 2) || i == PF;
+            mbar_init(BAR(i), many ? 128u : 1u);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // queries of the tile -> shared memory in the K-major swizzled operand layout (all 192 threads help)
+    for (int c = threadIdx.x; c < BM * (D / 8); c += blockDim.x) {
+        const int r = c / (D / 8), chunk = c - r * (D / 8);      // chunk: 8 bfloat16 = 16 bytes
+        const int row = row0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < nrows) {
+            const int tok = row / G, g = row - tok * G;
+            v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)(kvh * G + g) * D + chunk * 8);
+        }
+        const int blk = chunk >> 3, cin = chunk & 7;
+        *reinterpret_cast<uint4*>(Qs + blk * QBLK + r * 128 + ((cin ^ (r & 7)) << 4)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes of Q become visible to the tensor core
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int ps = p.page_size;
+            const int box_rows = ps < BN ? ps : BN;
+            const int* table = p.block_table + (size_t)seq * p.table_width;
+            for (int j = 0; j < ntiles; ++j) {
+                const int st = j & 1;
+                const uint32_t par = ((j >> 1) & 1) ^ 1;
+                const int key0 = (t_begin + j) * BN;
+                if (!mbar_wait(BAR(KE + st), par, 1)) break;
+                mbar_expect_tx(BAR(KF + st), KV_BYTES);
+                for (int kk = 0; kk < BN; kk += box_rows) {
+                    const int key = key0 + kk;
+                    const int pg = key / ps;
+                    const int page = pg < p.table_width ? table[pg] : 0;
+                    const int y = (page * p.Hkv + kvh) * ps + (key - pg * ps);
+#pragma unroll
+                    for (int cb = 0; cb < CB; ++cb)
+                        tma_load_2d(smem_u32(Ks + st * KV_BYTES + cb * KVBLK + kk * 128), &tmK, BAR(KF + st), cb * 64, y);
+                }
+                if (!mbar_wait(BAR(VE + st), par, 2)) break;
+                mbar_expect_tx(BAR(VF + st), KV_BYTES);
+                for (int kk = 0; kk < BN; kk += box_rows) {
+                    const int key = key0 + kk;
+                    const int pg = key / ps;
+                    const int page = pg < p.table_width ? table[pg] : 0;
+                    const int y = (page * p.Hkv + kvh) * ps + (key - pg * ps);
+#pragma unroll
+                    for (int cb = 0; cb < CB; ++cb)
+                        tma_load_2d(smem_u32(Vs + st * KV_BYTES + cb * KVBLK + kk * 128), &tmV, BAR(VF + st), cb * 64, y);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // S = Q K^T: D float32, A and B bfloat16 K-major, M = 128, N = 128
+            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // O_tile = P V: B (values) MN-major, N = D
+            constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            auto issue_s = [&](int j) -> bool {
+                const int st = j & 1, sb = j & 1;
+                if (!mbar_wait(BAR(KF + st), (j >> 1) & 1, 3)) return false;
+                if (!mbar_wait(BAR(SE + sb), ((j >> 1) & 1) ^ 1, 4)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t k_addr = smem_u32(Ks + st * KV_BYTES), q_addr = smem_u32(Qs);
+#pragma unroll
+                for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + S_COL + sb * BN, desc_kmajor(q_addr + cb * QBLK) + (uint64_t)(k * 2),
+                                  desc_kmajor(k_addr + cb * KVBLK) + (uint64_t)(k * 2), idesc_s, (cb | k) != 0);
+                umma_commit(BAR(SF + sb));
+                umma_commit(BAR(KE + st));
+                return true;
+            };
+            bool ok = ntiles > 0 ? issue_s(0) : true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                if (j + 1 < ntiles) { ok = issue_s(j + 1); if (!ok) break; }
+                const int st = j & 1, ob = j & 1;
+                if (!mbar_wait(BAR(VF + st), (j >> 1) & 1, 5)) { ok = false; break; }
+                if (!mbar_wait(BAR(OE + ob), ((j >> 1) & 1) ^ 1, 6)) { ok = false; break; }
+                if (!mbar_wait(BAR(PF), j & 1, 7)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t v_addr = smem_u32(Vs + st * KV_BYTES), p_addr = smem_u32(Ps);
+#pragma unroll
+                for (int kb = 0; kb < BN / 64; ++kb)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + O_COL + ob * D, desc_kmajor(p_addr + kb * QBLK) + (uint64_t)(k * 2),
+                                  desc_mnmajor(v_addr + (kb * 64 + k * 16) * 128, KVBLK), idesc_o, (kb | k) != 0);
+                umma_commit(BAR(OF + ob));
+                umma_commit(BAR(VE + st));
+                umma_commit(BAR(PE));
+            }
+        }
+    } else {
+        // softmax: thread = row
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int row = row0 + r;
+        const bool valid = row < nrows;
+        const int tok = valid ? row / G : 0, g = valid ? row - tok * G : 0;
+        const int pos = valid ? ctx + tok : -1;
+        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+        bool ok = true;
+        for (int j = 0; j <= ntiles && ok; ++j) {
+            if (j < ntiles) {
+                const int sb = j & 1;
+                ok = mbar_wait(BAR(SF + sb), (j >> 1) & 1, 8);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int key0 = (t_begin + j) * BN;
+                const bool tile_full = valid && key0 + BN - 1 <= pos && key0 >= lo;
+                // pass 1: scaled, masked scores stay in registers as packed pairs? no - two passes over tensor memory:
+                float mx = -INFINITY;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + S_COL + sb * BN + c * 32, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float s = __uint_as_float(v[i]) * p.scale_log2;
+                        if (!tile_full) {
+                            const int key = key0 + c * 32 + i;
+                            if (!(valid && key <= pos && key >= lo)) s = -INFINITY;
+                        }
+                        mx = fmaxf(mx, s);
+                    }
+                }
+                const float m_new = fmaxf(m_run, mx);
+                const float msub = m_new == -INFINITY ? 0.f : m_new;
+                const float alpha = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+                // the single P buffer must have been read by the previous tile's second product
+                if (j > 0) {
+                    ok = mbar_wait(BAR(PE), (j - 1) & 1, 9);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
+                float lsum = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + S_COL + sb * BN + c * 32, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float s0 = __uint_as_float(v[i]) * p.scale_log2, s1 = __uint_as_float(v[i + 1]) * p.scale_log2;
+                        if (!tile_full) {
+                            const int key = key0 + c * 32 + i;
+                            if (!(valid && key <= pos && key >= lo)) s0 = -INFINITY;
+                            if (!(valid && key + 1 <= pos && key + 1 >= lo)) s1 = -INFINITY;
+                        }
+                        const float p0 = exp2f(s0 - msub), p1 = exp2f(s1 - msub);
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        // the sum uses the rounded probabilities, the ones the second product sees
+                        lsum += __low2float(h) + __high2float(h);
+                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    // 32 keys = 4 chunks of 16 bytes in 64-key block (c / 2)
+                    unsigned char* prow = Ps + (c >> 1) * QBLK + r * 128;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const int cin = (c & 1) * 4 + q4;
+                        *reinterpret_cast<uint4*>(prow + ((cin ^ (r & 7)) << 4)) =
+                            make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                    }
+                }
+                l_run = l_run * alpha + lsum;
+                m_run = m_new;
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(BAR(SE + sb));                              // the scores of this buffer are consumed
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(BAR(PF));                                   // P is in shared memory
+                // rescale what has been summed so far to the new maximum
+                if (alpha != 1.f) {
+#pragma unroll
+                    for (int i = 0; i < D; ++i) o[i] *= alpha;
+                }
+                alpha_prev = alpha;
+            }
+            if (j > 0) {
+                // take the previous tile's product out of tensor memory.  It was computed with the maximum of
+                // tile j-1; the rescale for tile j (alpha above) must apply to it as well.
+                const int ob = (j - 1) & 1;
+                ok = mbar_wait(BAR(OF + ob), ((j - 1) >> 1) & 1, 10);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float f = j < ntiles ? alpha_prev : 1.f;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + O_COL + ob * D + c * 32, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(__uint_as_float(v[i]), f, o[c * 32 + i]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(BAR(OE + ob));
+            }
+        }
+        if (ok && valid) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            __nv_bfloat16* dst = p.out + ((size_t)(q0 + tok) * p.Hq + kvh * G + g) * D;
+#pragma unroll
+            for (int i = 0; i < D; i += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(o[i + 2 * k] * inv, o[i + 2 * k + 1] * inv);
+                    w[k] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+#undef BAR
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+// pages [num_pages][Hkv][page][D] seen as a matrix [num_pages*Hkv*page][D]; box = 64 columns x box_rows keys
+int make_page_map(CUtensorMap* map, const void* base, long long rows, int D, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) TTIE_FAIL("attention_tc: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TTIE_FAIL("attention_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+template <int D>
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, cudaStream_t s) {
+    const size_t smem = (size_t)(D / 64) * BM * 128 + (size_t)(BN / 64) * BM * 128 + 4 * (size_t)(D / 64) * BN * 128 + 1024;
+    auto k = attn_tc_kernel<D>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    k<<<p.num_seqs * p.Hkv * p.row_tiles, 192, smem, s>>>(mk, mv, p);
+    TTIE_CHECK_LAUNCH("attention_tc");
+    return 0;
+}
+}  // namespace
+
+extern "C" int ttie_attn_tc_error() {
+    int v = 0, zero = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&v, g_attn_tc_error, sizeof(int));
+    if (v) cudaMemcpyToSymbol(g_attn_tc_error, &zero, sizeof(int));
+    return v;
+}
+
+// Head size 64 or 128; page size a multiple of 8 that divides 128 or is a multiple of 128.
+extern "C" int ttie_attn_tc_supported(int D, int page_size) {
+    return (D == 64 || D == 128) && page_size >= 8 && page_size % 8 == 0 && (128 % page_size == 0 || page_size % 128 == 0) && page_size <= 256;
+}
+
+extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                       int num_pages, const int* block_table, int table_width, int page_size, const int* qsl,
+                                       const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                       int max_q_len, float scale, int window, void* stream) {
+    if (T <= 0 || num_seqs <= 0) return 0;
+    if (!ttie_attn_tc_supported(D, page_size)) TTIE_FAIL("attention_tc: head size %d with pages of %d keys is not supported", D, page_size);
+    if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("attention_tc: %d heads are not a multiple of %d kv heads", Hq, Hkv);
+    if (q_stride % 8 || ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15)
+        TTIE_FAIL("attention_tc: pointers must be 16-byte aligned and the query stride a multiple of 8");
+    CUtensorMap mk, mv;
+    const long long rows = (long long)num_pages * Hkv * page_size;
+    const int box_rows = page_size < BN ? page_size : BN;
+    if (make_page_map(&mk, k_pages, rows, D, box_rows)) return -1;
+    if (make_page_map(&mv, v_pages, rows, D, box_rows)) return -1;
+    AttnTcParams p;
+    p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.block_table = block_table; p.table_width = table_width;
+    p.page_size = page_size; p.qsl = qsl; p.seq_lens = seq_lens; p.out = (__nv_bfloat16*)out;
+    p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+    p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), BM);
+    if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("attention_tc: grid too large");
+    cudaStream_t s = (cudaStream_t)stream;
+    return D == 64 ? launch<64>(mk, mv, p, s) : launch<128>(mk, mv, p, s);
+}

@@ -48,6 +48,8 @@ _SIGNATURES = {
     "ttie_paged_attention_mma_form": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
                                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
                                       _c_void, _c_int, _c_void],
+    "ttie_paged_attention_tc": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
+                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
 }
@@ -83,7 +85,9 @@ class CudaOps:
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
         self.attn_target_ctas = 2 * NUM_SMS
+        self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
+        self.lib.ttie_attn_tc_supported.restype = _c_int
         for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows", "ttie_attn_decode_max_rows", "ttie_attn_decode_split_len"):
             getattr(self.lib, name).restype = _c_int
 
@@ -204,8 +208,11 @@ class CudaOps:
         return out
 
     def tc_error(self) -> int:
-        """Error word of the tensor-core kernels (0 = none); synchronises the device."""
-        return int(self.lib.ttie_tc_error())
+        """Error word of the tcgen05 kernels (0 = none; otherwise the code of the first bounded wait that
+        ran out: product 1-4, attention 101-110); synchronises the device."""
+        g = int(self.lib.ttie_tc_error())
+        a = int(self.lib.ttie_attn_tc_error())
+        return g or (100 + a if a else 0)
 
     def linear_swiglu(self, x, w_gu, b_gu, hidden):
         """silu(x @ Wg.T) * (x @ Wu.T) with w_gu = [Wg; Wu] ([2*hidden, K]) -> [M, hidden]."""
@@ -265,13 +272,16 @@ class CudaOps:
                                                  stream), "rope_store")
         self.launches += 1
 
-    def attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len):
+    def attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size=None):
         """Which attention kernel runs and how the key range is split: (kernel, num_splits,
         split_len).  bfloat16 with a head size that is a multiple of 16 up to 128 runs on
         tensor cores; everything else runs the general float32-arithmetic kernel.  The key
         range is split only when the query rows alone cannot fill the GPU."""
         G = num_heads // num_kv_heads
         rows = max_q_len * G
+        if (dtype == torch.bfloat16 and page_size is not None and rows >= self.attn_tc_min_rows
+                and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
+            return "tc", 1, 0                                   # prompt portions: the tcgen05 kernel
         if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
             kernel, tile_rows, unit, min_len = "mma", self.lib.ttie_attn_mma_tile_rows(max_q_len, num_heads, num_kv_heads), 64, 128
         else:
@@ -290,7 +300,14 @@ class CudaOps:
                         plan=None):
         T = qkv.shape[0]
         kernel, num_splits, split_len = plan if plan is not None else self.attention_plan(
-            qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
+            qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
+        if kernel == "tc":
+            self._check(self.lib.ttie_paged_attention_tc(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
+                block_table.shape[1], page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads,
+                num_kv_heads, head_dim, max_q_len, float(scale), int(window), self._stream(qkv)), "paged_attention_tc")
+            self.launches += 1
+            return
         scratch = None
         if num_splits > 1:
             scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
