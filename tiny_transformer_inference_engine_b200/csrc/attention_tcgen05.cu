@@ -81,6 +81,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ float ex2(float x) {                // 2^x, one instruction; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct AttnTcParams {
     const __nv_bfloat16* q; long long q_stride;
     const int* block_table; int table_width; int page_size;
@@ -257,33 +263,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int key0 = (t_begin + j) * BN;
-                const bool tile_full = valid && key0 + BN - 1 <= pos && key0 >= lo;
-                // pass 1: scaled, masked scores stay in registers as packed pairs? no - two passes over tensor memory:
+                // columns lo_col..hi_col of this tile are visible to the row; a tile that every row of the warp
+                // sees whole takes the path without compares
+                const int hi_col = valid ? pos - key0 : -1, lo_col = lo - key0;
+                const bool tile_full = __all_sync(0xffffffffu, valid && hi_col >= BN - 1 && lo_col <= 0);
+                // pass 1 over tensor memory: the row maximum of the raw scores (the scale is positive)
                 float mx = -INFINITY;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t v[32];
                     tmem_ld32(lane_addr + S_COL + sb * BN + c * 32, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (tile_full) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float s = __uint_as_float(v[i]) * p.scale_log2;
-                        if (!tile_full) {
-                            const int key = key0 + c * 32 + i;
-                            if (!(valid && key <= pos && key >= lo)) s = -INFINITY;
+                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int col = c * 32 + i;
+                            mx = fmaxf(mx, (col <= hi_col && col >= lo_col) ? __uint_as_float(v[i]) : -INFINITY);
                         }
-                        mx = fmaxf(mx, s);
                     }
                 }
+                mx *= p.scale_log2;                                          // -inf stays -inf
                 const float m_new = fmaxf(m_run, mx);
                 const float msub = m_new == -INFINITY ? 0.f : m_new;
-                const float alpha = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+                const float alpha = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);
                 // the single P buffer must have been read by the previous tile's second product
                 if (j > 0) {
                     ok = mbar_wait(BAR(PE), (j - 1) & 1, 9);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                 }
+                // pass 2: probabilities, rounded to bfloat16 into the operand layout; their sum in float32
                 float lsum = 0.f;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
@@ -291,19 +303,27 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                     tmem_ld32(lane_addr + S_COL + sb * BN + c * 32, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     uint32_t packed[16];
+                    if (tile_full) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float s0 = __uint_as_float(v[i]) * p.scale_log2, s1 = __uint_as_float(v[i + 1]) * p.scale_log2;
-                        if (!tile_full) {
-                            const int key = key0 + c * 32 + i;
-                            if (!(valid && key <= pos && key >= lo)) s0 = -INFINITY;
-                            if (!(valid && key + 1 <= pos && key + 1 >= lo)) s1 = -INFINITY;
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -msub));
+                            const float p1 = ex2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -msub));
+                            lsum += p0 + p1;
+                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
                         }
-                        const float p0 = exp2f(s0 - msub), p1 = exp2f(s1 - msub);
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        // the sum uses the rounded probabilities, the ones the second product sees
-                        lsum += __low2float(h) + __high2float(h);
-                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const int col = c * 32 + i;
+                            float p0 = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -msub));
+                            float p1 = ex2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -msub));
+                            if (!(col <= hi_col && col >= lo_col)) p0 = 0.f;
+                            if (!(col + 1 <= hi_col && col + 1 >= lo_col)) p1 = 0.f;
+                            lsum += p0 + p1;
+                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                        }
                     }
                     // 32 keys = 4 chunks of 16 bytes in 64-key block (c / 2)
                     unsigned char* prow = Ps + (c >> 1) * QBLK + r * 128;
