@@ -462,3 +462,41 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n):
     xs = wide[:, 8:8 + K]
     assert rel(ops.linear_tc(xs, w, None, torch.float32, tile_n).double(), xs.double() @ w.double().T) < 1e-5
     assert ops.tc_error() == 0
+
+
+# ------------------------------------------------------------------------------------------ tcgen05 attention
+TC_SHAPES = [(32, 1, 128, 64), (32, 1, 128, 16), (8, 2, 64, 8), (3, 1, 64, 128), (71, 1, 64, 64), (4, 2, 128, 32), (5, 5, 64, 256)]
+
+
+@pytest.mark.parametrize("scenario", ["prefill", "chunked", "mixed", "decode"])
+@pytest.mark.parametrize("Hq,Hkv,D,page", TC_SHAPES)
+def test_tcgen05_attention(ops, scenario, Hq, Hkv, D, page):
+    seqs = SCENARIOS[scenario] + [(700, 700)]
+    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=("tc", 1, 0))
+    assert ops.tc_error() == 0
+    assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("window", [1, 5, 100, 129, 300])
+def test_tcgen05_attention_window(ops, window):
+    out, exp, _, _ = attention_case(ops, "bfloat16", 4, 2, 64, 16, [(450, 450), (90, 1), (300, 40)], window=window, plan=("tc", 1, 0))
+    assert ops.tc_error() == 0 and rel(out, exp) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("kpos", [0, 63, 64, 127, 128, 447, 599])
+def test_tcgen05_attention_one_key_decides(ops, kpos):
+    seqs = [(50, 1), (600, 1), (64, 3), (600, 600)]
+    for spike_q in ((1, 0), (3, 599)):
+        out, exp, dense, qsl = attention_case(ops, "bfloat16", 4, 1, 64, 64, seqs, plan=("tc", 1, 0), spike=(spike_q[0], spike_q[1], kpos))
+        row = out[qsl[spike_q[0]] + spike_q[1]].view(4, 64)
+        assert (row - dense[spike_q[0]][1][kpos, 0]).abs().max() < 2e-2
+        assert rel(out, exp) < TOL["bfloat16"]
+    assert ops.tc_error() == 0
+
+
+def test_tcgen05_attention_refuses(ops):
+    from tiny_transformer_inference_engine_b200.ops import KernelError
+    with pytest.raises(KernelError, match="not supported"):
+        attention_case(ops, "bfloat16", 4, 1, 32, 16, [(40, 40)], plan=("tc", 1, 0))
+    with pytest.raises(KernelError, match="not supported"):
+        attention_case(ops, "bfloat16", 4, 1, 64, 24, [(40, 40)], plan=("tc", 1, 0))

@@ -106,6 +106,8 @@ class Engine:
             tokens = self.sampler.sample(logits[:len(slots)], slot_ids).tolist()       # one device-to-host read
         else:
             tokens = []
+        if hasattr(self.ops, "check_tc"):
+            self.ops.check_tc()
         return sched.update(entries, tokens)
 
     # ---------------------------------------------------------------- whole generations

@@ -79,6 +79,8 @@ def run(engine, lines, out_dir: str, log=sys.stdout) -> None:
                 lengths[e.rid] += len(e.tokens)
             if logits.shape[0]:
                 arr = logits.float().cpu().numpy().astype("<f4", copy=False)
+                if hasattr(engine.ops, "check_tc"):
+                    engine.ops.check_tc()
                 arr.tofile(os.path.join(out_dir, f"{step}.f32"))
         for rid in rec.get("end", []):
             if rid in lengths:

@@ -84,6 +84,7 @@ class CudaOps:
             fn.argtypes, fn.restype = argtypes, _c_int
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
+        self.tc_used = False                  # a tcgen05 kernel ran since the error word was last read
         self.attn_target_ctas = 2 * NUM_SMS
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
@@ -202,6 +203,7 @@ class CudaOps:
         M, K = x.shape
         N = w.shape[0]
         out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
+        self.tc_used = True
         self._check(self.lib.ttie_gemm_tc(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(0),
                                           M, N, K, 1 if out.dtype == torch.float32 else 0, tile_n, self._stream(x)), "gemm_tc")
         self.launches += 1
@@ -213,6 +215,15 @@ class CudaOps:
         g = int(self.lib.ttie_tc_error())
         a = int(self.lib.ttie_attn_tc_error())
         return g or (100 + a if a else 0)
+
+    def check_tc(self):
+        """After a point where the host has waited for the device: raises if a bounded wait inside a
+        tcgen05 kernel launched since the last check ran out (its result is then not to be trusted)."""
+        if self.tc_used:
+            self.tc_used = False
+            code = self.tc_error()
+            if code:
+                raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {code}); its output is invalid")
 
     def linear_swiglu(self, x, w_gu, b_gu, hidden):
         """silu(x @ Wg.T) * (x @ Wu.T) with w_gu = [Wg; Wu] ([2*hidden, K]) -> [M, hidden]."""
@@ -302,6 +313,7 @@ class CudaOps:
         kernel, num_splits, split_len = plan if plan is not None else self.attention_plan(
             qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
         if kernel == "tc":
+            self.tc_used = True
             self._check(self.lib.ttie_paged_attention_tc(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                 block_table.shape[1], page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads,
