@@ -70,6 +70,7 @@ paged_attn_mma_kernel(const MmaParams p) {
     __nv_bfloat16* Ks = Qs + BM * LDS;                                             // [2][BN][LDS]
     __nv_bfloat16* Vs = Ks + 2 * BN * LDS;                                         // [2][BN][LDS]
     long long* rowoff = reinterpret_cast<long long*>(Vs + 2 * BN * LDS);           // [2][BN] element offset of a key's row, -1: none
+    TTIE_PDL_ENTRY();
 
     const int G = p.Hq / p.Hkv;
     int tile = blockIdx.x;
@@ -496,7 +497,7 @@ int launch(const MmaParams& p, cudaStream_t s) {
         if (e != cudaSuccess) TTIE_FAIL("paged_attention_mma: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     }
     dim3 grid(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits);
-    k<<<grid, NWARPS * 32, smem, s>>>(p);
+    TTIE_LAUNCH(k, grid, NWARPS * 32, smem, s, p);
     TTIE_CHECK_LAUNCH("paged_attention_mma");
     return 0;
 }

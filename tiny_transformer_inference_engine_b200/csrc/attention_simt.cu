@@ -195,6 +195,7 @@ template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, T* __restrict__ out,
                                   int num_splits, int D) {
     extern __shared__ float wgt[];                                  // [num_splits]
+    TTIE_PDL_ENTRY();
     const size_t row = blockIdx.x;
     const float* ml = ws_ml + row * num_splits * 2;
     const int lane = threadIdx.x & 31;
@@ -230,7 +231,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
 
 namespace ttie {
 int attn_merge_bf16(const float* ws_o, const float* ws_ml, void* out, int rows, int num_splits, int D, cudaStream_t s) {
-    attn_merge_kernel<__nv_bfloat16><<<rows, D >= 128 ? 128 : 64, num_splits * sizeof(float), s>>>(ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    TTIE_LAUNCH(attn_merge_kernel<__nv_bfloat16>, rows, D >= 128 ? 128 : 64, num_splits * sizeof(float), s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
     TTIE_CHECK_LAUNCH("attention merge");
     return 0;
 }

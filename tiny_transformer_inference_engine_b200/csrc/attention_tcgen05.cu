@@ -7,11 +7,11 @@
 //   warp 1      one thread issues  S = Q K^T  (tcgen05.mma, both operands K-major in shared memory,
 //               S in tensor memory, two buffers) and  O_tile = P V  (P from shared memory, V as an
 //               MN-major operand, O_tile in tensor memory, two buffers)
-//   warps 2-5   softmax, one thread per row: tcgen05.ld the row of S, scale, mask, running maximum and
-//               sum in float32, P rounded to bfloat16 into shared memory in the operand layout; one
-//               iteration later the same thread takes O_tile out of tensor memory and adds it to its
-//               row of the output, rescaled - the running output lives in registers, so nothing in
-//               tensor memory is ever rescaled.
+//   warps 2-9   softmax, two threads per row (each one half of the columns): tcgen05.ld the row of S,
+//               scale, mask, running maximum and sum in float32, P rounded to bfloat16 into shared memory
+//               in the operand layout; one iteration later the same threads take O_tile out of tensor
+//               memory and add it to their part of the output row, rescaled - the running output lives
+//               in registers, so nothing in tensor memory is ever rescaled.
 // Mask, scale and table lookup are those of kernels/pagedattn/pagedattn.cu:196-207,256 of the reference.
 // Every mbarrier wait is bounded; a wait that runs out records a code and the CTA winds down.
 #include "common.cuh"
@@ -98,10 +98,10 @@ struct AttnTcParams {
 };
 
 // Barrier slots
-enum { KF = 0, KE = 2, VF = 4, VE = 6, SF = 8, SE = 10, OF = 12, OE = 14, PF = 16, PE = 17, NBARS = 18 };
+enum { KF = 0, KE = 2, VF = 4, VE = 6, SF = 8, SE = 10, OF = 12, OE = 14, PF = 16, PE = 17, XB = 18, XL = 20, NBARS = 21 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
     constexpr int CB = D / 64;                                   // 64-column blocks of the head dimension
     constexpr uint32_t QBLK = BM * 128, KVBLK = BN * 128;        // bytes of one 64-column block
@@ -116,6 +116,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     unsigned char* Vs = Ks + 2 * KV_BYTES;                       // [2 stages]
     __shared__ __align__(8) unsigned long long bars[NBARS];
     __shared__ uint32_t tmem_slot;
+    __shared__ float xch[2][2][BM];                               // row maxima of the two column halves, by tile parity
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.Hq / p.Hkv;
@@ -137,8 +138,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NBARS; ++i) {
-            const bool many = (i >= SE && i < SE + 2) || (i >= OE && i < OE + 2) || i == PF;
-            mbar_init(BAR(i), many ? 128u : 1u);
+            const bool many = (i >= SE && i < SE + 2) || (i >= OE && i < OE + 2) || i == PF || i >= XB;
+            mbar_init(BAR(i), many ? 256u : 1u);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -241,8 +242,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             }
         }
     } else {
-        // softmax: thread = row
-        const int quarter = warp & 3;
+        // softmax: two threads per row (warps w and w+4 reach the same 32 lanes of tensor memory); each
+        // owns one half of the tile's 128 score columns and one half of the output columns.  Only the row
+        // maximum is exchanged per tile (shared memory + an mbarrier with a bounded wait); the row sums are
+        // added at the end.  A thread reads its 64 scores once (two tcgen05.ld, one wait) and keeps them in
+        // registers across the exchange.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const int row = row0 + r;
         const bool valid = row < nrows;
@@ -250,9 +255,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const int pos = valid ? ctx + tok : -1;
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        float o[D];
+        constexpr int SC = BN / 2, OC = D / 2;                          // score and output columns of this thread
+        float o[OC];
 #pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        for (int i = 0; i < OC; ++i) o[i] = 0.f;
         float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
         bool ok = true;
         for (int j = 0; j <= ntiles && ok; ++j) {
@@ -267,25 +273,34 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 // sees whole takes the path without compares
                 const int hi_col = valid ? pos - key0 : -1, lo_col = lo - key0;
                 const bool tile_full = __all_sync(0xffffffffu, valid && hi_col >= BN - 1 && lo_col <= 0);
-                // pass 1 over tensor memory: the row maximum of the raw scores (the scale is positive)
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(lane_addr + S_COL + sb * BN + c * 32, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (tile_full) {
+                uint32_t sv[2][32];
+                tmem_ld32(lane_addr + S_COL + sb * BN + half * SC, sv[0]);
+                tmem_ld32(lane_addr + S_COL + sb * BN + half * SC + 32, sv[1]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(BAR(SE + sb));                              // the scores are in registers: the buffer is free
+                if (!tile_full) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                    } else {
+                    for (int c = 0; c < 2; ++c)
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const int col = c * 32 + i;
-                            mx = fmaxf(mx, (col <= hi_col && col >= lo_col) ? __uint_as_float(v[i]) : -INFINITY);
+                            const int col = half * SC + c * 32 + i;
+                            if (!(col <= hi_col && col >= lo_col)) sv[c][i] = 0xff800000u;       // -inf
                         }
-                    }
                 }
-                mx *= p.scale_log2;                                          // -inf stays -inf
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+                // exchange with the thread that owns the other half of the row (a bounded wait, not bar.sync:
+                // a warp that gave up elsewhere must not leave the others waiting for ever)
+                xch[j & 1][half][r] = mx;
+                mbar_arrive(BAR(XB + (j & 1)));
+                ok = mbar_wait(BAR(XB + (j & 1)), (j >> 1) & 1, 11);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                mx = fmaxf(mx, xch[j & 1][half ^ 1][r]) * p.scale_log2;      // -inf stays -inf (the scale is positive)
                 const float m_new = fmaxf(m_run, mx);
                 const float msub = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);
@@ -295,55 +310,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                 }
-                // pass 2: probabilities, rounded to bfloat16 into the operand layout; their sum in float32
+                // probabilities, rounded to bfloat16 into the operand layout; their sum in float32
                 float lsum = 0.f;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(lane_addr + S_COL + sb * BN + c * 32, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                unsigned char* prow = Ps + half * QBLK + r * 128;        // this half's 64 keys are 64-key block `half`
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
                     uint32_t packed[16];
-                    if (tile_full) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float p0 = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -msub));
-                            const float p1 = ex2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -msub));
-                            lsum += p0 + p1;
-                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const int col = c * 32 + i;
-                            float p0 = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -msub));
-                            float p1 = ex2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -msub));
-                            if (!(col <= hi_col && col >= lo_col)) p0 = 0.f;
-                            if (!(col + 1 <= hi_col && col + 1 >= lo_col)) p1 = 0.f;
-                            lsum += p0 + p1;
-                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-                        }
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -msub));
+                        const float p1 = ex2(fmaf(__uint_as_float(sv[c][i + 1]), p.scale_log2, -msub));
+                        lsum += p0 + p1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
                     }
-                    // 32 keys = 4 chunks of 16 bytes in 64-key block (c / 2)
-                    unsigned char* prow = Ps + (c >> 1) * QBLK + r * 128;
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
-                        const int cin = (c & 1) * 4 + q4;
+                        const int cin = c * 4 + q4;
                         *reinterpret_cast<uint4*>(prow + ((cin ^ (r & 7)) << 4)) =
                             make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                     }
                 }
                 l_run = l_run * alpha + lsum;
                 m_run = m_new;
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(BAR(SE + sb));                              // the scores of this buffer are consumed
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(BAR(PF));                                   // P is in shared memory
                 // rescale what has been summed so far to the new maximum
                 if (alpha != 1.f) {
 #pragma unroll
-                    for (int i = 0; i < D; ++i) o[i] *= alpha;
+                    for (int i = 0; i < OC; ++i) o[i] *= alpha;
                 }
                 alpha_prev = alpha;
             }
@@ -356,23 +351,31 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float f = j < ntiles ? alpha_prev : 1.f;
+                uint32_t ov[OC / 32][32];
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(lane_addr + O_COL + ob * D + c * 32, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(__uint_as_float(v[i]), f, o[c * 32 + i]);
-                }
+                for (int c = 0; c < OC / 32; ++c) tmem_ld32(lane_addr + O_COL + ob * D + half * OC + c * 32, ov[c]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(BAR(OE + ob));
+#pragma unroll
+                for (int c = 0; c < OC / 32; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(__uint_as_float(ov[c][i]), f, o[c * 32 + i]);
             }
         }
+        // the two halves of a row add their sums
+        float l_tot = 0.f;
+        if (ok) {
+            xch[ntiles & 1][half][r] = l_run;                            // the buffer the last tile did not use
+            mbar_arrive(BAR(XL));
+            ok = mbar_wait(BAR(XL), 0, 12);
+            l_tot = l_run + xch[ntiles & 1][half ^ 1][r];
+        }
         if (ok && valid) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            __nv_bfloat16* dst = p.out + ((size_t)(q0 + tok) * p.Hq + kvh * G + g) * D;
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+            __nv_bfloat16* dst = p.out + ((size_t)(q0 + tok) * p.Hq + kvh * G + g) * D + half * OC;
 #pragma unroll
-            for (int i = 0; i < D; i += 8) {
+            for (int i = 0; i < OC; i += 8) {
                 uint32_t w[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -425,7 +428,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, 
     auto k = attn_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-    k<<<p.num_seqs * p.Hkv * p.row_tiles, 192, smem, s>>>(mk, mv, p);
+    k<<<p.num_seqs * p.Hkv * p.row_tiles, 320, smem, s>>>(mk, mv, p);
     TTIE_CHECK_LAUNCH("attention_tc");
     return 0;
 }

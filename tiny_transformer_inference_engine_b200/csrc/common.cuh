@@ -22,6 +22,11 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// first statement of a kernel: wait for the predecessor's results, then let the successor be scheduled
+#define TTIE_PDL_ENTRY() do { ::ttie::pdl_wait(); ::ttie::pdl_launch_dependents(); } while (0)
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -51,5 +56,24 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 int attn_merge_bf16(const float* ws_o, const float* ws_ml, void* out, int rows, int num_splits, int D, cudaStream_t s);
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Programmatic dependent launch: a kernel launched this way may be scheduled while its predecessor in
+// the stream drains; it must call pdl_wait() before it touches anything the predecessor wrote (the
+// kernels here call it first thing, so only launch latency and CTA scheduling overlap).  Works inside
+// captured graphs.  ttie_set_pdl(0) turns it off.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#define TTIE_LAUNCH(kernel, grid, block, smem, stream, ...) \
+    ::ttie::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
+
 
 }  // namespace ttie

@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 
 namespace ttie {
 static thread_local char g_error[512] = "";
@@ -19,6 +20,14 @@ void set_error(const char* fmt, ...) {
 }  // namespace ttie
 using namespace ttie;
 
+namespace ttie {
+static int g_pdl = -1;
+bool pdl_enabled() {
+    if (g_pdl < 0) { const char* e = getenv("TTIE_PDL"); g_pdl = (e && e[0] == '0') ? 0 : 1; }
+    return g_pdl != 0;
+}
+}  // namespace ttie
+extern "C" void ttie_set_pdl(int on) { ttie::g_pdl = on ? 1 : 0; }
 extern "C" const char* ttie_last_error() { return ttie::g_error; }
 extern "C" int ttie_abi_version() { return 4; }
 
@@ -26,6 +35,7 @@ extern "C" int ttie_abi_version() { return 4; }
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                              int d, int vocab) {
+    TTIE_PDL_ENTRY();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);          // ids are validated on the host; never read outside
@@ -38,8 +48,8 @@ extern "C" int ttie_embed(const int* ids, const void* table, float* out, int T, 
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
-    if (dtype == kF32) embed_kernel<float><<<T, threads, 0, s>>>(ids, (const float*)table, out, d, vocab);
-    else if (dtype == kBF16) embed_kernel<__nv_bfloat16><<<T, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, out, d, vocab);
+    if (dtype == kF32) TTIE_LAUNCH(embed_kernel<float>, T, threads, 0, s, ids, (const float*)table, out, d, vocab);
+    else if (dtype == kBF16) TTIE_LAUNCH(embed_kernel<__nv_bfloat16>, T, threads, 0, s, ids, (const __nv_bfloat16*)table, out, d, vocab);
     else TTIE_FAIL("embed: unknown dtype %d", dtype);
     TTIE_CHECK_LAUNCH("embed");
     return 0;
@@ -107,6 +117,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, c
                        int S, long long part_stride, const int* __restrict__ rows,
                        const W* __restrict__ weight, T* __restrict__ out, int d, float eps) {
     __shared__ float scratch[32];
+    TTIE_PDL_ENTRY();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * d;
     float4 v[MAXC];
@@ -151,11 +162,11 @@ static int launch_rmsnorm(float* resid, const void* delta, const float* dpart, i
                          && (part_stride % 4 == 0);
     if (d % 4 == 0 && d <= 8192 && aligned) {
         if (w_dtype == kF32) {
-            if (d <= 2048) add_rmsnorm_vec_kernel<T, float, 128, 4><<<R, 128, 0, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
-            else add_rmsnorm_vec_kernel<T, float, 256, 8><<<R, 256, 0, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
+            if (d <= 2048) TTIE_LAUNCH((add_rmsnorm_vec_kernel<T, float, 128, 4>), R, 128, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
+            else TTIE_LAUNCH((add_rmsnorm_vec_kernel<T, float, 256, 8>), R, 256, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
         } else if (w_dtype == kBF16) {
-            if (d <= 2048) add_rmsnorm_vec_kernel<T, __nv_bfloat16, 128, 4><<<R, 128, 0, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
-            else add_rmsnorm_vec_kernel<T, __nv_bfloat16, 256, 8><<<R, 256, 0, s>>>(resid, (const T*)delta, dpart, S, part_stride, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
+            if (d <= 2048) TTIE_LAUNCH((add_rmsnorm_vec_kernel<T, __nv_bfloat16, 128, 4>), R, 128, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
+            else TTIE_LAUNCH((add_rmsnorm_vec_kernel<T, __nv_bfloat16, 256, 8>), R, 256, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
         } else TTIE_FAIL("rmsnorm: unknown weight dtype %d", w_dtype);
         TTIE_CHECK_LAUNCH("rmsnorm");
         return 0;
@@ -402,6 +413,7 @@ extern "C" int ttie_rope_store_partial(const float* part, int S, long long part_
 // Per step (not per layer): cos and sin of pos * inv_freq[j] for every token, [T][D/2] float2.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, float2* __restrict__ cs,
                                   int half, int total) {
+    TTIE_PDL_ENTRY();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int t = i / half, j = i - t * half;
@@ -413,7 +425,7 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 extern "C" int ttie_rope_table(const int* positions, const float* inv_freq, void* cs, int T, int half, void* stream) {
     if (T <= 0) return 0;
     const int total = T * half;
-    rope_table_kernel<<<ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, (float2*)cs, half, total);
+    TTIE_LAUNCH(rope_table_kernel, ceil_div(total, 256), 256, 0, (cudaStream_t)stream, positions, inv_freq, (float2*)cs, half, total);
     TTIE_CHECK_LAUNCH("rope_table");
     return 0;
 }
@@ -428,6 +440,7 @@ rope_store_vec_kernel(T* __restrict__ qkv, long long row_stride, const float* __
                       const float2* __restrict__ cs, T* __restrict__ q_out, long long q_stride,
                       T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                       int page_size, int num_pages, int write_kv) {
+    TTIE_PDL_ENTRY();
     const int t = blockIdx.x;
     const int width = (Hq + 2 * Hkv) * D, half = D >> 1;
     const int pos = positions[t];
@@ -481,7 +494,7 @@ extern "C" int ttie_rope_store_vec(void* qkv, long long row_stride, const float*
         TTIE_FAIL("rope_store_vec: pointers must be 16-byte aligned");
     if (row_stride % 4 || q_stride % 4 || part_stride % 4) TTIE_FAIL("rope_store_vec: strides must be multiples of 4");
     cudaStream_t s = (cudaStream_t)stream;
-#define TTIE_ROPE_VEC(TT, P) rope_store_vec_kernel<TT, P><<<T, 256, 0, s>>>((TT*)qkv, row_stride, part, S, part_stride, Hq, Hkv, D, \
+#define TTIE_ROPE_VEC(TT, P) TTIE_LAUNCH((rope_store_vec_kernel<TT, P>), T, 256, 0, s, (TT*)qkv, row_stride, part, S, part_stride, Hq, Hkv, D, \
         positions, token_seq, (const float2*)cs, (TT*)q_out, q_stride, (TT*)k_pages, (TT*)v_pages, block_table, table_width, \
         page_size, num_pages, write_kv)
     if (dtype == kF32) { if (part) TTIE_ROPE_VEC(float, true); else TTIE_ROPE_VEC(float, false); }

@@ -70,9 +70,11 @@ skinny_gemm_kernel(const SkinnyParams p) {
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
     // Two register buffers: the loads of the next 32*U keys are in flight while the current ones
-    // feed the tensor core, so every warp always has weight bytes on their way from HBM.
+    // feed the tensor core, so every warp always has weight bytes on their way from HBM.  The weights
+    // do not depend on the kernel before this one, so the first loads of both buffers are issued
+    // before the wait for that kernel's results: the stream from HBM ramps up while it drains.
     uint4 wA[U][NSET][2], xA[U][MT], wB[U][NSET][2], xB[U][MT];
-    auto load = [&](int k0, uint4 (&wv)[U][NSET][2], uint4 (&xv)[U][MT]) {
+    auto load_w = [&](int k0, uint4 (&wv)[U][NSET][2]) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int kk = k0 + 32 * u + 8 * q;
@@ -82,6 +84,13 @@ skinny_gemm_kernel(const SkinnyParams p) {
                 wv[u][s][0] = (ok && row_a) ? ld_stream(wrow[s][0] + kk) : zero;
                 wv[u][s][1] = (ok && row_b) ? ld_stream(wrow[s][1] + kk) : zero;
             }
+        }
+    };
+    auto load_x = [&](int k0, uint4 (&xv)[U][MT]) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int kk = k0 + 32 * u + 8 * q;
+            const bool ok = kk < k_end;
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
                 const int m = 8 * j + r;
@@ -100,13 +109,17 @@ skinny_gemm_kernel(const SkinnyParams p) {
                     mma_bf16(acc[s][j], wv[u][s][0].z, wv[u][s][1].z, wv[u][s][0].w, wv[u][s][1].w, xv[u][j].z, xv[u][j].w);
                 }
     };
-    if (k_begin < k_end) load(k_begin, wA, xA);
+    load_w(k_begin, wA);                                       // (loads past k_end give zeros)
+    load_w(k_begin + 32 * U, wB);
+    TTIE_PDL_ENTRY();                                          // the activations are the predecessor's output
+    load_x(k_begin, xA);
+    load_x(k_begin + 32 * U, xB);
     for (int k0 = k_begin; k0 < k_end; k0 += 64 * U) {
-        if (k0 + 32 * U < k_end) load(k0 + 32 * U, wB, xB);
         compute(wA, xA);
+        if (k0 + 64 * U < k_end) { load_w(k0 + 64 * U, wA); load_x(k0 + 64 * U, xA); }
         if (k0 + 32 * U < k_end) {
-            if (k0 + 64 * U < k_end) load(k0 + 64 * U, wA, xA);
             compute(wB, xB);
+            if (k0 + 96 * U < k_end) { load_w(k0 + 96 * U, wB); load_x(k0 + 96 * U, xB); }
         }
     }
 
@@ -147,7 +160,7 @@ skinny_gemm_kernel(const SkinnyParams p) {
 template <int MT, int EPI, int U>
 int launch(const SkinnyParams& p, int splits, cudaStream_t s) {
     dim3 grid(ceil_div(p.N, 16), splits);
-    skinny_gemm_kernel<MT, EPI, U><<<grid, 128, 0, s>>>(p);
+    TTIE_LAUNCH((skinny_gemm_kernel<MT, EPI, U>), grid, 128, 0, s, p);
     TTIE_CHECK_LAUNCH("skinny_gemm");
     return 0;
 }

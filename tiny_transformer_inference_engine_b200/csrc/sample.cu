@@ -73,6 +73,7 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     __shared__ int s_found;
     __shared__ u64 s_scan[THREADS];
 
+    TTIE_PDL_ENTRY();
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* row = logits + (size_t)r * V;
     int* st = state + (size_t)slot_ids[r] * 8;
@@ -231,7 +232,7 @@ extern "C" int ttie_sample(const float* logits, int R, int V, const int* slot_id
                            float* probs_out, void* stream) {
     if (R <= 0) return 0;
     if (V <= 0) TTIE_FAIL("sample: empty vocabulary");
-    sample_kernel<<<R, THREADS, 0, (cudaStream_t)stream>>>(logits, V, slot_ids, state, out, probs_out);
+    TTIE_LAUNCH(sample_kernel, R, THREADS, 0, (cudaStream_t)stream, logits, V, slot_ids, state, out, probs_out);
     TTIE_CHECK_LAUNCH("sample");
     return 0;
 }
