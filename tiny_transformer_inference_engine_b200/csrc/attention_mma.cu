@@ -61,15 +61,18 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <int D, int NWARPS>
+// STAGES = 2: the next key/value tile is in flight while the current one is used (prompt portions: few,
+// long-running CTAs).  STAGES = 1: half the shared memory, so more CTAs of a decode step share an SM and
+// hide each other's load latency.
+template <int D, int NWARPS, int STAGES>
 __global__ void __launch_bounds__(NWARPS * 32)
 paged_attn_mma_kernel(const MmaParams p) {
     constexpr int BM = NWARPS * 16, LDS = D + 8, NT = NWARPS * 32, CH = D / 8;      // CH: 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                // [BM][LDS]
     __nv_bfloat16* Ks = Qs + BM * LDS;                                             // [2][BN][LDS]
-    __nv_bfloat16* Vs = Ks + 2 * BN * LDS;                                         // [2][BN][LDS]
-    long long* rowoff = reinterpret_cast<long long*>(Vs + 2 * BN * LDS);           // [2][BN] element offset of a key's row, -1: none
+    __nv_bfloat16* Vs = Ks + STAGES * BN * LDS;                                    // [STAGES][BN][LDS]
+    long long* rowoff = reinterpret_cast<long long*>(Vs + STAGES * BN * LDS);      // [STAGES][BN] element offset of a key's row, -1: none
     TTIE_PDL_ENTRY();
 
     const int G = p.Hq / p.Hkv;
@@ -163,12 +166,23 @@ paged_attn_mma_kernel(const MmaParams p) {
 
     unsigned qf[D / 16][4];
     for (int t = 0; t < ntiles; ++t) {
-        const int stage = t & 1, kt = k_lo + t * BN;
-        if (t + 1 < ntiles) fill_rowoff(stage ^ 1, kt + BN);
-        __syncthreads();                           // row offsets visible; everyone is done with the other stage
-        if (t + 1 < ntiles) issue_tile(stage ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
+        const int stage = STAGES == 2 ? (t & 1) : 0, kt = k_lo + t * BN;
+        if (STAGES == 2) {
+            if (t + 1 < ntiles) fill_rowoff(stage ^ 1, kt + BN);
+            __syncthreads();                       // row offsets visible; everyone is done with the other stage
+            if (t + 1 < ntiles) issue_tile(stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            if (t > 0) {
+                __syncthreads();                   // everyone is done with the previous tile
+                fill_rowoff(0, kt);
+                __syncthreads();
+                issue_tile(0);
+                cp_async_commit();
+            }
+            cp_async_wait<0>();
+        }
         __syncthreads();                           // tile t (and the queries) have landed for every thread
         if (t == 0) {
 #pragma unroll
@@ -489,9 +503,9 @@ int launch_decode(const MmaParams& p, cudaStream_t s) {
 
 template <int D, int NWARPS>
 int launch(const MmaParams& p, cudaStream_t s) {
-    constexpr int BM = NWARPS * 16, LDS = D + 8;
-    const size_t smem = ((size_t)BM * LDS + 4 * (size_t)BN * LDS) * sizeof(__nv_bfloat16) + 2 * BN * sizeof(long long);
-    auto k = paged_attn_mma_kernel<D, NWARPS>;
+    constexpr int BM = NWARPS * 16, LDS = D + 8, STAGES = NWARPS >= 4 ? 2 : 1;
+    const size_t smem = ((size_t)BM * LDS + 2 * STAGES * (size_t)BN * LDS) * sizeof(__nv_bfloat16) + STAGES * BN * sizeof(long long);
+    auto k = paged_attn_mma_kernel<D, NWARPS, STAGES>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) TTIE_FAIL("paged_attention_mma: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));

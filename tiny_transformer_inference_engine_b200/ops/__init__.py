@@ -85,7 +85,7 @@ class CudaOps:
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
         self.tc_used = False                  # a tcgen05 kernel ran since the error word was last read
-        self.attn_target_ctas = 2 * NUM_SMS
+        self.attn_target_ctas = 4 * NUM_SMS      # decode tiles are small: four CTAs share an SM
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
         self.lib.ttie_attn_tc_supported.restype = _c_int
@@ -300,7 +300,7 @@ class CudaOps:
         base = num_seqs * num_kv_heads * math.ceil(rows / tile_rows)
         if base >= NUM_SMS or max_kv_len <= min_len:
             return kernel, 1, 0
-        # as many splits as fit one wave of resident CTAs (two per SM), none shorter than min_len keys
+        # as many splits as fit one wave of resident CTAs, none shorter than min_len keys
         want = max(1, min(self.attn_target_ctas // base, math.ceil(max_kv_len / min_len)))
         split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
         num_splits = math.ceil(max_kv_len / split_len)

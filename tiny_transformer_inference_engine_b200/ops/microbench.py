@@ -113,7 +113,7 @@ def decode(ops, a):
     qsl = torch.arange(B + 1, dtype=torch.int32, device=DEV)
     sl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
     o = torch.empty(B, Hq * D, device=DEV, dtype=torch.bfloat16)
-    plan = ops.attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx)
+    plan = ops.attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx, page)
     line(f"paged attention {plan} + merge", timeit(lambda i: ops.paged_attention(q, Hq, Hkv, D, kp, vp, table, page, qsl, sl, B, 1, ctx, 1 / math.sqrt(D), 0, o)),
          bytes_=B * ctx * Hkv * D * 2 * 2)
     logits = torch.randn(B, V, device=DEV)
@@ -148,7 +148,7 @@ def prefill(ops, a):
     qsl = torch.tensor([0, T], dtype=torch.int32, device=DEV)
     sl = torch.tensor([T], dtype=torch.int32, device=DEV)
     o = torch.empty(T, Hq * D, device=DEV, dtype=torch.bfloat16)
-    plan = ops.attention_plan(torch.bfloat16, 1, Hq, Hkv, D, T, T)
+    plan = ops.attention_plan(torch.bfloat16, 1, Hq, Hkv, D, T, T, page)
     line(f"causal paged attention {plan}", timeit(lambda i: ops.paged_attention(qkv, Hq, Hkv, D, kp, vp, table, page, qsl, sl, 1, T, T, 1 / math.sqrt(D), 0, o), iters=4),
          flops=4 * Hq * D * T * (T + 1) // 2)
 
