@@ -37,3 +37,30 @@ def test_layer_sizes(dtype, mode):
     bad = tu.first_wrong(got, exp, TOL[dtype])
     worst, where = tu.worst_relative(got, exp)
     assert bad is None, f"first wrong place {bad}; worst {worst} at {where}"
+
+
+OTHER = {
+    # Falcon-7B widths in Llama style: 71 heads (no power of two) of 64, width 4544, vocabulary 65024
+    "falcon": dict(architecture="mqa_gpt", vocab_size=65024, d_model=4544, num_layers=1, num_heads=71, num_kv_heads=1,
+                   hidden_size=18176, max_seq_len=256, rope_theta=10000.0, rms_norm_eps=1e-5, bias=False, eos_token_id=None),
+    # Gemma-2B sizes: 8 heads of 256, width 2048, vocabulary 256000
+    "gemma": dict(architecture="mqa_gpt", vocab_size=256000, d_model=2048, num_layers=1, num_heads=8, num_kv_heads=1,
+                  hidden_size=16384, max_seq_len=256, rope_theta=10000.0, rms_norm_eps=1e-6, bias=False, eos_token_id=None),
+}
+
+
+@pytest.mark.parametrize("name", list(OTHER))
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_other_layer_sizes(name, dtype):
+    """One layer at the Falcon-7B and Gemma-2B layer sizes: a prompt in portions, then decoded tokens."""
+    cfg = OTHER[name]
+    w = random_tensors(ModelConfig.from_dict(cfg), 3, perturb_norms=True)
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(0, cfg["vocab_size"], (90,), generator=g).tolist()
+    exp = {"a": plain_forward(cfg, w, toks)}
+    steps = [{"entries": [{"id": "a", "tokens": toks[:70], "want": [0, 33, 69]}], "end": []}]
+    steps += [{"entries": [{"id": "a", "tokens": toks[i:i + 1], "want": [0]}], "end": ["a"] if i == 89 else []} for i in range(70, 90)]
+    eng, _ = make_engine(cfg, 3, 16, 8, dtype, weights=w, budget=128)
+    got = tu.run_steps(eng, steps)
+    bad = tu.first_wrong(got, exp, TOL[dtype])
+    assert bad is None, f"first wrong place {bad}"

@@ -166,10 +166,10 @@ int launch(const SkinnyParams& p, int splits, cudaStream_t s) {
 }
 
 template <int EPI>
-int dispatch(const SkinnyParams& p, int splits, cudaStream_t s) {
+int dispatch(const SkinnyParams& p, int splits, int unroll, cudaStream_t s) {
     const int mt = ceil_div(p.M, 8);
-    // long K ranges per warp stream best with deep unrolling, short ones with more CTAs per SM
-    const bool deep = EPI != 2 && p.kslice / 4 >= 512;
+    // a product that is not split over CTAs streams best with deep unrolling, a split one with more CTAs per SM
+    const bool deep = EPI != 2 && (unroll ? unroll >= 4 : splits == 1);
     if (mt <= 1) return deep ? launch<1, EPI, 4>(p, splits, s) : launch<1, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
     if (mt <= 2) return launch<2, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
     if (mt <= 4) return launch<4, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
@@ -182,8 +182,17 @@ extern "C" int ttie_skinny_max_rows() { return 64; }
 // epilogue: 0 bfloat16 out, 1 float32 partial sums [splits][M][N], 2 SwiGLU (w holds gate rows then up
 // rows, N = F), 3 float32 out.  kslice: K range per CTA, a multiple of 128; splits = ceil(K / kslice),
 // which must be 1 unless epilogue is 1.
+extern "C" int ttie_skinny_gemm_tuned(const void* x, long long ldx, const void* w, long long ldw, const void* bias, void* out,
+                                      long long ldo, int M, int N, int K, int kslice, int epilogue, int up_offset, int unroll,
+                                      void* stream);
 extern "C" int ttie_skinny_gemm(const void* x, long long ldx, const void* w, long long ldw, const void* bias, void* out,
                                 long long ldo, int M, int N, int K, int kslice, int epilogue, int up_offset, void* stream) {
+    return ttie_skinny_gemm_tuned(x, ldx, w, ldw, bias, out, ldo, M, N, K, kslice, epilogue, up_offset, 0, stream);
+}
+// unroll: 0 = chosen from kslice; 2 or 4 = 32-key blocks per register buffer (rows <= 8 only).
+extern "C" int ttie_skinny_gemm_tuned(const void* x, long long ldx, const void* w, long long ldw, const void* bias, void* out,
+                                      long long ldo, int M, int N, int K, int kslice, int epilogue, int up_offset, int unroll,
+                                      void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64) TTIE_FAIL("skinny_gemm: %d rows; this kernel takes at most 64", M);
     if (K <= 0 || K % 8) TTIE_FAIL("skinny_gemm: K=%d must be a positive multiple of 8", K);
@@ -199,10 +208,10 @@ extern "C" int ttie_skinny_gemm(const void* x, long long ldx, const void* w, lon
     p.kslice = kslice; p.up_offset = up_offset;
     cudaStream_t s = (cudaStream_t)stream;
     switch (epilogue) {
-        case 0: return dispatch<0>(p, splits, s);
-        case 1: return dispatch<1>(p, splits, s);
-        case 2: return dispatch<2>(p, splits, s);
-        case 3: return dispatch<3>(p, splits, s);
+        case 0: return dispatch<0>(p, splits, unroll, s);
+        case 1: return dispatch<1>(p, splits, unroll, s);
+        case 2: return dispatch<2>(p, splits, unroll, s);
+        case 3: return dispatch<3>(p, splits, unroll, s);
     }
     TTIE_FAIL("skinny_gemm: unknown epilogue %d", epilogue);
 }
