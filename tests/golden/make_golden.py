@@ -2,7 +2,7 @@
 (models/transformer_block.py ``Transformer``, pytorch backend, float32, CPU) on tiny random
 models, for the plain implementation to be compared with once.
 
-Run from the repository root:  python tests/golden/make_golden.py [/path/to/reference]
+Run from the repository root:  python tests/golden/make_golden.py /path/to/reference/checkout
 
 The reference's CUDA extension modules cannot be imported here (they are built for
 another Python and GPU), so six empty stand-in modules are put into ``sys.modules``;
@@ -64,7 +64,9 @@ def reference_logits(ref_path, cfg, weights, prompts, chunked=None):
 
 
 def main():
-    ref_path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference/checkout")
+    ref_path = sys.argv[1]
     from tiny_configs import TINY_A, TINY_B, SEEDS
     from tiny_transformer_inference_engine_b200.config import ModelConfig
     from tiny_transformer_inference_engine_b200.weights import random_tensors
