@@ -131,9 +131,12 @@ class CacheManager:
         plan = []
         for g in self.groups:
             table = g.tables[rid]
+            last = pages_for(new_len, g.page_size)
+            if g.window is None:                               # nothing is ever given back early: only growth
+                plan.append(([], list(range(len(table), last)), last))
+                continue
             first = g.first_needed_page(start)
             to_free = [(i, p) for i, p in enumerate(table[:first]) if p != 0]
-            last = pages_for(new_len, g.page_size)
             to_fill = [i for i in range(first, last) if i >= len(table) or table[i] == 0]
             plan.append((to_free, to_fill, last))
         return plan

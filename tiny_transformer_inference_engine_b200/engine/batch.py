@@ -63,27 +63,29 @@ class BatchPacker:
             if en.start < 0 or en.start + n > self.max_seq_len:
                 raise ValueError(f"request {en.rid!r}: positions {en.start}..{en.start + n - 1} exceed "
                                  f"max_seq_len={self.max_seq_len}")
-            for t in en.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise ValueError(f"request {en.rid!r}: token id {t} outside [0, {self.vocab_size})")
-            for w in en.want:
-                if not 0 <= int(w) < n:
-                    raise ValueError(f"request {en.rid!r}: wanted place {w} outside its {n} tokens")
+            if min(en.tokens) < 0 or max(en.tokens) >= self.vocab_size:
+                bad = [t for t in en.tokens if not 0 <= int(t) < self.vocab_size]
+                raise ValueError(f"request {en.rid!r}: token id {bad[0]} outside [0, {self.vocab_size})")
+            if en.want and (min(en.want) < 0 or max(en.want) >= n):
+                bad = [w for w in en.want if not 0 <= int(w) < n]
+                raise ValueError(f"request {en.rid!r}: wanted place {bad[0]} outside its {n} tokens")
             for gi, g in enumerate(self.manager.groups):
                 table = g.tables.get(en.rid)
                 if table is None:
                     raise KeyError(f"request {en.rid!r} is not admitted")
                 first = g.first_needed_page(en.start)
                 last = -(-(en.start + n) // g.page_size)
-                if len(table) < last or any(p <= 0 or p >= g.num_pages for p in table[first:last]):
+                span = table[first:last]
+                if len(table) < last or (span and (min(span) <= 0 or max(span) >= g.num_pages)):
                     raise ValueError(f"request {en.rid!r}: block table of group {gi} does not cover "
                                      f"positions {en.start}..{en.start + n - 1}")
 
     def pack(self, entries: List[StepEntry], pad_seqs: int = 0, pages_per_seq: Optional[Dict[int, int]] = None,
-             buffers=None) -> StepContext:
+             buffers=None, copy_only: bool = False) -> Optional[StepContext]:
         """``pad_seqs``/``pages_per_seq``/``buffers`` give a fixed layout (for a captured
         graph): the batch is padded to ``pad_seqs`` one-token requests that sit on the
-        scratch page with length 1, and the tables get ``pages_per_seq[group]`` columns."""
+        scratch page with length 1, and the tables get ``pages_per_seq[group]`` columns.
+        ``copy_only``: fill and copy the buffer but build no context (a graph replay needs none)."""
         self.validate(entries)
         mgr = self.manager
         N_real = len(entries)
@@ -111,11 +113,7 @@ class BatchPacker:
                 if width > pages_per_seq[gi]:
                     raise ValueError("block table wider than the fixed layout")
                 width = pages_per_seq[gi]
-            arr = np.zeros((N, width), dtype=np.int32)
-            for i, en in enumerate(entries):
-                t = g.tables[en.rid]
-                arr[i, :len(t)] = t
-            tables.append(arr)
+            tables.append([g.tables[en.rid] for en in entries])
             widths.append(width)
 
         sizes = [T, T, T, N + 1, N, N, max(R, 1)] + [N * w for w in widths]
@@ -135,13 +133,18 @@ class BatchPacker:
         hn = host.numpy()
         for off, data in zip(offs[:7], (tok, pos, tseq, qsl, seql, slots, rows)):
             hn[off:off + len(data)] = data
-        for off, arr in zip(offs[7:], tables):
-            hn[off:off + arr.size] = arr.reshape(-1)
+        for off, rows_, w in zip(offs[7:], tables, widths):
+            block = hn[off:off + N * w].reshape(N, w)
+            block[:] = 0
+            for i, t in enumerate(rows_):
+                block[i, :len(t)] = t
         dev[:total].copy_(host[:total], non_blocking=True)
         if self.device.type == "cuda":
             if self._copied is None:
                 self._copied = torch.cuda.Event()
             self._copied.record()
+        if copy_only:
+            return None
 
         def view(k, n):
             return dev[offs[k]:offs[k] + n]

@@ -67,6 +67,8 @@ def run(engine, lines, out_dir: str, log=sys.stdout) -> None:
         entries = []
         for en in rec.get("entries", []):
             rid, tokens = en["id"], list(en["tokens"])
+            if not tokens:                                     # nothing to run for this request in this step
+                continue
             if rid not in lengths:
                 mgr.admit(rid)
                 lengths[rid] = 0

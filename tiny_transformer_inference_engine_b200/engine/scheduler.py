@@ -51,8 +51,21 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.num_cached
+
+    def span(self, start: int, n: int) -> List[int]:
+        """Tokens start..start+n-1 of prompt + output, without building the whole list."""
+        p = len(self.prompt)
+        if start >= p:
+            return self.output[start - p:start - p + n]
+        if start + n <= p:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.output[:start + n - p]
 
 
 class Scheduler:
@@ -131,7 +144,7 @@ class Scheduler:
     def _admit_ok(self, req: Request) -> bool:
         if not self.manager.can_admit() or len(self.running) >= self.config.max_num_seqs:
             return False
-        need = pages_for(len(req.tokens), self.manager.page_size)
+        need = pages_for(req.num_tokens, self.manager.page_size)
         # serving/scheduler.py:33-37: keep one growth page for every running request and this one
         return self.manager.num_free_pages - need >= len(self.running) + 1 or not self.running
 
@@ -186,7 +199,7 @@ class Scheduler:
             n = planned.get(req.rid)
             if not n:
                 continue
-            toks = req.tokens[req.num_cached:req.num_cached + n]
+            toks = req.span(req.num_cached, n)
             want = [n - 1] if n == req.remaining else []
             entries.append(StepEntry(req.rid, req.num_cached, toks, want))
         return entries

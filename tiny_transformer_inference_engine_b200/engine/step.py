@@ -83,7 +83,7 @@ class Stepper:
                 logits = self.model.forward(ctx, views)
             g = _DecodeGraph(bucket, host, dev, graph, logits, ctx, getattr(self.ops, "launches", 0) - before)
             self._graphs[bucket] = g
-        self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(g.host, g.dev))
+        self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(g.host, g.dev), copy_only=True)
         g.graph.replay()
         if hasattr(self.ops, "launches"):
             self.ops.launches += g.launches
