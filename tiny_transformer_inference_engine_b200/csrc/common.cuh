@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <cstdlib>
 
 namespace ttie {
 
@@ -62,18 +63,32 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // kernels here call it first thing, so only launch latency and CTA scheduling overlap).  Works inside
 // captured graphs.  ttie_set_pdl(0) turns it off.
 bool pdl_enabled();
+// cluster_x > 1: consecutive CTAs along x form a thread-block cluster (the grid's x must be a multiple).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster_x,
+                                 Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    // (a cluster launch does not take the attribute: as a programmatic dependent it was measured to start late)
+    if (pdl_enabled() && cluster_x <= 1) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster_x; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr; cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #define TTIE_LAUNCH(kernel, grid, block, smem, stream, ...) \
-    ::ttie::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
+    ::ttie::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, 1, __VA_ARGS__)
+#define TTIE_LAUNCH_CLUSTER(kernel, grid, block, smem, stream, cluster_x, ...) \
+    ::ttie::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, cluster_x, __VA_ARGS__)
 
 
 }  // namespace ttie

@@ -154,12 +154,92 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, c
     }
 }
 
+// Few rows (a decode step): a row is shared by a cluster of C CTAs, so C times as many SMs pull the row
+// and its partial sums, and each thread has all its loads in flight at once.  The CTAs exchange their
+// shares of the sum of squares through distributed shared memory and add them in rank order, so every
+// CTA of the cluster holds the same sum.  The norm weights do not depend on the kernel before this one
+// and are loaded ahead of the wait for it.
+template <typename T, typename W, int NT, int MAXC, int C>
+__global__ void __launch_bounds__(NT)
+add_rmsnorm_cluster_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart,
+                           int S, long long part_stride, const int* __restrict__ rows,
+                           const W* __restrict__ weight, T* __restrict__ out, int d, float eps) {
+    __shared__ float scratch[32];
+    __shared__ float share;                                         // this CTA's part of the sum of squares
+    const int r = blockIdx.x / C, rank = blockIdx.x - r * C;        // clusters are consecutive CTAs along x
+    const int nchunk = d >> 2, per = (nchunk + C - 1) / C;
+    const int c_begin = rank * per, c_end = min(nchunk, c_begin + per);
+    float4 w[MAXC];
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+        const int ch = c_begin + threadIdx.x + c * NT;
+        if (ch < c_end) w[c] = Vec4<W>::load(weight + ch * 4);
+    }
+    TTIE_PDL_ENTRY();
+    const size_t src = (size_t)(rows ? rows[r] : r) * d;
+    float4 v[MAXC];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+        const int ch = c_begin + threadIdx.x + c * NT;
+        if (ch < c_end) {
+            const int i = ch * 4;
+            float4 a = *reinterpret_cast<const float4*>(resid + src + i);
+            if (delta) { const float4 b = Vec4<T>::load(delta + src + i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+            if (dpart) {
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s0 = 0; s0 < S; s0 += 4) {                 // four loads in flight, added in the order s = 0..S-1
+                    float4 b[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (s0 + k < S) b[k] = *reinterpret_cast<const float4*>(dpart + (s0 + k) * part_stride + src + i);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (s0 + k < S) { t.x += b[k].x; t.y += b[k].y; t.z += b[k].z; t.w += b[k].w; }
+                }
+                a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+            }
+            if (!rows && (delta || dpart)) *reinterpret_cast<float4*>(resid + src + i) = a;
+            v[c] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    if (threadIdx.x == 0) share = ss;
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < C; ++k) {
+        uint32_t remote;
+        float part;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(&share)), "r"(k));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(remote) : "memory");
+        total += part;
+    }
+    const float inv = rsqrtf(total / (float)d + eps);
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+        const int ch = c_begin + threadIdx.x + c * NT;
+        if (ch < c_end)
+            Vec4<T>::store(out + (size_t)r * d + ch * 4, make_float4(v[c].x * inv * w[c].x, v[c].y * inv * w[c].y, v[c].z * inv * w[c].z, v[c].w * inv * w[c].w));
+    }
+    // no CTA may leave while another still reads its share
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 template <typename T>
 static int launch_rmsnorm(float* resid, const void* delta, const float* dpart, int S, long long part_stride,
                           const int* rows, const void* weight, int w_dtype, void* out,
                           int R, int d, float eps, cudaStream_t s) {
     const bool aligned = !(((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)dpart | (uintptr_t)weight | (uintptr_t)out) & 15)
                          && (part_stride % 4 == 0);
+    if (d % 4 == 0 && d <= 8192 && d >= 1024 && aligned && R <= 32 && (w_dtype == kF32 || w_dtype == kBF16)) {
+        constexpr int C = 4;                                        // (d / 4) chunks over 4 CTAs of 256 threads, 2 chunks each at most
+        if (w_dtype == kF32) TTIE_LAUNCH_CLUSTER((add_rmsnorm_cluster_kernel<T, float, 256, 2, C>), R * C, 256, 0, s, C, resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
+        else TTIE_LAUNCH_CLUSTER((add_rmsnorm_cluster_kernel<T, __nv_bfloat16, 256, 2, C>), R * C, 256, 0, s, C, resid, (const T*)delta, dpart, S, part_stride, rows, (const __nv_bfloat16*)weight, (T*)out, d, eps);
+        TTIE_CHECK_LAUNCH("rmsnorm (cluster)");
+        return 0;
+    }
     if (d % 4 == 0 && d <= 8192 && aligned) {
         if (w_dtype == kF32) {
             if (d <= 2048) TTIE_LAUNCH((add_rmsnorm_vec_kernel<T, float, 128, 4>), R, 128, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows, (const float*)weight, (T*)out, d, eps);
@@ -430,11 +510,12 @@ extern "C" int ttie_rope_table(const int* positions, const float* inv_freq, void
     return 0;
 }
 
-// Interleaved pairs, four values per thread, no shared memory: the input row is either the
-// packed q/k/v row in the compute dtype (then q and k are also written back in place) or float32
-// partial sums [S][T][width].  cos/sin come from the step's table.
+// Interleaved pairs, four values per thread (grid: tokens x pieces of 128 threads), no shared memory: the
+// input row is either the packed q/k/v row in the compute dtype (then q and k are also written back in
+// place) or float32 partial sums [S][T][width], of which a thread has up to four loads in flight.
+// cos/sin come from the step's table.
 template <typename T, bool PARTIAL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 rope_store_vec_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ part, int S, long long part_stride,
                       int Hq, int Hkv, int D, const int* __restrict__ positions, const int* __restrict__ token_seq,
                       const float2* __restrict__ cs, T* __restrict__ q_out, long long q_stride,
@@ -443,40 +524,43 @@ rope_store_vec_kernel(T* __restrict__ qkv, long long row_stride, const float* __
     TTIE_PDL_ENTRY();
     const int t = blockIdx.x;
     const int width = (Hq + 2 * Hkv) * D, half = D >> 1;
-    const int pos = positions[t];
-    long long page_base = 0;
-    if (write_kv && Hkv > 0) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= (width >> 2)) return;
+    const int col = c << 2;
+    const int h = col / D, i = col - h * D;
+    float4 v;
+    if (PARTIAL) {
+        v = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* src = part + (long long)t * width + col;
+        for (int s0 = 0; s0 < S; s0 += 4) {                         // added in the order s = 0..S-1
+            float4 b[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (s0 + k < S) b[k] = *reinterpret_cast<const float4*>(src + (s0 + k) * part_stride);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (s0 + k < S) { v.x += b[k].x; v.y += b[k].y; v.z += b[k].z; v.w += b[k].w; }
+        }
+    } else {
+        v = Vec4<T>::load(qkv + (long long)t * row_stride + col);
+    }
+    if (h < Hq + Hkv && cs) {
+        const float4 t2 = *reinterpret_cast<const float4*>(cs + (size_t)t * half + (i >> 1));   // cos0 sin0 cos1 sin1
+        v = make_float4(v.x * t2.x - v.y * t2.y, v.x * t2.y + v.y * t2.x, v.z * t2.z - v.w * t2.w, v.z * t2.w + v.w * t2.z);
+    }
+    if (h < Hq) {
+        Vec4<T>::store(q_out + (long long)t * q_stride + col, v);
+        return;
+    }
+    if (!PARTIAL && h < Hq + Hkv) Vec4<T>::store(qkv + (long long)t * row_stride + col, v);
+    if (write_kv) {
+        const int pos = positions[t];
         int page = block_table[(size_t)token_seq[t] * table_width + pos / page_size];
         if (page < 0 || page >= num_pages) page = 0;
-        page_base = (long long)page * Hkv * page_size + pos % page_size;      // + h * page_size, all times D
-    }
-    for (int c = threadIdx.x; c < (width >> 2); c += blockDim.x) {
-        const int col = c << 2;
-        const int h = col / D, i = col - h * D;
-        float4 v;
-        if (PARTIAL) {
-            v = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int sp = 0; sp < S; ++sp) {
-                const float4 b = *reinterpret_cast<const float4*>(part + sp * part_stride + (long long)t * width + col);
-                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-            }
-        } else {
-            v = Vec4<T>::load(qkv + (long long)t * row_stride + col);
-        }
-        if (h < Hq + Hkv && cs) {
-            const float4 t2 = *reinterpret_cast<const float4*>(cs + (size_t)t * half + (i >> 1));   // cos0 sin0 cos1 sin1
-            v = make_float4(v.x * t2.x - v.y * t2.y, v.x * t2.y + v.y * t2.x, v.z * t2.z - v.w * t2.w, v.z * t2.w + v.w * t2.z);
-        }
-        if (h < Hq) {
-            Vec4<T>::store(q_out + (long long)t * q_stride + col, v);
-        } else {
-            if (!PARTIAL && h < Hq + Hkv) Vec4<T>::store(qkv + (long long)t * row_stride + col, v);
-            if (write_kv) {
-                const int hk = h < Hq + Hkv ? h - Hq : h - Hq - Hkv;
-                T* dst = (h < Hq + Hkv ? k_pages : v_pages) + (page_base + (long long)hk * page_size) * D + i;
-                Vec4<T>::store(dst, v);
-            }
-        }
+        const long long page_base = (long long)page * Hkv * page_size + pos % page_size;      // + h * page_size, all times D
+        const int hk = h < Hq + Hkv ? h - Hq : h - Hq - Hkv;
+        T* dst = (h < Hq + Hkv ? k_pages : v_pages) + (page_base + (long long)hk * page_size) * D + i;
+        Vec4<T>::store(dst, v);
     }
 }
 
@@ -494,7 +578,7 @@ extern "C" int ttie_rope_store_vec(void* qkv, long long row_stride, const float*
         TTIE_FAIL("rope_store_vec: pointers must be 16-byte aligned");
     if (row_stride % 4 || q_stride % 4 || part_stride % 4) TTIE_FAIL("rope_store_vec: strides must be multiples of 4");
     cudaStream_t s = (cudaStream_t)stream;
-#define TTIE_ROPE_VEC(TT, P) TTIE_LAUNCH((rope_store_vec_kernel<TT, P>), T, 256, 0, s, (TT*)qkv, row_stride, part, S, part_stride, Hq, Hkv, D, \
+#define TTIE_ROPE_VEC(TT, P) TTIE_LAUNCH((rope_store_vec_kernel<TT, P>), dim3(T, ceil_div((Hq + 2 * Hkv) * D / 4, 128)), 128, 0, s, (TT*)qkv, row_stride, part, S, part_stride, Hq, Hkv, D, \
         positions, token_seq, (const float2*)cs, (TT*)q_out, q_stride, (TT*)k_pages, (TT*)v_pages, block_table, table_width, \
         page_size, num_pages, write_kv)
     if (dtype == kF32) { if (part) TTIE_ROPE_VEC(float, true); else TTIE_ROPE_VEC(float, false); }

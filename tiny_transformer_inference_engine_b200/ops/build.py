@@ -21,7 +21,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_NAME = "_ttie_b200.so"
 
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-              "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+              "-Xcompiler", "-fPIC", "-Xptxas", "-v"] + os.environ.get("TTIE_NVCC_EXTRA", "").split()
 
 
 def _nvcc() -> str:
