@@ -422,26 +422,49 @@ def test_partial_sums_feed_norm_and_rope(ops):
     assert rel(kp.float().cpu(), kp2) < 8e-3 and rel(vp.float().cpu(), vp2) < 8e-3
 
 
+def cluster_plan(ops, groups, cluster, max_kv, D, max_q, Hq, Hkv):
+    C = cluster
+    while C > 1 and ops.lib.ttie_attn_cluster_active(D, max_q, Hq, Hkv, groups, C) < 1:
+        C //= 2
+    assert ops.lib.ttie_attn_cluster_active(D, max_q, Hq, Hkv, groups, C) >= 1
+    return (f"mma_c{groups}", C, -(-(-(-max_kv // C)) // 64) * 64)
+
+
 @pytest.mark.parametrize("Hq,Hkv,D,page", [(32, 1, 128, 64), (71, 1, 64, 16), (6, 2, 48, 32), (3, 1, 32, 8), (4, 4, 16, 5), (128, 1, 64, 64)])
-@pytest.mark.parametrize("seqs", [[(200, 1), (64, 1), (65, 1), (1, 1), (513, 1)], [(130, 2), (128, 1), (129, 1)], [(4096, 1)] * 2])
-def test_decode_form_attention(ops, Hq, Hkv, D, page, seqs):
-    max_kv = max(L for L, _ in seqs)
-    n = -(-max_kv // 128)
-    plan = ("mma_decode", n, 128) if n > 1 else ("mma_decode", 1, 0)
-    if max(q for _, q in seqs) * (Hq // Hkv) > 128:
-        pytest.skip("more query rows than the decode form takes")
+@pytest.mark.parametrize("seqs", [[(200, 1), (64, 1), (65, 1), (1, 1), (513, 1)], [(130, 2), (128, 1), (129, 1)], [(4096, 1)] * 2,
+                                  [(700, 5), (3, 3), (1100, 1)]])
+@pytest.mark.parametrize("groups,cluster", [(4, 16), (4, 4), (2, 8), (2, 1), (4, 1), (2, 2)])
+def test_decode_form_attention(ops, Hq, Hkv, D, page, seqs, groups, cluster):
+    """One cluster per (request, kv head, row tile): every cluster size, both numbers of key groups, requests
+    far shorter than the longest (CTAs and groups without keys), several row tiles, a window."""
+    max_kv, max_q = max(L for L, _ in seqs), max(q for _, q in seqs)
+    plan = cluster_plan(ops, groups, cluster, max_kv, D, max_q, Hq, Hkv)
     out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=plan)
     assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
     out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=plan, window=70)
     assert rel(out, exp) < TOL["bfloat16"]
 
 
-@pytest.mark.parametrize("kpos", [0, 127, 128, 447, 599])
-def test_decode_form_one_key_decides(ops, kpos):
+@pytest.mark.parametrize("kpos", [0, 63, 64, 127, 128, 447, 599])
+@pytest.mark.parametrize("groups,cluster", [(4, 4), (2, 16)])
+def test_decode_form_one_key_decides(ops, kpos, groups, cluster):
     seqs = [(50, 1), (600, 1), (64, 1)]
-    out, exp, dense, qsl = attention_case(ops, "bfloat16", 4, 1, 64, 64, seqs, plan=("mma_decode", 5, 128), spike=(1, 0, kpos))
+    plan = cluster_plan(ops, groups, cluster, 600, 64, 1, 4, 1)
+    out, exp, dense, qsl = attention_case(ops, "bfloat16", 4, 1, 64, 64, seqs, plan=plan, spike=(1, 0, kpos))
     assert (out[qsl[1]].view(4, 64) - dense[1][1][kpos, 0]).abs().max() < 2e-2
     assert rel(out, exp) < TOL["bfloat16"]
+
+
+def test_decode_form_is_planned(ops):
+    """Decode steps of the bfloat16 path take the decode form while a warp has one key tile to walk; longer
+    contexts take the tile loop with splits, prompt portions the tcgen05 kernel or the tile loop."""
+    kernel, C, split_len = ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 2048, 64)
+    assert kernel == "mma_c4" and C * split_len >= 2048 and C & (C - 1) == 0 and split_len <= 256
+    assert ops.attention_plan(torch.bfloat16, 3, 4, 2, 64, 1, 100, 16)[0] == "mma_c2"
+    assert ops.attention_plan(torch.bfloat16, 64, 32, 1, 128, 1, 256, 64) == ("mma_c4", 1, 256)
+    assert ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 32768, 64)[0] == "mma"
+    assert ops.attention_plan(torch.bfloat16, 1, 32, 1, 128, 2048, 2048, 64)[0] == "tc"
+    assert ops.attention_plan(torch.bfloat16, 2, 8, 2, 48, 200, 200, 16)[0] == "mma"
 
 
 # ------------------------------------------------------------------------------------------ tcgen05 product

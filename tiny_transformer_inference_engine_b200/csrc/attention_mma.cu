@@ -56,6 +56,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (ex2(-inf) = 0); exp2f() wraps the same instruction in range handling
+__device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -215,7 +217,7 @@ paged_attn_mma_kernel(const MmaParams p) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int h = e >> 1;
-                    float v = s[i][e] * p.scale_log2;
+                    float v = s[i][e];                                 // raw scores; the scale (positive) goes into the exponent's fma
                     if (!full) {
                         const int key = kt + i * 8 + 2 * (lane & 3) + (e & 1);
                         if (!(rvalid[h] && key <= rpos[h] && key >= rlo[h] && key < k_hi)) v = -INFINITY;
@@ -228,9 +230,9 @@ paged_attn_mma_kernel(const MmaParams p) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2)) * p.scale_log2;
                 const float m_new = fmaxf(m_run[h], mx[h]);
-                alpha[h] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[h] - m_new);
+                alpha[h] = (m_new == -INFINITY) ? 1.f : ex2(m_run[h] - m_new);
                 m_run[h] = m_new;
                 l_run[h] *= alpha[h];
             }
@@ -239,7 +241,7 @@ paged_attn_mma_kernel(const MmaParams p) {
             for (int i = 0; i < BN / 8; ++i) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = exp2f(s[i][e] - msub[e >> 1]);           // exp2(-inf) = 0 for masked keys
+                    const float pv = ex2(fmaf(s[i][e], p.scale_log2, -msub[e >> 1]));           // exp2(-inf) = 0 for masked keys
                     s[i][e] = pv;
                     l_run[e >> 1] += pv;
                 }
@@ -297,132 +299,250 @@ paged_attn_mma_kernel(const MmaParams p) {
 
 // ------------------------------------------------------------------------------------------ decode form
 // Few query rows per request (one decoded token times the heads of a kv head's group, or a short
-// portion): there is too little work per key tile for the tile loop above to hide latency, so the
-// key range is cut finer.  A CTA takes DEC_KEYS keys of one (request, kv head); each of its four
-// warps loads its own 32 keys (cp.async, no CTA-wide barrier) and computes all query rows against
-// them, 16 rows at a time; the four partial results of a 16-row tile are merged in shared memory
-// and leave as one partial result per CTA (or as the final output if the request has one split).
-constexpr int DEC_WARPS = 4, DEC_WKEYS = 32, DEC_KEYS = DEC_WARPS * DEC_WKEYS, DEC_MAX_ROWS = 128;
+// portion).  A thread-block cluster takes one (request, kv head, row tile): its C CTAs cut the key range
+// into C pieces, and inside a CTA KG groups of RW warps walk their piece in 64-key tiles, group g taking
+// tiles g, g + KG, ...  A group loads its own tile (cp.async) and synchronises only with itself (a named
+// barrier), so one group's loads run under another's products.  At the end the groups' partial results
+// are merged in shared memory, then the C CTAs' results through distributed shared memory: CTA r reads
+// rows r, r + C, ... of every CTA, adds them in rank order and writes the output.  No scratch in global
+// memory and no second kernel.
+constexpr int CL_MAX_ROWS = 32;
 
-template <int D>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
-paged_attn_decode_kernel(const MmaParams p) {
-    constexpr int LDS = D + 8, CH = D / 8, NT = DEC_WARPS * 32;
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned cluster_size() { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned map_to_rank(const void* local, unsigned rank) {
+    unsigned remote;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
+    return remote;
+}
+#ifdef TTIE_PROFILE_DEC
+__device__ long long g_dec_prof[32];
+#define DPROF(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_dec_prof[i] = clock64(); } while (0)
+#else
+#define DPROF(i) do {} while (0)
+#endif
+__device__ __forceinline__ void st_cluster_f32x4(unsigned addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32x2(unsigned addr, float2 v) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+// bytes of the key/value tiles and their row offsets (the area that later holds the groups' partial results)
+template <int D, int RW, int KG>
+__host__ __device__ constexpr size_t cluster_tile_bytes() {
+    constexpr size_t tiles = (size_t)KG * 2 * BN * (D + 8) * 2;
+    constexpr size_t part = (size_t)KG * RW * 16 * (D + 8 + 2) * 4;
+    return ((tiles > part ? tiles : part) + 15) / 16 * 16;
+}
+template <int D, int RW, int KG>
+__global__ void __launch_bounds__(RW * KG * 32)
+paged_attn_cluster_kernel(const MmaParams p) {
+    constexpr int BM = RW * 16, LDS = D + 8, CH = D / 8, NT = RW * KG * 32, GT = RW * 32;     // GT: threads of a key group
+    constexpr int LDO = D + 8;                                                     // float row stride of the exchange buffers (no bank conflicts)
+    constexpr int NI = BN * CH / GT;                                               // 16-byte pieces of a tile per thread
+    static_assert(BN == 64 && (BN * CH) % GT == 0, "a lane holds the row offsets of keys lane and lane + 32");
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(smem_raw);                // [KG][2][BN][LDS]
+    // after the key loop the tile area holds the partial results
+    float* Op = reinterpret_cast<float*>(KV);                                      // [KG][BM][LDO]
+    float* MLp = Op + KG * BM * LDO;                                               // [KG][BM][2]
+    // Rows that the other CTAs of the cluster send here (never aliased: they may arrive while this CTA still
+    // works on its tiles): slot = sender's rank * rows per owner + local row
+    float* Recv = reinterpret_cast<float*>(smem_raw + cluster_tile_bytes<D, RW, KG>());   // [BM + 16][LDO]
+    float* MLrecv = Recv + (BM + 16) * LDO;                                        // [BM + 16][2]
+    DPROF(0);
+    TTIE_PDL_ENTRY();
+    DPROF(1);
+
     const int G = p.Hq / p.Hkv;
-    const int kvh = blockIdx.x % p.Hkv, seq = blockIdx.x / p.Hkv, split = blockIdx.y;
+    int tile = blockIdx.x;
+    const int rt = tile % p.row_tiles;
+    tile /= p.row_tiles;
+    const int kvh = tile % p.Hkv, seq = tile / p.Hkv;
+    const unsigned rank = cluster_rank(), C = cluster_size();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kg = warp / RW, rw = warp - kg * RW, gtid = tid - kg * GT;
+    const int* table = p.block_table + (size_t)seq * p.table_width;
+    // Without a window the first tile of this group is known before the request's lengths are: its page
+    // numbers are asked for together with the lengths (one memory latency instead of two).
+    const int kt_guess = (int)rank * p.split_len + kg * BN;
+    int page_guess[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int pg = (kt_guess + lane + 32 * i) / p.page_size;
+        page_guess[i] = pg < p.table_width ? table[pg] : 0;
+    }
     const int q0 = p.qsl[seq], q_len = p.qsl[seq + 1] - q0, kv_len = p.seq_lens[seq];
     const int nrows = q_len * G;
-    if (nrows <= 0) return;
-    const int nmt = (nrows + 15) / 16;
-    const int rows_pad = nmt * 16;
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [rows_pad][LDS]
-    __nv_bfloat16* Ks = Qs + p.row_tiles * LDS;                                     // [4 warps][32][LDS]; row_tiles holds the padded row capacity here
-    __nv_bfloat16* Vs = Ks + DEC_WARPS * DEC_WKEYS * LDS;
-    float* Op = reinterpret_cast<float*>(Vs + DEC_WARPS * DEC_WKEYS * LDS);         // [4 warps][16][D] partial outputs
-    float* MLp = Op + DEC_WARPS * 16 * D;                                           // [4 warps][16][2]
+    const int row0 = rt * BM;
+    if (row0 >= nrows) return;                                                     // the same for every CTA of the cluster
     const int ctx = kv_len - q_len;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kbase = split * DEC_KEYS;
-    const bool cta_has_keys = kbase < kv_len;
 
-    if (cta_has_keys) {
-        for (int c = tid; c < rows_pad * CH; c += NT) {
-            const int r = c / CH, part = c - r * CH;
-            const bool ok = r < nrows;
-            const int tok = ok ? r / G : 0, g = ok ? r - tok * G : 0;
-            const __nv_bfloat16* src = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)(kvh * G + g) * D + part * 8;
-            cp_async16(Qs + r * LDS + part * 8, ok ? src : p.q, ok);
-        }
-        // this warp's 32 keys
-        const int key = kbase + warp * DEC_WKEYS + lane;
-        long long off = -1;
-        if (key < kv_len) {
-            const int pg = key / p.page_size;
-            const int page = p.block_table[(size_t)seq * p.table_width + pg];
-            off = (((long long)page * p.Hkv + kvh) * p.page_size + (key - pg * p.page_size)) * D;
-        }
-        __nv_bfloat16* kd = Ks + warp * DEC_WKEYS * LDS;
-        __nv_bfloat16* vd = Vs + warp * DEC_WKEYS * LDS;
+    const int tok_lo = row0 / G, tok_hi = (min(nrows, row0 + BM) - 1) / G;
+    int k_hi = ctx + tok_hi + 1;
+    int k_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    k_lo = max(k_lo, (int)rank * p.split_len);
+    k_hi = min(k_hi, ((int)rank + 1) * p.split_len);
+    k_lo = k_lo / BN * BN;
+
+    int rpos[2], rlo[2]; bool rvalid[2];
 #pragma unroll
-        for (int i = 0; i < DEC_WKEYS * CH / 32; ++i) {
-            const int c = lane + 32 * i;
-            const int j = c / CH, part = c - j * CH;
-            const long long o = __shfl_sync(0xffffffffu, off, j);
-            const bool ok = o >= 0;
-            const long long src = ok ? o + part * 8 : 0;
-            cp_async16(kd + j * LDS + part * 8, p.k_pages + src, ok);
-            cp_async16(vd + j * LDS + part * 8, p.v_pages + src, ok);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
+    for (int h = 0; h < 2; ++h) {
+        const int row = row0 + rw * 16 + (lane >> 2) + 8 * h;
+        rvalid[h] = row < nrows;
+        rpos[h] = rvalid[h] ? ctx + row / G : -1;
+        rlo[h] = p.window > 0 ? max(0, rpos[h] - p.window + 1) : 0;
     }
-    __syncthreads();
+    const int wrow_lo = row0 + rw * 16, wrow_hi = min(nrows, wrow_lo + 16) - 1;
+    const bool warp_active = wrow_lo < nrows;
+    const int wpos_hi = warp_active ? ctx + wrow_hi / G : -1;
+    const int wpos_lo = warp_active ? ctx + wrow_lo / G : -1;
+    const int wkey_lo = p.window > 0 ? max(0, wpos_lo - p.window + 1) : 0;
 
-    const int wkey0 = kbase + warp * DEC_WKEYS;
-    const __nv_bfloat16* kb = Ks + warp * DEC_WKEYS * LDS;
-    const __nv_bfloat16* vb = Vs + warp * DEC_WKEYS * LDS;
-    for (int mt = 0; mt < nmt; ++mt) {
-        float o[D / 8][4];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[D / 8][4];
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-        float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
-        int rpos[2], rlo[2]; bool rvalid[2];
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+    const int kt0 = k_lo + kg * BN;                                                // this group's first tile
+    // this warp's 16 query rows straight into mma A fragments (4-byte loads; no shared memory, no barrier):
+    // fragment registers 0,1 hold columns 2q, 2q+1 of rows g and g+8, registers 2,3 the same 8 columns on
+    unsigned qf[D / 16][4];
+    {
+        const __nv_bfloat16* qrow[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int row = mt * 16 + (lane >> 2) + 8 * h;
-            rvalid[h] = row < nrows;
-            rpos[h] = rvalid[h] ? ctx + row / G : -1;
-            rlo[h] = p.window > 0 ? max(0, rpos[h] - p.window + 1) : 0;
+            const int row = row0 + rw * 16 + (lane >> 2) + 8 * h;
+            const int tok = rvalid[h] ? row / G : 0, g = rvalid[h] ? row - tok * G : 0;
+            qrow[h] = p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)(kvh * G + g) * D + 2 * (lane & 3);
         }
-        const int mt_pos_hi = ctx + (min(nrows, mt * 16 + 16) - 1) / G;
-        const int mt_key_lo = p.window > 0 ? max(0, ctx + (mt * 16) / G - p.window + 1) : 0;
-        const bool needed = cta_has_keys && wkey0 < kv_len && wkey0 <= mt_pos_hi && wkey0 + DEC_WKEYS > mt_key_lo;
-        if (needed) {
-            float s[DEC_WKEYS / 8][4];
+        const bool any_keys = kt0 < k_hi;
 #pragma unroll
-            for (int i = 0; i < DEC_WKEYS / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+        for (int ks = 0; ks < D / 16; ++ks)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                qf[ks][j] = (any_keys && rvalid[j & 1]) ? *reinterpret_cast<const unsigned*>(qrow[j & 1] + ks * 16 + 8 * (j >> 1)) : 0u;
+    }
+    __nv_bfloat16* kb = KV + (kg * 2) * BN * LDS;
+    __nv_bfloat16* vb = kb + BN * LDS;
+    auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(kg + 1), "r"(GT) : "memory"); };
+    // Row offsets of tile `kt`: lane l of every warp holds those of keys l and l + 32 (-1: no such key); the
+    // copy loop fetches the one it needs by shuffle, so no shared memory and no barrier come between the
+    // page numbers and the copies.  `pages`: page numbers already loaded for exactly this tile, or null.
+    // (unsigned row numbers: a pool of 2^32 rows of keys and as many of values would not fit the GPU's memory)
+    constexpr unsigned NO_ROW = 0xffffffffu;
+    auto row_offsets = [&](unsigned (&off)[2], int kt, const int* pages) {  // in rows of D elements
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int key = kt + lane + 32 * i;
+            off[i] = NO_ROW;
+            if (key < k_hi) {
+                const int pg = key / p.page_size;
+                const int page = pages ? pages[i] : table[pg];
+                off[i] = ((unsigned)page * (unsigned)p.Hkv + (unsigned)kvh) * (unsigned)p.page_size + (unsigned)(key - pg * p.page_size);
+            }
+        }
+    };
+    auto issue = [&](__nv_bfloat16* dst, const __nv_bfloat16* pages, const unsigned (&off)[2]) {
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const int c = gtid + i * GT;
+            const int j = c / CH, part = c - j * CH;
+            const unsigned lo = __shfl_sync(0xffffffffu, off[0], j & 31), hi = __shfl_sync(0xffffffffu, off[1], j & 31);
+            const unsigned o = j < 32 ? lo : hi;
+            const bool ok = o != NO_ROW;
+            cp_async16(dst + j * LDS + part * 8, pages + (ok ? (size_t)o * D + part * 8 : 0), ok);
+        }
+        cp_async_commit();
+    };
+    DPROF(2);
+    // Keys and values are separate copy groups: the next tile's keys are asked for as soon as this tile's
+    // scores are done, its values after the second product, so most of their latency hides behind arithmetic.
+    unsigned off_cur[2], off_next[2] = {NO_ROW, NO_ROW};
+    if (kt0 < k_hi) {
+        row_offsets(off_cur, kt0, kt0 == kt_guess ? page_guess : nullptr);
+        issue(kb, p.k_pages, off_cur);
+        issue(vb, p.v_pages, off_cur);
+    }
+    DPROF(3);
+    for (int kt = kt0; kt < k_hi; kt += KG * BN) {
+        const int kt_next = kt + KG * BN;
+        const bool more = kt_next < k_hi;
+        if (more) row_offsets(off_next, kt_next, nullptr);      // (its page loads overlap the wait below)
+        cp_async_wait<1>();                                     // this tile's keys (its values may still be on their way)
+        group_sync();
+        DPROF(4);
+        const bool needed = warp_active && kt <= wpos_hi && kt + BN > wkey_lo;
+        float s[BN / 8][4];
+        if (needed) {
+#pragma unroll
+            for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-                unsigned qf[4];
-                ldmatrix_x4(qf, Qs + (mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
 #pragma unroll
-                for (int np = 0; np < DEC_WKEYS / 16; ++np) {
+                for (int np = 0; np < BN / 16; ++np) {
                     unsigned b[4];
                     ldmatrix_x4(b, kb + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
-                    mma_bf16(s[2 * np], qf, b[0], b[1]);
-                    mma_bf16(s[2 * np + 1], qf, b[2], b[3]);
+                    mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+                    mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
                 }
             }
+        }
+        group_sync();                                           // the group has read the keys: their buffer is free
+        if (more) issue(kb, p.k_pages, off_next); else cp_async_commit();
+        DPROF(5);
+        if (needed) {
+            const bool full = kt + BN - 1 <= wpos_lo && kt >= (p.window > 0 ? max(0, wpos_hi - p.window + 1) : 0) && kt + BN <= k_hi
+                              && wrow_hi - wrow_lo == 15;
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < DEC_WKEYS / 8; ++i)
+            for (int i = 0; i < BN / 8; ++i) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int h = e >> 1;
-                    const int key = wkey0 + i * 8 + 2 * (lane & 3) + (e & 1);
-                    float v = s[i][e] * p.scale_log2;
-                    if (!(rvalid[h] && key <= rpos[h] && key >= rlo[h] && key < kv_len)) v = -INFINITY;
+                    float v = s[i][e];                                 // raw scores; the scale (positive) goes into the exponent's fma
+                    if (!full) {
+                        const int key = kt + i * 8 + 2 * (lane & 3) + (e & 1);
+                        if (!(rvalid[h] && key <= rpos[h] && key >= rlo[h] && key < k_hi)) v = -INFINITY;
+                    }
                     s[i][e] = v;
                     mx[h] = fmaxf(mx[h], v);
                 }
+            }
+            float alpha[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-                mrow[h] = mx[h];
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2)) * p.scale_log2;
+                const float m_new = fmaxf(m_run[h], mx[h]);
+                alpha[h] = (m_new == -INFINITY) ? 1.f : ex2(m_run[h] - m_new);
+                m_run[h] = m_new;
+                l_run[h] *= alpha[h];
             }
-            const float msub[2] = {mrow[0] == -INFINITY ? 0.f : mrow[0], mrow[1] == -INFINITY ? 0.f : mrow[1]};
+            const float msub[2] = {m_run[0] == -INFINITY ? 0.f : m_run[0], m_run[1] == -INFINITY ? 0.f : m_run[1]};
 #pragma unroll
-            for (int i = 0; i < DEC_WKEYS / 8; ++i)
+            for (int i = 0; i < BN / 8; ++i) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = exp2f(s[i][e] - msub[e >> 1]);
+                    const float pv = ex2(fmaf(s[i][e], p.scale_log2, -msub[e >> 1]));
                     s[i][e] = pv;
-                    lrow[e >> 1] += pv;
+                    l_run[e >> 1] += pv;
                 }
+            }
+            if (alpha[0] != 1.f || alpha[1] != 1.f) {
 #pragma unroll
-            for (int kk = 0; kk < DEC_WKEYS / 16; ++kk) {
+                for (int i = 0; i < D / 8; ++i) { o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1]; }
+            }
+        }
+        DPROF(6);
+        cp_async_wait<1>();                                     // this tile's values (the next keys may still be on their way)
+        group_sync();
+        if (needed) {
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
                 unsigned pf[4];
                 pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
                 pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -437,68 +557,141 @@ paged_attn_decode_kernel(const MmaParams p) {
                 }
             }
         }
-        // this warp's partial result of the 16 rows -> shared memory
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            float l = lrow[h];
-            l += __shfl_xor_sync(0xffffffffu, l, 1);
-            l += __shfl_xor_sync(0xffffffffu, l, 2);
-            const int r = (lane >> 2) + 8 * h;
-            float* op = Op + (warp * 16 + r) * D + 2 * (lane & 3);
-#pragma unroll
-            for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(op + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
-            if ((lane & 3) == 0) { MLp[(warp * 16 + r) * 2] = mrow[h]; MLp[(warp * 16 + r) * 2 + 1] = l; }
-        }
-        __syncthreads();
-        // merge the four warps' partial results (maxima are in log2 units)
-        for (int e = tid; e < 16 * D; e += NT) {
-            const int r = e / D, d = e - r * D;
-            const int row = mt * 16 + r;
-            if (row >= nrows) continue;
-            float M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < DEC_WARPS; ++w) if (MLp[(w * 16 + r) * 2 + 1] > 0.f) M = fmaxf(M, MLp[(w * 16 + r) * 2]);
-            float acc = 0.f, L = 0.f;
-#pragma unroll
-            for (int w = 0; w < DEC_WARPS; ++w) {
-                const float lw = MLp[(w * 16 + r) * 2 + 1];
-                if (lw > 0.f) {
-                    const float f = exp2f(MLp[(w * 16 + r) * 2] - M);
-                    acc += f * Op[(w * 16 + r) * D + d];
-                    L += f * lw;
-                }
-            }
-            const int tok = row / G, g = row - tok * G;
-            const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
-            if (p.num_splits == 1) {
-                p.out[grow * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-            } else {
-                p.ws_o[(grow * p.num_splits + split) * D + d] = acc;
-                if (d == 0) {
-                    float* ml = p.ws_ml + (grow * p.num_splits + split) * 2;
-                    ml[0] = M * 0.6931471805599453f;                // natural-log units for the merge kernel
-                    ml[1] = L;
-                }
-            }
-        }
-        __syncthreads();
+        group_sync();                                           // the group has read the values
+        if (more) issue(vb, p.v_pages, off_next); else cp_async_commit();
     }
+    DPROF(7);
+    cp_async_wait<0>();
+    __syncthreads();                               // every group is done with its tiles: the area becomes the exchange buffers
+    DPROF(8);
+
+    // each warp's partial result -> shared memory
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = l_run[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int r = rw * 16 + (lane >> 2) + 8 * h;
+        float* op = Op + ((size_t)kg * BM + r) * LDO + 2 * (lane & 3);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(op + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+        if ((lane & 3) == 0) { MLp[(kg * BM + r) * 2] = m_run[h]; MLp[(kg * BM + r) * 2 + 1] = l; }
+    }
+    __syncthreads();
+    DPROF(9);
+    // the groups of this CTA, in group order (maxima are in log2 units)
+    const int rows_per_owner = (BM + (int)C - 1) / (int)C;
+    for (int e = tid; e < BM * (D / 4); e += NT) {
+        const int r = e / (D / 4), c4 = e - r * (D / 4);
+        float mg[KG], lg[KG];
+        float4 vg[KG];
+#pragma unroll
+        for (int g2 = 0; g2 < KG; ++g2) {
+            const float2 ml = *reinterpret_cast<const float2*>(MLp + (g2 * BM + r) * 2);
+            mg[g2] = ml.x; lg[g2] = ml.y;
+            vg[g2] = *reinterpret_cast<const float4*>(Op + ((size_t)g2 * BM + r) * LDO + c4 * 4);
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int g2 = 0; g2 < KG; ++g2) if (lg[g2] > 0.f) M = fmaxf(M, mg[g2]);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+#pragma unroll
+        for (int g2 = 0; g2 < KG; ++g2) {
+            const float f = lg[g2] > 0.f ? ex2(mg[g2] - M) : 0.f;
+            acc.x += f * vg[g2].x; acc.y += f * vg[g2].y; acc.z += f * vg[g2].z; acc.w += f * vg[g2].w;
+            L += f * lg[g2];
+        }
+        // row r belongs to CTA r % C of the cluster, which adds the C partial results
+        const unsigned owner = (unsigned)r % C;
+        const int slot = (int)rank * rows_per_owner + r / (int)C;
+        st_cluster_f32x4(map_to_rank(Recv + (size_t)slot * LDO + c4 * 4, owner), acc);
+        if (c4 == 0) st_cluster_f32x2(map_to_rank(MLrecv + slot * 2, owner), make_float2(M, L));
+    }
+    DPROF(10);
+    cluster_sync_all();                            // release / acquire: what was sent is visible to its owner
+    DPROF(11);
+    // the CTAs of the cluster, in rank order: this CTA finishes rows rank, rank + C, ... (from its own shared memory)
+    const int my_rows = (BM - (int)rank + (int)C - 1) / (int)C;
+    for (int e = tid; e < my_rows * (D / 4); e += NT) {
+        const int lr = e / (D / 4), c4 = e - lr * (D / 4);
+        const int r = (int)rank + lr * (int)C;
+        const int row = row0 + r;
+        if (row >= nrows) continue;
+        float M = -INFINITY;
+        for (unsigned k = 0; k < C; ++k) {
+            const float2 ml = *reinterpret_cast<const float2*>(MLrecv + (k * rows_per_owner + lr) * 2);
+            if (ml.y > 0.f) M = fmaxf(M, ml.x);
+        }
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (unsigned k = 0; k < C; ++k) {
+            const float2 ml = *reinterpret_cast<const float2*>(MLrecv + (k * rows_per_owner + lr) * 2);
+            const float f = ml.y > 0.f ? ex2(ml.x - M) : 0.f;
+            const float4 v = *reinterpret_cast<const float4*>(Recv + (size_t)(k * rows_per_owner + lr) * LDO + c4 * 4);
+            acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+            L += f * ml.y;
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        const int tok = row / G, g = row - tok * G;
+        __nv_bfloat16* dst = p.out + ((size_t)(q0 + tok) * p.Hq + kvh * G + g) * D + c4 * 4;
+        uint2 w;
+        w.x = pack_bf16(acc.x * inv, acc.y * inv);
+        w.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(dst) = w;
+    }
+    DPROF(12);
+}
+
+template <int D, int RW, int KG>
+size_t cluster_smem() {
+    return cluster_tile_bytes<D, RW, KG>() + (size_t)(RW * 16 + 16) * (D + 8 + 2) * sizeof(float);
+}
+
+// How many clusters of `size` CTAs (a power of two up to 16) the device holds at once; 0: such a cluster cannot
+// be placed.  Asked once per kernel and size.
+template <int D, int RW, int KG>
+int active_clusters(int size) {
+    static int cached[5] = {-1, -1, -1, -1, -1};                 // sizes 1, 2, 4, 8, 16
+    int slot = 0;
+    while ((1 << slot) < size) ++slot;
+    if (slot > 4 || (1 << slot) != size) return 0;
+    if (cached[slot] >= 0) return cached[slot];
+    auto k = paged_attn_cluster_kernel<D, RW, KG>;
+    const size_t smem = cluster_smem<D, RW, KG>();
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return cached[slot] = 0; }
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, size); cfg.blockDim = dim3(RW * KG * 32); cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = (unsigned)size; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, k, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    return cached[slot] = n;
+}
+
+template <int D, int RW, int KG>
+int launch_cluster(const MmaParams& p, cudaStream_t s) {
+    if (active_clusters<D, RW, KG>(p.num_splits) < 1)
+        TTIE_FAIL("paged_attention (decode form): the device places no cluster of %d CTAs for this kernel", p.num_splits);
+    dim3 grid(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits);
+    TTIE_LAUNCH_CLUSTER((paged_attn_cluster_kernel<D, RW, KG>), grid, RW * KG * 32, (cluster_smem<D, RW, KG>()), s, dim3(1, p.num_splits, 1), p);
+    TTIE_CHECK_LAUNCH("paged_attention (decode form)");
+    return 0;
 }
 
 template <int D>
-int launch_decode(const MmaParams& p, cudaStream_t s) {
-    constexpr int LDS = D + 8;
-    const size_t smem = ((size_t)p.row_tiles * LDS + 2 * (size_t)DEC_KEYS * LDS) * sizeof(__nv_bfloat16)
-                        + (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
-    auto k = paged_attn_decode_kernel<D>;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) TTIE_FAIL("paged_attention_decode: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-    }
-    dim3 grid(p.num_seqs * p.Hkv, p.num_splits);
-    k<<<grid, DEC_WARPS * 32, smem, s>>>(p);
-    TTIE_CHECK_LAUNCH("paged_attention_decode");
-    return 0;
+int pick_cluster(const MmaParams& p, int rows, int key_groups, cudaStream_t s) {
+    if (rows <= 16) return key_groups >= 4 ? launch_cluster<D, 1, 4>(p, s) : launch_cluster<D, 1, 2>(p, s);
+    return key_groups >= 4 ? launch_cluster<D, 2, 4>(p, s) : launch_cluster<D, 2, 2>(p, s);
+}
+template <int D>
+int active_clusters_of(int rows, int key_groups, int size) {
+    if (rows <= 16) return key_groups >= 4 ? active_clusters<D, 1, 4>(size) : active_clusters<D, 1, 2>(size);
+    return key_groups >= 4 ? active_clusters<D, 2, 4>(size) : active_clusters<D, 2, 2>(size);
 }
 
 template <int D, int NWARPS>
@@ -532,12 +725,27 @@ extern "C" int ttie_attn_mma_tile_rows(int max_q_len, int Hq, int Hkv) {
 
 extern "C" int ttie_attn_mma_supported(int D) { return D % 16 == 0 && D >= 16 && D <= 128; }
 
-// The decode form takes requests that bring at most this many query rows (tokens x heads per kv head)
-// and splits keys in pieces of ttie_attn_decode_split_len().
-extern "C" int ttie_attn_decode_max_rows() { return DEC_MAX_ROWS; }
-extern "C" int ttie_attn_decode_split_len() { return DEC_KEYS; }
+// The decode form tiles query rows (tokens x heads per kv head) by at most this many per cluster.
+extern "C" int ttie_attn_cluster_tile_rows(int max_q_len, int Hq, int Hkv) { return max_q_len * (Hq / Hkv) <= 16 ? 16 : CL_MAX_ROWS; }
+// How many clusters of `size` CTAs (1, 2, 4, 8 or 16: the CTAs over which one request's keys are cut) the device
+// holds at once, for this head size, row count per request and number of key groups (2 or 4); 0: none.
+extern "C" int ttie_attn_cluster_active(int D, int max_q_len, int Hq, int Hkv, int key_groups, int size) {
+    const int rows = max_q_len * (Hq / Hkv);
+    switch (D) {
+        case 16: return active_clusters_of<16>(rows, key_groups, size);
+        case 32: return active_clusters_of<32>(rows, key_groups, size);
+        case 48: return active_clusters_of<48>(rows, key_groups, size);
+        case 64: return active_clusters_of<64>(rows, key_groups, size);
+        case 80: return active_clusters_of<80>(rows, key_groups, size);
+        case 96: return active_clusters_of<96>(rows, key_groups, size);
+        case 112: return active_clusters_of<112>(rows, key_groups, size);
+        case 128: return active_clusters_of<128>(rows, key_groups, size);
+    }
+    return 0;
+}
 
-// form 0: tile loop (prompt portions; decode with caller-chosen splits).  form 1: decode form.
+// form 0: tile loop (prompt portions; decode with caller-chosen splits and a merge kernel).  form 2 or 4: decode form
+// with that many key groups; num_splits is then the cluster size and split_len the keys per CTA (no scratch).
 extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                              const int* block_table, int table_width, int page_size, const int* qsl,
                                              const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
@@ -564,7 +772,7 @@ extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, 
     if (q_stride % 8) TTIE_FAIL("paged_attention_mma: query row stride %lld must be a multiple of 8 elements", q_stride);
     if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) TTIE_FAIL("paged_attention_mma: pointers must be 16-byte aligned");
     if (num_splits < 1) num_splits = 1;
-    if (num_splits > 1 && (split_len <= 0 || split_len % BN || !scratch))
+    if (form == 0 && num_splits > 1 && (split_len <= 0 || split_len % BN || !scratch))
         TTIE_FAIL("paged_attention_mma: splits need scratch and a split length that is a multiple of %d", BN);
     if (num_splits > 65535) TTIE_FAIL("paged_attention_mma: too many splits (%d)", num_splits);
     MmaParams p;
@@ -577,25 +785,24 @@ extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, 
     p.num_splits = num_splits; p.split_len = split_len;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     const int rows = max_q_len * (Hq / Hkv);
-    if (form == 1) {
-        if (rows > DEC_MAX_ROWS) TTIE_FAIL("paged_attention_mma: the decode form takes at most %d query rows per request, got %d", DEC_MAX_ROWS, rows);
-        if (num_splits > 1 && split_len != DEC_KEYS) TTIE_FAIL("paged_attention_mma: the decode form splits keys by %d", DEC_KEYS);
-        p.row_tiles = ceil_div(rows, 16) * 16;                  // padded query-row capacity of the CTA's shared memory
-        int rc;
+    if (form == 2 || form == 4) {
+        if (num_splits > 1 && (split_len <= 0 || split_len % BN)) TTIE_FAIL("paged_attention_mma: the split length must be a multiple of %d", BN);
+        if (num_splits == 1) p.split_len = 1 << 30;
+        const int tile_rows = ttie_attn_cluster_tile_rows(max_q_len, Hq, Hkv);
+        p.row_tiles = ceil_div(rows, tile_rows);
+        if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("paged_attention_mma: grid too large");
+        cudaStream_t s = (cudaStream_t)stream;
         switch (D) {
-            case 16: rc = launch_decode<16>(p, (cudaStream_t)stream); break;
-            case 32: rc = launch_decode<32>(p, (cudaStream_t)stream); break;
-            case 48: rc = launch_decode<48>(p, (cudaStream_t)stream); break;
-            case 64: rc = launch_decode<64>(p, (cudaStream_t)stream); break;
-            case 80: rc = launch_decode<80>(p, (cudaStream_t)stream); break;
-            case 96: rc = launch_decode<96>(p, (cudaStream_t)stream); break;
-            case 112: rc = launch_decode<112>(p, (cudaStream_t)stream); break;
-            case 128: rc = launch_decode<128>(p, (cudaStream_t)stream); break;
+            case 16: return pick_cluster<16>(p, rows, form, s);
+            case 32: return pick_cluster<32>(p, rows, form, s);
+            case 48: return pick_cluster<48>(p, rows, form, s);
+            case 64: return pick_cluster<64>(p, rows, form, s);
+            case 80: return pick_cluster<80>(p, rows, form, s);
+            case 96: return pick_cluster<96>(p, rows, form, s);
+            case 112: return pick_cluster<112>(p, rows, form, s);
+            case 128: return pick_cluster<128>(p, rows, form, s);
             default: TTIE_FAIL("paged_attention_mma: head size %d", D);
         }
-        if (rc) return rc;
-        if (num_splits > 1) return attn_merge_bf16(p.ws_o, p.ws_ml, out, T * Hq, num_splits, D, (cudaStream_t)stream);
-        return 0;
     }
     const int bm = ttie_attn_mma_tile_rows(max_q_len, Hq, Hkv);
     p.row_tiles = ceil_div(rows, bm);
@@ -617,3 +824,7 @@ extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, 
     if (num_splits > 1) return attn_merge_bf16(p.ws_o, p.ws_ml, out, T * Hq, num_splits, D, s);
     return 0;
 }
+
+#ifdef TTIE_PROFILE_DEC
+extern "C" int ttie_dec_profile(long long* out) { return cudaMemcpyFromSymbol(out, g_dec_prof, sizeof(long long) * 32) == cudaSuccess ? 0 : 1; }
+#endif

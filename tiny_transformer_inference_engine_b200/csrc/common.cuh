@@ -63,32 +63,33 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // kernels here call it first thing, so only launch latency and CTA scheduling overlap).  Works inside
 // captured graphs.  ttie_set_pdl(0) turns it off.
 bool pdl_enabled();
-// cluster_x > 1: consecutive CTAs along x form a thread-block cluster (the grid's x must be a multiple).
+// cluster: CTAs per thread-block cluster along x, y, z (the grid must be a multiple); dim3(1) for none.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster_x,
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, dim3 cluster,
                                  Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute attr[2];
     int n = 0;
     // (a cluster launch does not take the attribute: as a programmatic dependent it was measured to start late)
-    if (pdl_enabled() && cluster_x <= 1) {
+    const bool clustered = cluster.x * cluster.y * cluster.z > 1;
+    if (pdl_enabled() && !clustered) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (cluster_x > 1) {
+    if (clustered) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = (unsigned)cluster_x; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+        attr[n].val.clusterDim.x = cluster.x; attr[n].val.clusterDim.y = cluster.y; attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
     cfg.attrs = attr; cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #define TTIE_LAUNCH(kernel, grid, block, smem, stream, ...) \
-    ::ttie::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, 1, __VA_ARGS__)
-#define TTIE_LAUNCH_CLUSTER(kernel, grid, block, smem, stream, cluster_x, ...) \
-    ::ttie::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, cluster_x, __VA_ARGS__)
+    ::ttie::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, dim3(1), __VA_ARGS__)
+#define TTIE_LAUNCH_CLUSTER(kernel, grid, block, smem, stream, cluster, ...) \
+    ::ttie::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, dim3(cluster), __VA_ARGS__)
 
 
 }  // namespace ttie

@@ -86,10 +86,14 @@ class CudaOps:
         self.launches = 0                     # kernels of this library launched so far
         self.tc_used = False                  # a tcgen05 kernel ran since the error word was last read
         self.attn_target_ctas = 4 * NUM_SMS      # decode tiles are small: four CTAs share an SM
+        self.attn_cluster_max_rows = 64         # query rows per request (tokens x heads per kv head) up to which the decode form runs
+        self.attn_cluster_max_size = 8          # CTAs per cluster (16 is placed on fewer SMs at a time)
+        self.attn_cluster_tiles_per_warp = 1    # ... and only while a warp walks at most this many 64-key tiles
+        self._cluster_max = {}
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
         self.lib.ttie_attn_tc_supported.restype = _c_int
-        for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows", "ttie_attn_decode_max_rows", "ttie_attn_decode_split_len"):
+        for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows", "ttie_attn_cluster_tile_rows", "ttie_attn_cluster_active"):
             getattr(self.lib, name).restype = _c_int
 
     # ------------------------------------------------------------------ helpers
@@ -294,6 +298,9 @@ class CudaOps:
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
             return "tc", 1, 0                                   # prompt portions: the tcgen05 kernel
         if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
+            plan = self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
+            if plan is not None:
+                return plan
             kernel, tile_rows, unit, min_len = "mma", self.lib.ttie_attn_mma_tile_rows(max_q_len, num_heads, num_kv_heads), 64, 128
         else:
             kernel, tile_rows, unit, min_len = "simt", 32, 32, 128
@@ -305,6 +312,36 @@ class CudaOps:
         split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
         num_splits = math.ceil(max_kv_len / split_len)
         return (kernel, num_splits, split_len) if num_splits > 1 else (kernel, 1, 0)
+
+    def _clusters_active(self, head_dim, max_q_len, num_heads, num_kv_heads, groups, size):
+        key = (head_dim, max_q_len * (num_heads // num_kv_heads) <= 16, groups, size)
+        if key not in self._cluster_max:
+            self._cluster_max[key] = self.lib.ttie_attn_cluster_active(head_dim, max_q_len, num_heads, num_kv_heads, groups, size)
+        return self._cluster_max[key]
+
+    def _cluster_plan(self, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len):
+        """The decode form ("mma_c4" / "mma_c2": one thread-block cluster per request and kv head, 4 or 2 key
+        groups per CTA) for steps whose requests bring few query rows: (kernel, cluster size, keys per CTA),
+        or None where the tile loop serves better (many rows; a long context with too few requests to
+        fill the GPU with clusters)."""
+        rows = max_q_len * (num_heads // num_kv_heads)
+        if rows > self.attn_cluster_max_rows:
+            return None
+        tile_rows = self.lib.ttie_attn_cluster_tile_rows(max_q_len, num_heads, num_kv_heads)
+        base = num_seqs * num_kv_heads * math.ceil(rows / tile_rows)
+        groups = 4 if max_kv_len > 128 else 2
+        want = max(1, min(self.attn_cluster_max_size, (NUM_SMS + base // 2) // base, math.ceil(max_kv_len / (64 * groups))))
+        C = 1 << (want.bit_length() - 1)                       # a power of two
+        while C > 1 and self._clusters_active(head_dim, max_q_len, num_heads, num_kv_heads, groups, C) < base:
+            C //= 2                                            # all clusters of the step have to run at once
+        if self._clusters_active(head_dim, max_q_len, num_heads, num_kv_heads, groups, C) < 1:
+            return None
+        split_len = math.ceil(math.ceil(max_kv_len / C) / 64) * 64
+        # measured: the form pays while a warp walks few tiles; beyond that the tile loop with more, smaller CTAs
+        # and a merge kernel is as fast or faster
+        if split_len > self.attn_cluster_tiles_per_warp * 64 * groups:
+            return None
+        return f"mma_c{groups}", C, split_len
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table, page_size,
                         query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out,
@@ -320,15 +357,18 @@ class CudaOps:
                 num_kv_heads, head_dim, max_q_len, float(scale), int(window), self._stream(qkv)), "paged_attention_tc")
             self.launches += 1
             return
+        form = {"mma": 0, "mma_c2": 2, "mma_c4": 4}.get(kernel)
         scratch = None
-        if num_splits > 1:
+        if num_splits > 1 and not form:
             scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
-        if kernel in ("mma", "mma_decode"):
+        if form is not None:
             self._check(self.lib.ttie_paged_attention_mma_form(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
                 head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
-                1 if kernel == "mma_decode" else 0, self._stream(qkv)), "paged_attention_mma")
+                form, self._stream(qkv)), "paged_attention_mma")
+            self.launches += 2 if (num_splits > 1 and not form) else 1
+            return
         else:
             self._check(self.lib.ttie_paged_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
