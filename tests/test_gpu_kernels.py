@@ -455,6 +455,33 @@ def test_decode_form_one_key_decides(ops, kpos, groups, cluster):
     assert rel(out, exp) < TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,page", [(32, 1, 128, 64), (71, 1, 64, 16), (8, 2, 128, 8), (3, 1, 64, 128), (128, 1, 64, 64), (40, 1, 128, 32)])
+@pytest.mark.parametrize("seqs", [[(200, 1), (64, 1), (65, 1), (1, 1), (513, 1)], [(130, 2), (128, 1), (129, 1)], [(4096, 1)] * 2,
+                                  [(700, 5), (3, 3), (1100, 1)]])
+@pytest.mark.parametrize("split_len", [128, 256, 1024])
+def test_tcgen05_attention_with_splits(ops, Hq, Hkv, D, page, seqs, split_len):
+    """The tcgen05 kernel on decode-shaped steps: key range cut over CTAs (some of them without a visible key),
+    one to four quarters of the 128-row tile in use, partial results merged by the merge kernel."""
+    max_kv = max(L for L, _ in seqs)
+    n = -(-max_kv // split_len)
+    plan = ("tc", n, split_len) if n > 1 else ("tc", 1, 0)
+    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=plan)
+    assert ops.tc_error() == 0
+    assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
+    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=plan, window=70)
+    assert ops.tc_error() == 0
+    assert rel(out, exp) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("kpos", [0, 127, 128, 447, 599])
+def test_tcgen05_splits_one_key_decides(ops, kpos):
+    seqs = [(50, 1), (600, 1), (64, 1)]
+    out, exp, dense, qsl = attention_case(ops, "bfloat16", 4, 1, 64, 64, seqs, plan=("tc", 5, 128), spike=(1, 0, kpos))
+    assert ops.tc_error() == 0
+    assert (out[qsl[1]].view(4, 64) - dense[1][1][kpos, 0]).abs().max() < 2e-2
+    assert rel(out, exp) < TOL["bfloat16"]
+
+
 def test_decode_form_is_planned(ops):
     """Decode steps of the bfloat16 path take the decode form while a warp has one key tile to walk; longer
     contexts take the tile loop with splits, prompt portions the tcgen05 kernel or the tile loop."""
@@ -462,7 +489,10 @@ def test_decode_form_is_planned(ops):
     assert kernel == "mma_c4" and C * split_len >= 2048 and C & (C - 1) == 0 and split_len <= 256
     assert ops.attention_plan(torch.bfloat16, 3, 4, 2, 64, 1, 100, 16)[0] == "mma_c2"
     assert ops.attention_plan(torch.bfloat16, 64, 32, 1, 128, 1, 256, 64) == ("mma_c4", 1, 256)
-    assert ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 32768, 64)[0] == "mma"
+    kernel, n, split_len = ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 32768, 64)
+    assert kernel == "tc" and n * split_len >= 32768 and split_len % 128 == 0 and 8 * n <= 148
+    assert ops.attention_plan(torch.bfloat16, 8, 32, 1, 96, 1, 32768, 64)[0] == "mma"       # a head size the tcgen05 kernel does not take
+    assert ops.attention_plan(torch.bfloat16, 8, 32, 8, 128, 1, 32768, 64)[0] == "mma"      # four rows per kv head
     assert ops.attention_plan(torch.bfloat16, 1, 32, 1, 128, 2048, 2048, 64)[0] == "tc"
     assert ops.attention_plan(torch.bfloat16, 2, 8, 2, 48, 200, 200, 16)[0] == "mma"
 

@@ -1,4 +1,5 @@
-// Causal paged attention for prompt portions on tcgen05 tensor cores (bfloat16, head size 64 or 128).
+// Causal paged attention on tcgen05 tensor cores (bfloat16, head size 64 or 128): prompt portions, and
+// decode steps with the key range cut over CTAs (partial results for the merge kernel).
 //
 // A CTA owns 128 query rows - (token, head of a kv head's group) pairs, so with multi-query attention
 // 4 tokens x 32 heads share every key/value tile - and walks over 128-key tiles:
@@ -95,6 +96,8 @@ struct AttnTcParams {
     int num_seqs, Hq, Hkv;
     float scale_log2; int window;
     int row_tiles;
+    int num_splits, split_len;                                   // keys per CTA along grid y (a multiple of 128); 1: no split
+    float* ws_o; float* ws_ml;                                   // partial results [row][split][D] and [row][split][2] (max in natural log, sum)
 };
 
 // Barrier slots
@@ -129,17 +132,38 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (row0 >= nrows) return;                                   // uniform over the CTA, before anything is allocated
     const int ctx = kv_len - q_len;
     const int tok_lo = row0 / G, tok_hi = (min(nrows, row0 + BM) - 1) / G;
-    const int key_hi = ctx + tok_hi + 1;                         // exclusive
-    const int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    int key_hi = ctx + tok_hi + 1;                               // exclusive
+    int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    const int split = blockIdx.y;
+    if (p.num_splits > 1) {                                      // splits start on tile boundaries
+        key_lo = max(key_lo, split * p.split_len);
+        key_hi = min(key_hi, (split + 1) * p.split_len);
+    }
     const int t_begin = key_lo / BN, t_end = (key_hi + BN - 1) / BN;
     const int ntiles = t_end - t_begin;
+    const int rows_here = min(BM, nrows - row0);
+    if (ntiles <= 0) {
+        // (only with splits) no key of this split is visible: an empty partial result, nothing allocated
+        for (int e = threadIdx.x; e < rows_here * D; e += blockDim.x) {
+            const int r = e / D, row = row0 + r;
+            const int tok = row / G, g = row - tok * G;
+            const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
+            p.ws_o[(grow * p.num_splits + split) * D + (e - r * D)] = 0.f;
+            if (e - r * D == 0) { p.ws_ml[(grow * p.num_splits + split) * 2] = -INFINITY; p.ws_ml[(grow * p.num_splits + split) * 2 + 1] = 0.f; }
+        }
+        return;
+    }
+    // softmax warps whose 32 rows hold no query (a decode step fills the first quarter or two) take no part:
+    // the barriers count the others only
+    const int nquarters = (rows_here + 31) / 32;
+    const uint32_t softmax_threads = 64u * (uint32_t)nquarters;
     const uint32_t bar0 = smem_u32(&bars[0]);
 #define BAR(i) (bar0 + 8u * (uint32_t)(i))
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NBARS; ++i) {
             const bool many = (i >= SE && i < SE + 2) || (i >= OE && i < OE + 2) || i == PF || i >= XB;
-            mbar_init(BAR(i), many ? 256u : 1u);
+            mbar_init(BAR(i), many ? softmax_threads : 1u);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -241,7 +265,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 umma_commit(BAR(PE));
             }
         }
-    } else {
+    } else if ((warp & 3) < nquarters) {
         // softmax: two threads per row (warps w and w+4 reach the same 32 lanes of tensor memory); each
         // owns one half of the tile's 128 score columns and one half of the output columns.  Only the row
         // maximum is exchanged per tile (shared memory + an mbarrier with a bounded wait); the row sums are
@@ -371,7 +395,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             ok = mbar_wait(BAR(XL), 0, 12);
             l_tot = l_run + xch[ntiles & 1][half ^ 1][r];
         }
-        if (ok && valid) {
+        if (ok && valid && p.num_splits > 1) {
+            const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
+            float* dst = p.ws_o + (grow * p.num_splits + split) * D + half * OC;
+#pragma unroll
+            for (int i = 0; i < OC; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+            if (half == 0) {
+                float* ml = p.ws_ml + (grow * p.num_splits + split) * 2;
+                ml[0] = m_run * 0.6931471805599453f;                 // natural-log units for the merge
+                ml[1] = l_tot;
+            }
+        } else if (ok && valid) {
             const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
             __nv_bfloat16* dst = p.out + ((size_t)(q0 + tok) * p.Hq + kvh * G + g) * D + half * OC;
 #pragma unroll
@@ -428,7 +462,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, 
     auto k = attn_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-    k<<<p.num_seqs * p.Hkv * p.row_tiles, 320, smem, s>>>(mk, mv, p);
+    k<<<dim3(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits), 320, smem, s>>>(mk, mv, p);
     TTIE_CHECK_LAUNCH("attention_tc");
     return 0;
 }
@@ -447,15 +481,22 @@ extern "C" int ttie_attn_tc_supported(int D, int page_size) {
     return (D == 64 || D == 128) && page_size >= 8 && page_size % 8 == 0 && (128 % page_size == 0 || page_size % 128 == 0) && page_size <= 256;
 }
 
+// num_splits > 1: the key range is cut into pieces of split_len keys (a multiple of 128) over grid y; the partial
+// results go to `scratch` (ttie_attn_scratch_floats) and a merge kernel writes `out`.
 extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                        int num_pages, const int* block_table, int table_width, int page_size, const int* qsl,
                                        const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                       int max_q_len, float scale, int window, void* stream) {
+                                       int max_q_len, float scale, int window, int num_splits, int split_len, float* scratch,
+                                       void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (!ttie_attn_tc_supported(D, page_size)) TTIE_FAIL("attention_tc: head size %d with pages of %d keys is not supported", D, page_size);
     if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("attention_tc: %d heads are not a multiple of %d kv heads", Hq, Hkv);
-    if (q_stride % 8 || ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15)
+    if (q_stride % 8 || ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out | (uintptr_t)scratch) & 15)
         TTIE_FAIL("attention_tc: pointers must be 16-byte aligned and the query stride a multiple of 8");
+    if (num_splits < 1) num_splits = 1;
+    if (num_splits > 1 && (split_len <= 0 || split_len % BN || !scratch))
+        TTIE_FAIL("attention_tc: splits need scratch and a split length that is a multiple of %d", BN);
+    if (num_splits > 65535) TTIE_FAIL("attention_tc: too many splits (%d)", num_splits);
     CUtensorMap mk, mv;
     const long long rows = (long long)num_pages * Hkv * page_size;
     const int box_rows = page_size < BN ? page_size : BN;
@@ -466,7 +507,12 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     p.page_size = page_size; p.qsl = qsl; p.seq_lens = seq_lens; p.out = (__nv_bfloat16*)out;
     p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
     p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), BM);
+    p.num_splits = num_splits; p.split_len = split_len;
+    p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("attention_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
-    return D == 64 ? launch<64>(mk, mv, p, s) : launch<128>(mk, mv, p, s);
+    const int rc = D == 64 ? launch<64>(mk, mv, p, s) : launch<128>(mk, mv, p, s);
+    if (rc) return rc;
+    if (num_splits > 1) return attn_merge_bf16(p.ws_o, p.ws_ml, out, T * Hq, num_splits, D, s);
+    return 0;
 }

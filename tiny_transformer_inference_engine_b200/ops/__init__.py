@@ -49,7 +49,7 @@ _SIGNATURES = {
                                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
                                       _c_void, _c_int, _c_void],
     "ttie_paged_attention_tc": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
 }
@@ -90,6 +90,7 @@ class CudaOps:
         self.attn_cluster_max_size = 8          # CTAs per cluster (16 is placed on fewer SMs at a time)
         self.attn_cluster_tiles_per_warp = 1    # ... and only while a warp walks at most this many 64-key tiles
         self._cluster_max = {}
+        self.attn_tc_min_split = 256            # keys per CTA from which the tcgen05 kernel splits a decode step's key range
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
         self.lib.ttie_attn_tc_supported.restype = _c_int
@@ -301,6 +302,9 @@ class CudaOps:
             plan = self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
             if plan is not None:
                 return plan
+            plan = self._tc_split_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
+            if plan is not None:
+                return plan
             kernel, tile_rows, unit, min_len = "mma", self.lib.ttie_attn_mma_tile_rows(max_q_len, num_heads, num_kv_heads), 64, 128
         else:
             kernel, tile_rows, unit, min_len = "simt", 32, 32, 128
@@ -312,6 +316,21 @@ class CudaOps:
         split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
         num_splits = math.ceil(max_kv_len / split_len)
         return (kernel, num_splits, split_len) if num_splits > 1 else (kernel, 1, 0)
+
+    def _tc_split_plan(self, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size):
+        """The tcgen05 kernel for steps with few query rows per request and contexts too long for the decode
+        form: one wave of CTAs (the kernel takes a whole SM), each walking at least 256 keys; the merge
+        kernel adds the pieces.  None where the head or page size is not the kernel's, the rows exceed one
+        128-row tile or fill less than an eighth of it (the mma.sync kernel's 16-row tiles waste less there), or
+        the requests alone fill the GPU."""
+        rows = max_q_len * (num_heads // num_kv_heads)
+        base = num_seqs * num_kv_heads
+        if page_size is None or rows > 128 or rows < 16 or base > NUM_SMS or not self.lib.ttie_attn_tc_supported(head_dim, page_size):
+            return None
+        n = max(1, min(NUM_SMS // base, math.ceil(max_kv_len / self.attn_tc_min_split)))
+        split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
+        n = math.ceil(max_kv_len / split_len)
+        return ("tc", n, split_len) if n > 1 else ("tc", 1, 0)
 
     def _clusters_active(self, head_dim, max_q_len, num_heads, num_kv_heads, groups, size):
         key = (head_dim, max_q_len * (num_heads // num_kv_heads) <= 16, groups, size)
@@ -351,11 +370,15 @@ class CudaOps:
             qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
         if kernel == "tc":
             self.tc_used = True
+            scratch = None
+            if num_splits > 1:
+                scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
             self._check(self.lib.ttie_paged_attention_tc(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                 block_table.shape[1], page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads,
-                num_kv_heads, head_dim, max_q_len, float(scale), int(window), self._stream(qkv)), "paged_attention_tc")
-            self.launches += 1
+                num_kv_heads, head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
+                self._stream(qkv)), "paged_attention_tc")
+            self.launches += 2 if num_splits > 1 else 1
             return
         form = {"mma": 0, "mma_c2": 2, "mma_c4": 4}.get(kernel)
         scratch = None
