@@ -318,12 +318,6 @@ __device__ __forceinline__ unsigned map_to_rank(const void* local, unsigned rank
     asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
     return remote;
 }
-#ifdef TTIE_PROFILE_DEC
-__device__ long long g_dec_prof[32];
-#define DPROF(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_dec_prof[i] = clock64(); } while (0)
-#else
-#define DPROF(i) do {} while (0)
-#endif
 __device__ __forceinline__ void st_cluster_f32x4(unsigned addr, float4 v) {
     asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
@@ -353,9 +347,7 @@ paged_attn_cluster_kernel(const MmaParams p) {
     // works on its tiles): slot = sender's rank * rows per owner + local row
     float* Recv = reinterpret_cast<float*>(smem_raw + cluster_tile_bytes<D, RW, KG>());   // [BM + 16][LDO]
     float* MLrecv = Recv + (BM + 16) * LDO;                                        // [BM + 16][2]
-    DPROF(0);
     TTIE_PDL_ENTRY();
-    DPROF(1);
 
     const int G = p.Hq / p.Hkv;
     int tile = blockIdx.x;
@@ -458,7 +450,6 @@ paged_attn_cluster_kernel(const MmaParams p) {
         }
         cp_async_commit();
     };
-    DPROF(2);
     // Keys and values are separate copy groups: the next tile's keys are asked for as soon as this tile's
     // scores are done, its values after the second product, so most of their latency hides behind arithmetic.
     unsigned off_cur[2], off_next[2] = {NO_ROW, NO_ROW};
@@ -467,14 +458,12 @@ paged_attn_cluster_kernel(const MmaParams p) {
         issue(kb, p.k_pages, off_cur);
         issue(vb, p.v_pages, off_cur);
     }
-    DPROF(3);
     for (int kt = kt0; kt < k_hi; kt += KG * BN) {
         const int kt_next = kt + KG * BN;
         const bool more = kt_next < k_hi;
         if (more) row_offsets(off_next, kt_next, nullptr);      // (its page loads overlap the wait below)
         cp_async_wait<1>();                                     // this tile's keys (its values may still be on their way)
         group_sync();
-        DPROF(4);
         const bool needed = warp_active && kt <= wpos_hi && kt + BN > wkey_lo;
         float s[BN / 8][4];
         if (needed) {
@@ -493,7 +482,6 @@ paged_attn_cluster_kernel(const MmaParams p) {
         }
         group_sync();                                           // the group has read the keys: their buffer is free
         if (more) issue(kb, p.k_pages, off_next); else cp_async_commit();
-        DPROF(5);
         if (needed) {
             const bool full = kt + BN - 1 <= wpos_lo && kt >= (p.window > 0 ? max(0, wpos_hi - p.window + 1) : 0) && kt + BN <= k_hi
                               && wrow_hi - wrow_lo == 15;
@@ -537,7 +525,6 @@ paged_attn_cluster_kernel(const MmaParams p) {
                 for (int i = 0; i < D / 8; ++i) { o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1]; }
             }
         }
-        DPROF(6);
         cp_async_wait<1>();                                     // this tile's values (the next keys may still be on their way)
         group_sync();
         if (needed) {
@@ -560,10 +547,8 @@ paged_attn_cluster_kernel(const MmaParams p) {
         group_sync();                                           // the group has read the values
         if (more) issue(vb, p.v_pages, off_next); else cp_async_commit();
     }
-    DPROF(7);
     cp_async_wait<0>();
     __syncthreads();                               // every group is done with its tiles: the area becomes the exchange buffers
-    DPROF(8);
 
     // each warp's partial result -> shared memory
 #pragma unroll
@@ -578,7 +563,6 @@ paged_attn_cluster_kernel(const MmaParams p) {
         if ((lane & 3) == 0) { MLp[(kg * BM + r) * 2] = m_run[h]; MLp[(kg * BM + r) * 2 + 1] = l; }
     }
     __syncthreads();
-    DPROF(9);
     // the groups of this CTA, in group order (maxima are in log2 units)
     const int rows_per_owner = (BM + (int)C - 1) / (int)C;
     for (int e = tid; e < BM * (D / 4); e += NT) {
@@ -608,9 +592,7 @@ paged_attn_cluster_kernel(const MmaParams p) {
         st_cluster_f32x4(map_to_rank(Recv + (size_t)slot * LDO + c4 * 4, owner), acc);
         if (c4 == 0) st_cluster_f32x2(map_to_rank(MLrecv + slot * 2, owner), make_float2(M, L));
     }
-    DPROF(10);
     cluster_sync_all();                            // release / acquire: what was sent is visible to its owner
-    DPROF(11);
     // the CTAs of the cluster, in rank order: this CTA finishes rows rank, rank + C, ... (from its own shared memory)
     const int my_rows = (BM - (int)rank + (int)C - 1) / (int)C;
     for (int e = tid; e < my_rows * (D / 4); e += NT) {
@@ -641,7 +623,6 @@ paged_attn_cluster_kernel(const MmaParams p) {
         w.y = pack_bf16(acc.z * inv, acc.w * inv);
         *reinterpret_cast<uint2*>(dst) = w;
     }
-    DPROF(12);
 }
 
 template <int D, int RW, int KG>
@@ -824,7 +805,3 @@ extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, 
     if (num_splits > 1) return attn_merge_bf16(p.ws_o, p.ws_ml, out, T * Hq, num_splits, D, s);
     return 0;
 }
-
-#ifdef TTIE_PROFILE_DEC
-extern "C" int ttie_dec_profile(long long* out) { return cudaMemcpyFromSymbol(out, g_dec_prof, sizeof(long long) * 32) == cudaSuccess ? 0 : 1; }
-#endif

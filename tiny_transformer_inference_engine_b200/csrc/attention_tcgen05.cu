@@ -8,7 +8,7 @@
 //   warp 1      one thread issues  S = Q K^T  (tcgen05.mma, both operands K-major in shared memory,
 //               S in tensor memory, two buffers) and  O_tile = P V  (P from shared memory, V as an
 //               MN-major operand, O_tile in tensor memory, two buffers)
-//   warps 2-9   softmax, two threads per row (each one half of the columns): tcgen05.ld the row of S,
+//   warps 2-17  softmax, four threads per row (each one quarter of the columns): tcgen05.ld the row of S,
 //               scale, mask, running maximum and sum in float32, P rounded to bfloat16 into shared memory
 //               in the operand layout; one iteration later the same threads take O_tile out of tensor
 //               memory and add it to their part of the output row, rescaled - the running output lives
@@ -50,6 +50,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
     }
     return true;
 }
+// The same for a warp that runs ahead of the others (the copy producer): it sleeps between polls, so its polling
+// does not take issue slots from the softmax warps of its SM sub-partition.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const long long deadline = clock64() + WAIT_CYCLES;
+    while (!mbar_try(bar, parity)) {
+        __nanosleep(64);
+        if (clock64() > deadline) { atomicCAS(&g_attn_tc_error, 0, code); return false; }
+    }
+    return true;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
@@ -82,6 +93,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+
 __device__ __forceinline__ float ex2(float x) {                // 2^x, one instruction; 2^-inf = 0
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -103,8 +124,12 @@ struct AttnTcParams {
 // Barrier slots
 enum { KF = 0, KE = 2, VF = 4, VE = 6, SF = 8, SE = 10, OF = 12, OE = 14, PF = 16, PE = 17, XB = 18, XL = 20, NBARS = 21 };
 
-template <int D>
-__global__ void __launch_bounds__(320, 1)
+constexpr int NP = 4;                                            // softmax threads per query row
+constexpr int NTHREADS = 64 + NP * 128;
+
+// AHEAD: the copy producer looks pages up one tile ahead (prompt portions); otherwise as it goes (decode steps).
+template <int D, bool AHEAD>
+__global__ void __launch_bounds__(NTHREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
     constexpr int CB = D / 64;                                   // 64-column blocks of the head dimension
     constexpr uint32_t QBLK = BM * 128, KVBLK = BN * 128;        // bytes of one 64-column block
@@ -119,7 +144,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     unsigned char* Vs = Ks + 2 * KV_BYTES;                       // [2 stages]
     __shared__ __align__(8) unsigned long long bars[NBARS];
     __shared__ uint32_t tmem_slot;
-    __shared__ float xch[2][2][BM];                               // row maxima of the two column halves, by tile parity
+    __shared__ float xch[2][NP][BM];                              // row maxima of the column parts, by tile parity
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.Hq / p.Hkv;
@@ -156,7 +181,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // softmax warps whose 32 rows hold no query (a decode step fills the first quarter or two) take no part:
     // the barriers count the others only
     const int nquarters = (rows_here + 31) / 32;
-    const uint32_t softmax_threads = 64u * (uint32_t)nquarters;
+    const uint32_t softmax_threads = 32u * NP * (uint32_t)nquarters;
     const uint32_t bar0 = smem_u32(&bars[0]);
 #define BAR(i) (bar0 + 8u * (uint32_t)(i))
 
@@ -190,7 +215,56 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
 
-    if (warp == 0) {
+    if (warp == 0 && AHEAD) {
+        // Prompt portions.  The whole warp walks the tiles: lane b looks up the page of box b (a
+        // tile is 128 / box_rows boxes) one tile ahead, so the table's latency hides behind the waits; lane 0
+        // waits for the stages and issues the copies.
+        const int ps = p.page_size;
+        const int box_rows = ps < BN ? ps : BN, nboxes = BN / box_rows;
+        const int* table = p.block_table + (size_t)seq * p.table_width;
+        auto box_row = [&](int j) -> int {                      // first row of this lane's box of tile j in the page matrix
+            int y = 0;
+            if (lane < nboxes && j < ntiles) {
+                const int key = (t_begin + j) * BN + lane * box_rows;
+                const int pg = key / ps;
+                const int page = pg < p.table_width ? table[pg] : 0;
+                y = (page * p.Hkv + kvh) * ps + (key - pg * ps);
+            }
+            return y;
+        };
+        int y_cur = box_row(0);
+        for (int j = 0; j < ntiles; ++j) {
+            const int y_next = box_row(j + 1);
+            const int st = j & 1;
+            const uint32_t par = ((j >> 1) & 1) ^ 1;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait_relaxed(BAR(KE + st), par, 1);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            if (lane == 0) mbar_expect_tx(BAR(KF + st), KV_BYTES);
+            for (int b = 0; b < nboxes; ++b) {
+                const int y = __shfl_sync(0xffffffffu, y_cur, b);
+                if (lane == 0) {
+#pragma unroll
+                    for (int cb = 0; cb < CB; ++cb)
+                        tma_load_2d(smem_u32(Ks + st * KV_BYTES + cb * KVBLK + b * box_rows * 128), &tmK, BAR(KF + st), cb * 64, y);
+                }
+            }
+            if (lane == 0) ok = mbar_wait_relaxed(BAR(VE + st), par, 2);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            if (lane == 0) mbar_expect_tx(BAR(VF + st), KV_BYTES);
+            for (int b = 0; b < nboxes; ++b) {
+                const int y = __shfl_sync(0xffffffffu, y_cur, b);
+                if (lane == 0) {
+#pragma unroll
+                    for (int cb = 0; cb < CB; ++cb)
+                        tma_load_2d(smem_u32(Vs + st * KV_BYTES + cb * KVBLK + b * box_rows * 128), &tmV, BAR(VF + st), cb * 64, y);
+                }
+            }
+            y_cur = y_next;
+        }
+    } else if (warp == 0 && !AHEAD) {
+        // Few rows (decode steps, where the softmax threads set the pace): one thread looks pages up as it goes,
+        // which spaces the copies out; measured faster there than asking for both stages at once.
         if (lane == 0) {
             const int ps = p.page_size;
             const int box_rows = ps < BN ? ps : BN;
@@ -266,12 +340,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             }
         }
     } else if ((warp & 3) < nquarters) {
-        // softmax: two threads per row (warps w and w+4 reach the same 32 lanes of tensor memory); each
-        // owns one half of the tile's 128 score columns and one half of the output columns.  Only the row
+        // softmax: NP threads per row (warps w, w+4, w+8, ... reach the same 32 lanes of tensor memory); each
+        // owns one part of the tile's 128 score columns and one part of the output columns.  Only the row
         // maximum is exchanged per tile (shared memory + an mbarrier with a bounded wait); the row sums are
-        // added at the end.  A thread reads its 64 scores once (two tcgen05.ld, one wait) and keeps them in
-        // registers across the exchange.
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        // added at the end.  A thread reads its scores once and keeps them in registers across the exchange.
+        const int quarter = warp & 3, part = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const int row = row0 + r;
         const bool valid = row < nrows;
@@ -279,7 +352,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const int pos = valid ? ctx + tok : -1;
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        constexpr int SC = BN / 2, OC = D / 2;                          // score and output columns of this thread
+        constexpr int SC = BN / NP, OC = D / NP;                        // score and output columns of this thread
+        static_assert(SC == 32 && (OC == 32 || OC == 16), "one tcgen05.ld per tile for the scores and one for the output");
         float o[OC];
 #pragma unroll
         for (int i = 0; i < OC; ++i) o[i] = 0.f;
@@ -297,34 +371,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 // sees whole takes the path without compares
                 const int hi_col = valid ? pos - key0 : -1, lo_col = lo - key0;
                 const bool tile_full = __all_sync(0xffffffffu, valid && hi_col >= BN - 1 && lo_col <= 0);
-                uint32_t sv[2][32];
-                tmem_ld32(lane_addr + S_COL + sb * BN + half * SC, sv[0]);
-                tmem_ld32(lane_addr + S_COL + sb * BN + half * SC + 32, sv[1]);
+                uint32_t sv[SC];
+                tmem_ld32(lane_addr + S_COL + sb * BN + part * SC, sv);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(BAR(SE + sb));                              // the scores are in registers: the buffer is free
                 if (!tile_full) {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int col = half * SC + c * 32 + i;
-                            if (!(col <= hi_col && col >= lo_col)) sv[c][i] = 0xff800000u;       // -inf
-                        }
+                    for (int i = 0; i < SC; ++i) {
+                        const int col = part * SC + i;
+                        if (!(col <= hi_col && col >= lo_col)) sv[i] = 0xff800000u;                   // -inf
+                    }
                 }
-                float mx = -INFINITY;
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one
 #pragma unroll
-                for (int c = 0; c < 2; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
-                // exchange with the thread that owns the other half of the row (a bounded wait, not bar.sync:
+                for (int i = 0; i < SC; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                // exchange with the threads that own the other parts of the row (a bounded wait, not bar.sync:
                 // a warp that gave up elsewhere must not leave the others waiting for ever)
-                xch[j & 1][half][r] = mx;
+                xch[j & 1][part][r] = mx;
                 mbar_arrive(BAR(XB + (j & 1)));
                 ok = mbar_wait(BAR(XB + (j & 1)), (j >> 1) & 1, 11);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                mx = fmaxf(mx, xch[j & 1][half ^ 1][r]) * p.scale_log2;      // -inf stays -inf (the scale is positive)
+#pragma unroll
+                for (int k = 0; k < NP; ++k) mx = fmaxf(mx, xch[j & 1][k][r]);
+                mx *= p.scale_log2;                                      // -inf stays -inf (the scale is positive)
                 const float m_new = fmaxf(m_run, mx);
                 const float msub = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);
@@ -335,27 +407,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                     if (!ok) break;
                 }
                 // probabilities, rounded to bfloat16 into the operand layout; their sum in float32
-                float lsum = 0.f;
-                unsigned char* prow = Ps + half * QBLK + r * 128;        // this half's 64 keys are 64-key block `half`
+                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+                // this part's 32 keys are one half of 64-key block part / 2: chunks (part & 1) * 4 .. + 3 of the row
+                unsigned char* prow = Ps + (part >> 1) * QBLK + r * 128;
+                uint32_t packed[SC / 2];
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = ex2(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -msub));
-                        const float p1 = ex2(fmaf(__uint_as_float(sv[c][i + 1]), p.scale_log2, -msub));
-                        lsum += p0 + p1;
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-                    }
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const int cin = c * 4 + q4;
-                        *reinterpret_cast<uint4*>(prow + ((cin ^ (r & 7)) << 4)) =
-                            make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                    }
+                for (int i = 0; i < SC; i += 2) {
+                    const float p0 = ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -msub));
+                    const float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -msub));
+                    ls4[(i >> 1) & 3] += p0 + p1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
                 }
-                l_run = l_run * alpha + lsum;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int cin = (part & 1) * 4 + q4;
+                    *reinterpret_cast<uint4*>(prow + ((cin ^ (r & 7)) << 4)) =
+                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+                l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
                 m_run = m_new;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(BAR(PF));                                   // P is in shared memory
@@ -375,39 +445,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float f = j < ntiles ? alpha_prev : 1.f;
-                uint32_t ov[OC / 32][32];
-#pragma unroll
-                for (int c = 0; c < OC / 32; ++c) tmem_ld32(lane_addr + O_COL + ob * D + half * OC + c * 32, ov[c]);
+                uint32_t ov[OC];
+                tmem_ld_cols(lane_addr + O_COL + ob * D + part * OC, ov);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(BAR(OE + ob));
 #pragma unroll
-                for (int c = 0; c < OC / 32; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(__uint_as_float(ov[c][i]), f, o[c * 32 + i]);
+                for (int i = 0; i < OC; ++i) o[i] = fmaf(__uint_as_float(ov[i]), f, o[i]);
             }
         }
-        // the two halves of a row add their sums
+        // the parts of a row add their sums (in part order)
         float l_tot = 0.f;
         if (ok) {
-            xch[ntiles & 1][half][r] = l_run;                            // the buffer the last tile did not use
+            xch[ntiles & 1][part][r] = l_run;                            // the buffer the last tile did not use
             mbar_arrive(BAR(XL));
             ok = mbar_wait(BAR(XL), 0, 12);
-            l_tot = l_run + xch[ntiles & 1][half ^ 1][r];
+#pragma unroll
+            for (int k = 0; k < NP; ++k) l_tot += xch[ntiles & 1][k][r];
         }
         if (ok && valid && p.num_splits > 1) {
             const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
-            float* dst = p.ws_o + (grow * p.num_splits + split) * D + half * OC;
+            float* dst = p.ws_o + (grow * p.num_splits + split) * D + part * OC;
 #pragma unroll
             for (int i = 0; i < OC; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
-            if (half == 0) {
+            if (part == 0) {
                 float* ml = p.ws_ml + (grow * p.num_splits + split) * 2;
                 ml[0] = m_run * 0.6931471805599453f;                 // natural-log units for the merge
                 ml[1] = l_tot;
             }
         } else if (ok && valid) {
             const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            __nv_bfloat16* dst = p.out + ((size_t)(q0 + tok) * p.Hq + kvh * G + g) * D + half * OC;
+            __nv_bfloat16* dst = p.out + ((size_t)(q0 + tok) * p.Hq + kvh * G + g) * D + part * OC;
 #pragma unroll
             for (int i = 0; i < OC; i += 8) {
                 uint32_t w[4];
@@ -456,13 +524,13 @@ int make_page_map(CUtensorMap* map, const void* base, long long rows, int D, int
     return 0;
 }
 
-template <int D>
+template <int D, bool AHEAD>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, cudaStream_t s) {
     const size_t smem = (size_t)(D / 64) * BM * 128 + (size_t)(BN / 64) * BM * 128 + 4 * (size_t)(D / 64) * BN * 128 + 1024;
-    auto k = attn_tc_kernel<D>;
+    auto k = attn_tc_kernel<D, AHEAD>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-    k<<<dim3(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits), 320, smem, s>>>(mk, mv, p);
+    k<<<dim3(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits), NTHREADS, smem, s>>>(mk, mv, p);
     TTIE_CHECK_LAUNCH("attention_tc");
     return 0;
 }
@@ -511,7 +579,9 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("attention_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
-    const int rc = D == 64 ? launch<64>(mk, mv, p, s) : launch<128>(mk, mv, p, s);
+    const bool ahead = max_q_len * (Hq / Hkv) >= BM;             // full row tiles: a prompt portion
+    const int rc = D == 64 ? (ahead ? launch<64, true>(mk, mv, p, s) : launch<64, false>(mk, mv, p, s))
+                           : (ahead ? launch<128, true>(mk, mv, p, s) : launch<128, false>(mk, mv, p, s));
     if (rc) return rc;
     if (num_splits > 1) return attn_merge_bf16(p.ws_o, p.ws_ml, out, T * Hq, num_splits, D, s);
     return 0;
