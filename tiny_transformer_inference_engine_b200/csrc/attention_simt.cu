@@ -227,11 +227,53 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
     }
 }
 
+// Up to NS <= 32 splits: every thread asks for all (max, sum) pairs of its row and for its column of every split's
+// partial output at once, so the whole merge costs one memory latency; weights are computed redundantly per thread.
+template <typename T, int NS>
+__global__ void __launch_bounds__(128)
+attn_merge_small_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, T* __restrict__ out, int num_splits, int D) {
+    TTIE_PDL_ENTRY();
+    const size_t row = blockIdx.x;
+    const int d = blockIdx.y * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    const float2* ml = reinterpret_cast<const float2*>(ws_ml + row * num_splits * 2);
+    const float* o = ws_o + row * num_splits * D + d;
+    float2 v[NS];
+    float x[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        v[s] = s < num_splits ? ml[s] : make_float2(-INFINITY, 0.f);
+        x[s] = s < num_splits ? o[(size_t)s * D] : 0.f;
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) if (v[s].y > 0.f) M = fmaxf(M, v[s].x);
+    float acc = 0.f, den = 0.f;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {                               // fixed order
+        const float e = v[s].y > 0.f ? expf(v[s].x - M) : 0.f;
+        acc = fmaf(e, v[s].y > 0.f ? x[s] : 0.f, acc);
+        den = fmaf(e, v[s].y, den);
+    }
+    out[row * D + d] = from_f32<T>(den > 0.f ? acc / den : 0.f);
+}
+
 }  // namespace
 
 namespace ttie {
 int attn_merge_bf16(const float* ws_o, const float* ws_ml, void* out, int rows, int num_splits, int D, cudaStream_t s) {
-    TTIE_LAUNCH(attn_merge_kernel<__nv_bfloat16>, rows, D >= 128 ? 128 : 64, num_splits * sizeof(float), s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    const dim3 grid(rows, ceil_div(D, 128));
+    if (num_splits <= 4) {
+        TTIE_LAUNCH((attn_merge_small_kernel<__nv_bfloat16, 4>), grid, 128, 0, s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    } else if (num_splits <= 8) {
+        TTIE_LAUNCH((attn_merge_small_kernel<__nv_bfloat16, 8>), grid, 128, 0, s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    } else if (num_splits <= 16) {
+        TTIE_LAUNCH((attn_merge_small_kernel<__nv_bfloat16, 16>), grid, 128, 0, s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    } else if (num_splits <= 32) {
+        TTIE_LAUNCH((attn_merge_small_kernel<__nv_bfloat16, 32>), grid, 128, 0, s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    } else {
+        TTIE_LAUNCH(attn_merge_kernel<__nv_bfloat16>, rows, D >= 128 ? 128 : 64, num_splits * sizeof(float), s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+    }
     TTIE_CHECK_LAUNCH("attention merge");
     return 0;
 }

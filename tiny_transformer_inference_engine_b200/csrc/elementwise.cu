@@ -515,7 +515,7 @@ extern "C" int ttie_rope_table(const int* positions, const float* inv_freq, void
 // place) or float32 partial sums [S][T][width], of which a thread has up to four loads in flight.
 // cos/sin come from the step's table.
 template <typename T, bool PARTIAL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 rope_store_vec_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ part, int S, long long part_stride,
                       int Hq, int Hkv, int D, const int* __restrict__ positions, const int* __restrict__ token_seq,
                       const float2* __restrict__ cs, T* __restrict__ q_out, long long q_stride,
@@ -524,8 +524,8 @@ rope_store_vec_kernel(T* __restrict__ qkv, long long row_stride, const float* __
     TTIE_PDL_ENTRY();
     const int t = blockIdx.x;
     const int width = (Hq + 2 * Hkv) * D, half = D >> 1;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
-    if (c >= (width >> 2)) return;
+    // decode steps: one chunk per thread (grid y covers the row); prompt portions: one CTA walks the row
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < (width >> 2); c += gridDim.y * blockDim.x) {
     const int col = c << 2;
     const int h = col / D, i = col - h * D;
     float4 v;
@@ -550,7 +550,7 @@ rope_store_vec_kernel(T* __restrict__ qkv, long long row_stride, const float* __
     }
     if (h < Hq) {
         Vec4<T>::store(q_out + (long long)t * q_stride + col, v);
-        return;
+        continue;
     }
     if (!PARTIAL && h < Hq + Hkv) Vec4<T>::store(qkv + (long long)t * row_stride + col, v);
     if (write_kv) {
@@ -561,6 +561,7 @@ rope_store_vec_kernel(T* __restrict__ qkv, long long row_stride, const float* __
         const int hk = h < Hq + Hkv ? h - Hq : h - Hq - Hkv;
         T* dst = (h < Hq + Hkv ? k_pages : v_pages) + (page_base + (long long)hk * page_size) * D + i;
         Vec4<T>::store(dst, v);
+    }
     }
 }
 
@@ -578,7 +579,10 @@ extern "C" int ttie_rope_store_vec(void* qkv, long long row_stride, const float*
         TTIE_FAIL("rope_store_vec: pointers must be 16-byte aligned");
     if (row_stride % 4 || q_stride % 4 || part_stride % 4) TTIE_FAIL("rope_store_vec: strides must be multiples of 4");
     cudaStream_t s = (cudaStream_t)stream;
-#define TTIE_ROPE_VEC(TT, P) TTIE_LAUNCH((rope_store_vec_kernel<TT, P>), dim3(T, ceil_div((Hq + 2 * Hkv) * D / 4, 128)), 128, 0, s, (TT*)qkv, row_stride, part, S, part_stride, Hq, Hkv, D, \
+    const bool few = T <= 64;                                       // a decode step: spread a row over CTAs of 128 threads
+    const dim3 grid(T, few ? ceil_div((Hq + 2 * Hkv) * D / 4, 128) : 1);
+    const int threads = few ? 128 : 256;
+#define TTIE_ROPE_VEC(TT, P) TTIE_LAUNCH((rope_store_vec_kernel<TT, P>), grid, threads, 0, s, (TT*)qkv, row_stride, part, S, part_stride, Hq, Hkv, D, \
         positions, token_seq, (const float2*)cs, (TT*)q_out, q_stride, (TT*)k_pages, (TT*)v_pages, block_table, table_width, \
         page_size, num_pages, write_kv)
     if (dtype == kF32) { if (part) TTIE_ROPE_VEC(float, true); else TTIE_ROPE_VEC(float, false); }

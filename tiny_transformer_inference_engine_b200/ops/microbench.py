@@ -1,6 +1,6 @@
 """Per-kernel timings against their rooflines, at the sizes of a model configuration.
 
-    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|all]
+    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|all]
                                                                     [--batch 8] [--ctx 4096] [--tokens 2048]
 
 Every kernel is timed alone inside a captured CUDA graph of ``--iters`` launches (so the host's launch
@@ -153,6 +153,36 @@ def prefill(ops, a):
          flops=4 * Hq * D * T * (T + 1) // 2)
 
 
+def attention(ops, a):
+    """Decode attention over batch sizes and context lengths: the planned kernel beside the mma.sync tile loop
+    with split keys (the plan before the decode form and the tcgen05 splits existed)."""
+    Hq, Hkv, D, page = a.heads, a.kv_heads, a.d_model // a.heads, 64
+    print("== decode attention: planned kernel | mma.sync tile loop with split keys and merge")
+    batches = [int(v) for v in a.attn_batches.split(",")]
+    contexts = [int(v) for v in a.attn_contexts.split(",")] if a.attn_contexts else [512, 2048, a.ctx, 4 * a.ctx]
+    for B in batches:
+        for ctx in contexts:
+            nb = B * (ctx // page) + 1
+            kp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
+            vp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
+            table = (torch.arange(B * (ctx // page), device=DEV, dtype=torch.int32) + 1).view(B, -1)
+            q = torch.randn(B, Hq * D, device=DEV).bfloat16()
+            qsl = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+            sl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+            o = torch.empty(B, Hq * D, device=DEV, dtype=torch.bfloat16)
+            planned = ops.attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx, page)
+            keep = ops._cluster_plan, ops._tc_split_plan
+            ops._cluster_plan = ops._tc_split_plan = lambda *x: None
+            loop = ops.attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx, page)
+            ops._cluster_plan, ops._tc_split_plan = keep
+            for plan in (planned, loop):
+                us = timeit(lambda i: ops.paged_attention(q, Hq, Hkv, D, kp, vp, table, page, qsl, sl, B, 1, ctx, 1 / math.sqrt(D), 0, o, plan=plan))
+                line(f"batch {B:3d} context {ctx:6d} {plan}", us, bytes_=B * ctx * Hkv * D * 2 * 2)
+    err = ops.tc_error()
+    if err:
+        raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
+
+
 def gemm_tc(ops, a):
     d, F, Hq, Hkv, D = a.d_model, a.hidden, a.heads, a.kv_heads, a.d_model // a.heads
     M = a.tokens
@@ -170,7 +200,7 @@ def gemm_tc(ops, a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "all"))
+    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "all"))
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -179,6 +209,8 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=1)
     ap.add_argument("--hidden", type=int, default=11008)
     ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--attn-batches", default="1,8,64", help="batch sizes of --what attention")
+    ap.add_argument("--attn-contexts", default="", help="context lengths of --what attention (default 512, 2048, ctx, 4 ctx)")
     a = ap.parse_args(argv)
     ops = get_ops(DEV)
     if a.what in ("decode", "all"):
@@ -187,6 +219,8 @@ def main(argv=None):
         prefill(ops, a)
     if a.what in ("gemm_tc", "all"):
         gemm_tc(ops, a)
+    if a.what in ("attention", "all"):
+        attention(ops, a)
     return 0
 
 
