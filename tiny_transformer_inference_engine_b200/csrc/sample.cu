@@ -61,9 +61,12 @@ __device__ u64 block_sum_u64(u64 v, u64* scratch) {
     return r;
 }
 
+// staged: the row (divided by the temperature) lives in shared memory after the first pass, so the later passes
+// do not go back to global memory; a row too long for that is read from global memory every time.
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ slot_ids, int* __restrict__ state,
-              int* __restrict__ out, float* __restrict__ probs_out) {
+              int* __restrict__ out, float* __restrict__ probs_out, int staged) {
+    extern __shared__ __align__(16) float s_row[];
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ u64 s_u64[32];
@@ -71,7 +74,7 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     __shared__ unsigned s_prefix;
     __shared__ u64 s_acc;
     __shared__ int s_found;
-    __shared__ u64 s_scan[THREADS];
+    __shared__ u64 s_warp[THREADS / 32];
 
     TTIE_PDL_ENTRY();
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -82,11 +85,23 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     const float temperature = __int_as_float(st[4]), top_p = __int_as_float(st[5]);
     const int greedy = st[6];
 
-    // 1. maximum and the lowest index that holds it
+    // 1. maximum and the lowest index that holds it (and the row into shared memory)
     float best = -INFINITY; int best_i = 0x7fffffff;
-    for (int i = tid; i < V; i += THREADS) {
-        const float x = row[i];
-        if (x > best || (x == best && i < best_i)) { best = x; best_i = i; }
+    if (staged && (V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        for (int i = tid * 4; i < V; i += THREADS * 4) {
+            const float4 x = *reinterpret_cast<const float4*>(row + i);
+            *reinterpret_cast<float4*>(s_row + i) = x;
+            const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (xs[k] > best || (xs[k] == best && i + k < best_i)) { best = xs[k]; best_i = i + k; }
+        }
+    } else {
+        for (int i = tid; i < V; i += THREADS) {
+            const float x = row[i];
+            if (staged) s_row[i] = x;
+            if (x > best || (x == best && i < best_i)) { best = x; best_i = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -115,6 +130,11 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
         return;
     }
     const float ymax = best / temperature;
+    if (staged) {
+        for (int i = tid; i < V; i += THREADS) s_row[i] = s_row[i] / temperature;
+        __syncthreads();
+    }
+    auto Y = [&](int i) -> float { return staged ? s_row[i] : row[i] / temperature; };
 
     // 2. top-k threshold: the k-th largest key, by radix select over 4 digits of 8 bits
     unsigned cut_key = 0;
@@ -124,7 +144,7 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
             for (int b = tid; b < 256; b += THREADS) s_hist[b] = 0;
             __syncthreads();
             for (int i = tid; i < V; i += THREADS) {
-                const unsigned key = ordered_key(row[i] / temperature);
+                const unsigned key = ordered_key(Y(i));
                 if (shift == 24 || (key >> (shift + 8)) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], (u64)1);
             }
             __syncthreads();
@@ -148,7 +168,7 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     if (top_p < 1.0f) {
         u64 z = 0;
         for (int i = tid; i < V; i += THREADS) {
-            const float y = row[i] / temperature;
+            const float y = Y(i);
             if (ordered_key(y) >= cut_key) z += mass_of(y, ymax);
         }
         z = block_sum_u64(z, s_u64);
@@ -158,7 +178,7 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
             for (int b = tid; b < 256; b += THREADS) s_hist[b] = 0;
             __syncthreads();
             for (int i = tid; i < V; i += THREADS) {
-                const float y = row[i] / temperature;
+                const float y = Y(i);
                 const unsigned key = ordered_key(y);
                 if (key >= cut_key && (shift == 24 || (key >> (shift + 8)) == prefix))
                     atomicAdd(&s_hist[(key >> shift) & 255u], mass_of(y, ymax));
@@ -180,24 +200,36 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
         if (prefix > cut_key) cut_key = prefix;
     }
 
-    // 4. draw: inverse CDF in index order over the kept tokens
-    const int chunk = (V + THREADS - 1) / THREADS;
+    // 4. draw: inverse CDF in index order over the kept tokens.  A thread owns a run of consecutive tokens (an odd
+    // number of them, so the threads of a warp read different banks of the staged row).
+    const int chunk = ((V + THREADS - 1) / THREADS) | 1;
     const int i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
     u64 local = 0;
     for (int i = i0; i < i1; ++i) {
-        const float y = row[i] / temperature;
+        const float y = Y(i);
         if (ordered_key(y) >= cut_key) local += mass_of(y, ymax);
     }
-    s_scan[tid] = local;
-    __syncthreads();
-    // inclusive scan over 1024 partial sums (Hillis-Steele on integers: exact)
-    for (int off = 1; off < THREADS; off <<= 1) {
-        const u64 add = tid >= off ? s_scan[tid - off] : 0;
-        __syncthreads();
-        s_scan[tid] += add;
-        __syncthreads();
+    // inclusive scan of the threads' sums: inside each warp by shuffles, then over the warps' totals (integers: exact)
+    u64 incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const u64 up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
     }
-    const u64 total = s_scan[THREADS - 1];
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        u64 w = s_warp[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const u64 up = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += up;
+        }
+        s_warp[lane] = w;
+    }
+    __syncthreads();
+    incl += warp ? s_warp[warp - 1] : 0;
+    const u64 total = s_warp[THREADS / 32 - 1];
     unsigned rnd[4];
     philox4x32_10(draws, 0u, 0u, 0u, seed_lo, seed_hi, rnd);
     const double u = (double)(rnd[0] >> 8) * (1.0 / 16777216.0);
@@ -205,11 +237,11 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     if (target >= total) target = total ? total - 1 : 0;
     if (tid == 0) s_found = best_i;                                   // total == 0 cannot happen (the maximum has mass 2^40)
     __syncthreads();
-    const u64 before = s_scan[tid] - local;
+    const u64 before = incl - local;
     if (local > 0 && target >= before && target < before + local) {
         u64 c = before;
         for (int i = i0; i < i1; ++i) {
-            const float y = row[i] / temperature;
+            const float y = Y(i);
             if (ordered_key(y) >= cut_key) {
                 c += mass_of(y, ymax);
                 if (target < c) { s_found = i; break; }
@@ -221,7 +253,7 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     if (probs_out) {
         const double inv = total ? 1.0 / (double)total : 0.0;
         for (int i = tid; i < V; i += THREADS) {
-            const float y = row[i] / temperature;
+            const float y = Y(i);
             probs_out[(size_t)r * V + i] = ordered_key(y) >= cut_key ? (float)((double)mass_of(y, ymax) * inv) : 0.f;
         }
     }
@@ -232,7 +264,13 @@ extern "C" int ttie_sample(const float* logits, int R, int V, const int* slot_id
                            float* probs_out, void* stream) {
     if (R <= 0) return 0;
     if (V <= 0) TTIE_FAIL("sample: empty vocabulary");
-    TTIE_LAUNCH(sample_kernel, R, THREADS, 0, (cudaStream_t)stream, logits, V, slot_ids, state, out, probs_out);
+    // the row in shared memory when it fits beside the kernel's own (200 KB: 51,200 tokens)
+    const size_t smem = (size_t)V * sizeof(float);
+    const int staged = smem <= 200 * 1024;
+    if (staged && smem > 40 * 1024 &&
+        cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        TTIE_FAIL("sample: 200 KB of shared memory refused");
+    TTIE_LAUNCH(sample_kernel, R, THREADS, staged ? smem : 0, (cudaStream_t)stream, logits, V, slot_ids, state, out, probs_out, staged);
     TTIE_CHECK_LAUNCH("sample");
     return 0;
 }
