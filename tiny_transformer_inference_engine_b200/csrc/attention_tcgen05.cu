@@ -25,6 +25,7 @@ constexpr int BM = 128, BN = 128;
 constexpr long long WAIT_CYCLES = 2000000000LL;
 
 __device__ int g_attn_tc_error = 0;
+__device__ int* g_attn_tc_error_mirror = nullptr;                // the same word in pinned host memory, if the host gave one
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -46,7 +47,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
     if (mbar_try(bar, parity)) return true;
     const long long deadline = clock64() + WAIT_CYCLES;
     while (!mbar_try(bar, parity)) {
-        if (clock64() > deadline) { atomicCAS(&g_attn_tc_error, 0, code); return false; }
+        if (clock64() > deadline) {
+            atomicCAS(&g_attn_tc_error, 0, code);
+            if (g_attn_tc_error_mirror) { *reinterpret_cast<volatile int*>(g_attn_tc_error_mirror) = code; __threadfence_system(); }
+            return false;
+        }
     }
     return true;
 }
@@ -57,7 +62,11 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
     const long long deadline = clock64() + WAIT_CYCLES;
     while (!mbar_try(bar, parity)) {
         __nanosleep(64);
-        if (clock64() > deadline) { atomicCAS(&g_attn_tc_error, 0, code); return false; }
+        if (clock64() > deadline) {
+            atomicCAS(&g_attn_tc_error, 0, code);
+            if (g_attn_tc_error_mirror) { *reinterpret_cast<volatile int*>(g_attn_tc_error_mirror) = code; __threadfence_system(); }
+            return false;
+        }
     }
     return true;
 }
@@ -535,6 +544,12 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, 
     return 0;
 }
 }  // namespace
+
+// A word of pinned host memory (device-accessible) that also receives the failure code, so the host can look at it
+// after every step without a call into the runtime.  nullptr: none.
+extern "C" int ttie_attn_tc_set_mirror(int* host_word) {
+    return cudaMemcpyToSymbol(g_attn_tc_error_mirror, &host_word, sizeof(int*)) == cudaSuccess ? 0 : 1;
+}
 
 extern "C" int ttie_attn_tc_error() {
     int v = 0, zero = 0;

@@ -22,6 +22,7 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr long long WAIT_CYCLES = 2000000000LL;            // about one second
 
 __device__ int g_tc_error = 0;                             // first failure code of any launch since the last read
+__device__ int* g_tc_error_mirror = nullptr;                // the same word in pinned host memory, if the host gave one
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -42,7 +43,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
     if (mbar_try(bar, parity)) return true;
     const long long deadline = clock64() + WAIT_CYCLES;
     while (!mbar_try(bar, parity)) {
-        if (clock64() > deadline) { atomicCAS(&g_tc_error, 0, code); return false; }
+        if (clock64() > deadline) {
+            atomicCAS(&g_tc_error, 0, code);
+            if (g_tc_error_mirror) { *reinterpret_cast<volatile int*>(g_tc_error_mirror) = code; __threadfence_system(); }
+            return false;
+        }
     }
     return true;
 }
@@ -289,6 +294,12 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const TcParams& p, cudaSt
 
 // Reads and clears the error word of the tensor-core kernels (0: none; 1 producer, 2 issuer, 3 epilogue
 // wait ran out).  Synchronises the device.
+// A word of pinned host memory (device-accessible) that also receives the failure code, so the host can look at it
+// after every step without a call into the runtime.  nullptr: none.
+extern "C" int ttie_gemm_tc_set_mirror(int* host_word) {
+    return cudaMemcpyToSymbol(g_tc_error_mirror, &host_word, sizeof(int*)) == cudaSuccess ? 0 : 1;
+}
+
 extern "C" int ttie_tc_error() {
     int v = 0, zero = 0;
     cudaDeviceSynchronize();

@@ -40,6 +40,7 @@ class BatchPacker:
         self._dev = None
         self._cap = 0
         self._copied = None            # event: the last host-to-device copy has read the host buffer
+        self._last = None              # layout of the last fixed-layout decode step (see _repack_decode)
 
     def _ensure(self, n: int):
         if n > self._cap:
@@ -80,12 +81,59 @@ class BatchPacker:
                     raise ValueError(f"request {en.rid!r}: block table of group {gi} does not cover "
                                      f"positions {en.start}..{en.start + n - 1}")
 
+    def _repack_decode(self, entries: List[StepEntry], key) -> bool:
+        """A decode step of the same requests in the same order and layout as the last packed one: only the
+        tokens, positions, lengths and newly appended pages are written into the host buffer (which still holds
+        the rest), with the checks of ``validate`` on what changes.  False: not that case, pack in full."""
+        st = self._last
+        if st is None or st["key"] != key:
+            return False
+        mgr, hn = self.manager, st["hn"]
+        if self._copied is not None:
+            self._copied.synchronize()
+        o_tok, o_pos, o_seql = st["o_tok"], st["o_pos"], st["o_seql"]
+        for i, en in enumerate(entries):
+            tok, start = int(en.tokens[0]), en.start
+            if not 0 <= tok < self.vocab_size:
+                raise ValueError(f"request {en.rid!r}: token id {tok} outside [0, {self.vocab_size})")
+            if start < 0 or start >= self.max_seq_len:
+                raise ValueError(f"request {en.rid!r}: positions {start}..{start} exceed max_seq_len={self.max_seq_len}")
+            hn[o_tok + i] = tok
+            hn[o_pos + i] = start
+            hn[o_seql + i] = start + 1
+            for gi, g in enumerate(mgr.groups):
+                table = g.tables.get(en.rid)
+                if table is None:
+                    raise KeyError(f"request {en.rid!r} is not admitted")
+                have = st["tlen"][gi][i]
+                if len(table) * g.page_size <= start or len(table) < have or len(table) > st["widths"][gi]:
+                    raise ValueError(f"request {en.rid!r}: block table of group {gi} does not cover positions {start}..{start}")
+                if len(table) != have:
+                    new = table[have:]
+                    if min(new) <= 0 or max(new) >= g.num_pages:
+                        raise ValueError(f"request {en.rid!r}: block table of group {gi} does not cover positions {start}..{start}")
+                    off = st["o_tab"][gi] + i * st["widths"][gi]
+                    hn[off + have:off + len(table)] = new
+                    st["tlen"][gi][i] = len(table)
+        total = st["total"]
+        st["dev"][:total].copy_(st["host"][:total], non_blocking=True)
+        self._copied.record()
+        return True
+
     def pack(self, entries: List[StepEntry], pad_seqs: int = 0, pages_per_seq: Optional[Dict[int, int]] = None,
              buffers=None, copy_only: bool = False) -> Optional[StepContext]:
         """``pad_seqs``/``pages_per_seq``/``buffers`` give a fixed layout (for a captured
         graph): the batch is padded to ``pad_seqs`` one-token requests that sit on the
         scratch page with length 1, and the tables get ``pages_per_seq[group]`` columns.
         ``copy_only``: fill and copy the buffer but build no context (a graph replay needs none)."""
+        key = None
+        if (copy_only and buffers is not None and self.device.type == "cuda"
+                and all(len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e in entries)
+                and all(g.window is None for g in self.manager.groups)):
+            key = (tuple(e.rid for e in entries), pad_seqs, tuple(sorted(pages_per_seq.items())), buffers[0].data_ptr())
+            if self._repack_decode(entries, key):
+                return None
+        self._last = None
         self.validate(entries)
         mgr = self.manager
         N_real = len(entries)
@@ -143,6 +191,10 @@ class BatchPacker:
             if self._copied is None:
                 self._copied = torch.cuda.Event()
             self._copied.record()
+        if key is not None:
+            self._last = {"key": key, "hn": hn, "host": host, "dev": dev, "total": total, "o_tok": offs[0], "o_pos": offs[1],
+                          "o_seql": offs[4], "o_tab": offs[7:], "widths": widths,
+                          "tlen": [[len(t) for t in rows_] for rows_ in tables]}
         if copy_only:
             return None
 

@@ -61,6 +61,7 @@ class Engine:
         graphs = ec.sched.cudagraph_batch_sizes if (ec.use_cuda_graphs and self.device.type == "cuda") else []
         self.stepper = Stepper(self.model, self.manager, ops, self.dtype, self.device, graphs)
         self.sampler = Sampler(ops, ec.sched.max_num_seqs, config.vocab_size, self.device)
+        self._slot_ids = None
         self.scheduler = Scheduler(self.manager, ec.sched, config.max_seq_len, config.eos_token_id)
         self._requests: Dict[int, object] = {}
 
@@ -102,7 +103,10 @@ class Engine:
         logits = self.stepper.step(entries)
         slots = [self.manager.slot_of[e.rid] for e in entries if e.want]
         if slots:
-            slot_ids = torch.tensor(slots, dtype=torch.int32).to(self.device, non_blocking=True)
+            key = tuple(slots)
+            if self._slot_ids is None or self._slot_ids[0] != key:          # the same requests step after step: one upload
+                self._slot_ids = (key, torch.tensor(slots, dtype=torch.int32).to(self.device))
+            slot_ids = self._slot_ids[1]
             tokens = self.sampler.sample(logits[:len(slots)], slot_ids).tolist()       # one device-to-host read
         else:
             tokens = []

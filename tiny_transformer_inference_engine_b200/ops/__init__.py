@@ -84,7 +84,6 @@ class CudaOps:
             fn.argtypes, fn.restype = argtypes, _c_int
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
-        self.tc_used = False                  # a tcgen05 kernel ran since the error word was last read
         self.attn_target_ctas = 4 * NUM_SMS      # decode tiles are small: four CTAs share an SM
         self.attn_cluster_max_rows = 64         # query rows per request (tokens x heads per kv head) up to which the decode form runs
         self.attn_cluster_max_size = 8          # CTAs per cluster (16 is placed on fewer SMs at a time)
@@ -94,6 +93,13 @@ class CudaOps:
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
         self.lib.ttie_attn_tc_supported.restype = _c_int
+        self._tc_pinned = torch.zeros(2, dtype=torch.int32).pin_memory()       # failure codes of the tcgen05 kernels, written by the device
+        self._tc_words = self._tc_pinned.numpy()
+        for i, name in enumerate(("ttie_gemm_tc_set_mirror", "ttie_attn_tc_set_mirror")):
+            fn = getattr(self.lib, name)
+            fn.argtypes, fn.restype = [_c_void], _c_int
+            if fn(self._tc_pinned.data_ptr() + 4 * i):
+                raise KernelError(f"{name} failed")
         for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows", "ttie_attn_cluster_tile_rows", "ttie_attn_cluster_active"):
             getattr(self.lib, name).restype = _c_int
 
@@ -208,7 +214,6 @@ class CudaOps:
         M, K = x.shape
         N = w.shape[0]
         out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
-        self.tc_used = True
         self._check(self.lib.ttie_gemm_tc(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), out.stride(0),
                                           M, N, K, 1 if out.dtype == torch.float32 else 0, tile_n, self._stream(x)), "gemm_tc")
         self.launches += 1
@@ -222,13 +227,14 @@ class CudaOps:
         return g or (100 + a if a else 0)
 
     def check_tc(self):
-        """After a point where the host has waited for the device: raises if a bounded wait inside a
-        tcgen05 kernel launched since the last check ran out (its result is then not to be trusted)."""
-        if self.tc_used:
-            self.tc_used = False
-            code = self.tc_error()
-            if code:
-                raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {code}); its output is invalid")
+        """After a point where the host has waited for the device: raises if a bounded wait inside a tcgen05
+        kernel ran out since the last check (its result is then not to be trusted).  The kernels also write
+        their failure code into two words of pinned host memory, so this costs two loads - it is called
+        after every step, graph replays included."""
+        if self._tc_words[0] or self._tc_words[1]:
+            self._tc_words[:] = 0
+            code = self.tc_error() or -1
+            raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {code}); its output is invalid")
 
     def linear_swiglu(self, x, w_gu, b_gu, hidden):
         """silu(x @ Wg.T) * (x @ Wu.T) with w_gu = [Wg; Wu] ([2*hidden, K]) -> [M, hidden]."""
@@ -369,7 +375,6 @@ class CudaOps:
         kernel, num_splits, split_len = plan if plan is not None else self.attention_plan(
             qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
         if kernel == "tc":
-            self.tc_used = True
             scratch = None
             if num_splits > 1:
                 scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
