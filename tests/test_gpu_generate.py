@@ -54,3 +54,40 @@ def test_sampling_does_not_depend_on_batch():
     assert all(len(o) == 24 for o in together)
     assert together == alone
     assert eng.manager.num_free_pages == eng.manager.num_usable_pages
+
+
+def test_graph_replays_match_whole_prompts_bfloat16():
+    """Captured decode steps in bfloat16 against the same engine without graphs running every request whole.
+    Requests of different lengths end at different steps (the batch shrinks and changes its graph bucket),
+    contexts cross page boundaries while steps are replayed (the incremental repacking of a steady decode
+    step), and with 16 heads of size 64 on one kv head both decode attention kernels run inside graphs: the
+    kernels of a graph are planned for the longest context, 4,096 keys, which is the tcgen05 kernel with
+    split keys; the eager steps of the short requests take the cluster form."""
+    from trace_util import run_steps, whole, worst_relative
+    from gpu_util import TOL
+    cfg = dict(architecture="mqa_gpt", vocab_size=300, d_model=1024, num_layers=2, num_heads=16, num_kv_heads=1,
+               hidden_size=320, max_seq_len=4096, rope_theta=10000.0, rms_norm_eps=1e-5, bias=False,
+               eos_token_id=None, dtype="bfloat16")
+    g = torch.Generator().manual_seed(5)
+    prefix = {"a": 2300, "b": 40, "c": 700, "d": 9}
+    tail = {"a": 70, "b": 33, "c": 50, "d": 12}
+    reqs = {r: torch.randint(0, 300, (prefix[r] + tail[r],), generator=g).tolist() for r in prefix}
+    eager, w = make_engine(cfg, 3, 64, 80, "bfloat16", max_seqs=4, budget=4096, graphs=False)
+    ref = run_steps(eager, whole(reqs))
+    expected = {r: [ref[(r, i)] for i in range(len(t))] for r, t in reqs.items()}
+    steps = [{"entries": [{"id": r, "tokens": t[:prefix[r]], "want": [prefix[r] - 1]}], "end": []} for r, t in reqs.items()]
+    fed = dict(prefix)
+    while fed:
+        entries = [{"id": r, "tokens": reqs[r][fed[r]:fed[r] + 1], "want": [0]} for r in fed]
+        for r in fed:
+            fed[r] += 1
+        end = [r for r in fed if fed[r] == len(reqs[r])]
+        steps.append({"entries": entries, "end": end})
+        for r in end:
+            del fed[r]
+    graphs, _ = make_engine(cfg, 3, 64, 80, "bfloat16", max_seqs=4, budget=4096, graphs=True, weights=w, cudagraph_batch_sizes=[1, 2, 4])
+    got = run_steps(graphs, steps)
+    assert graphs.stats()["step_graph_replays"] == 70
+    assert {graphs.ops.attention_plan(torch.bfloat16, 4, 16, 1, 64, 1, n, 64)[0] for n in (300, 4096)} == {"mma_c4", "tc"}
+    worst, where = worst_relative(got, expected)
+    assert worst < TOL["bfloat16"], (worst, where)
