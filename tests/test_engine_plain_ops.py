@@ -39,3 +39,61 @@ def test_cutting_does_not_change_logits(name, cfg, lens, mode):
     assert len(got) == sum(len(t) for t in reqs.values())
     worst, where = tu.worst_relative(got, expected)
     assert worst < 1e-5, (worst, where)
+
+
+def test_steady_decode_steps_repack_to_the_same_buffer():
+    """A decode step of the same requests in the same fixed layout rewrites only what changed; the device
+    buffer must equal a full packing of the same step, across page boundaries, and a changed request set,
+    a bad token or a table that does not cover the position must not slip through."""
+    from tiny_transformer_inference_engine_b200.engine.batch import StepEntry
+    eng, _ = make(TINY_A, SEEDS["A"], 4, 40)
+    mgr, packer = eng.manager, eng.stepper.packer
+    pages = {gi: -(-TINY_A["max_seq_len"] // g.page_size) for gi, g in enumerate(mgr.groups)}
+    words = 8 * (4 + 4) + sum(4 * w + 4 for w in pages.values()) + 64
+
+    def buffers():
+        return torch.zeros(words, dtype=torch.int32), torch.zeros(words, dtype=torch.int32)
+
+    lengths = {"a": 3, "b": 7, "c": 1}
+    for rid, n in lengths.items():
+        mgr.admit(rid)
+        mgr.extend(rid, 0, n)
+    fast, full = buffers(), buffers()
+    short = []
+    repack = packer._repack_decode
+    packer._repack_decode = lambda entries, key: short.append(repack(entries, key)) or short[-1]
+    g = torch.Generator().manual_seed(1)
+    for step in range(14):                                           # pages of 4 tokens: every request crosses several
+        entries = []
+        for rid in lengths:
+            mgr.extend(rid, lengths[rid], lengths[rid] + 1)
+            entries.append(StepEntry(rid, lengths[rid], [int(torch.randint(0, 256, (1,), generator=g))], [0]))
+            lengths[rid] += 1
+        packer.pack(entries, pad_seqs=4, pages_per_seq=pages, buffers=fast, copy_only=True)
+        assert short[-1] == (step > 0)                                # every step but the first takes the short path
+        saved, packer._last = packer._last, None                     # a full packing into other buffers, then back
+        packer.pack(entries, pad_seqs=4, pages_per_seq=pages, buffers=full, copy_only=True)
+        packer._last = saved
+        assert torch.equal(fast[1], full[1]), step
+    # one request leaves: the layout key changes and the step is packed in full again
+    mgr.release("b")
+    del lengths["b"]
+    entries = []
+    for rid in lengths:
+        mgr.extend(rid, lengths[rid], lengths[rid] + 1)
+        entries.append(StepEntry(rid, lengths[rid], [5], [0]))
+    packer.pack(entries, pad_seqs=4, pages_per_seq=pages, buffers=fast, copy_only=True)
+    packer._last, saved = None, packer._last
+    packer.pack(entries, pad_seqs=4, pages_per_seq=pages, buffers=full, copy_only=True)
+    packer._last = saved
+    assert torch.equal(fast[1], full[1])
+    # the checks of a full packing hold on the short path too
+    nxt = [StepEntry(rid, lengths[rid] + 1, [5], [0]) for rid in lengths]
+    for rid in lengths:
+        mgr.extend(rid, lengths[rid] + 1, lengths[rid] + 2)
+    bad = [StepEntry(nxt[0].rid, nxt[0].start, [256], [0])] + nxt[1:]
+    with pytest.raises(ValueError):
+        packer.pack(bad, pad_seqs=4, pages_per_seq=pages, buffers=fast, copy_only=True)
+    far = [StepEntry(nxt[0].rid, nxt[0].start + 9, [5], [0])] + nxt[1:]
+    with pytest.raises(ValueError):
+        packer.pack(far, pad_seqs=4, pages_per_seq=pages, buffers=fast, copy_only=True)

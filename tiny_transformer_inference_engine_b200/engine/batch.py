@@ -117,7 +117,8 @@ class BatchPacker:
                     st["tlen"][gi][i] = len(table)
         total = st["total"]
         st["dev"][:total].copy_(st["host"][:total], non_blocking=True)
-        self._copied.record()
+        if self._copied is not None:
+            self._copied.record()
         return True
 
     def pack(self, entries: List[StepEntry], pad_seqs: int = 0, pages_per_seq: Optional[Dict[int, int]] = None,
@@ -127,7 +128,7 @@ class BatchPacker:
         scratch page with length 1, and the tables get ``pages_per_seq[group]`` columns.
         ``copy_only``: fill and copy the buffer but build no context (a graph replay needs none)."""
         key = None
-        if (copy_only and buffers is not None and self.device.type == "cuda"
+        if (copy_only and buffers is not None
                 and all(len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e in entries)
                 and all(g.window is None for g in self.manager.groups)):
             key = (tuple(e.rid for e in entries), pad_seqs, tuple(sorted(pages_per_seq.items())), buffers[0].data_ptr())
