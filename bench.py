@@ -157,8 +157,9 @@ def decode_kernel_path(eng, batch, start_len, steps, warmup, vocab, synthetic_fi
         for rid in rids:
             mgr.extend(rid, pos[0], pos[0] + 1)
         entries = [StepEntry(rid, pos[0], [tokens[base + i][j]], [0]) for j, rid in enumerate(rids)]
-        logits = eng.stepper.step(entries)
-        eng.sampler.sample(logits, slot_ids)
+        logits = eng.stepper.step(entries, eng.sampler)         # a captured step samples inside its graph
+        if eng.stepper.last_tokens is None:
+            eng.sampler.sample(logits, slot_ids)
         pos[0] += 1
 
     for i in range(warmup):

@@ -79,6 +79,10 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     TTIE_PDL_ENTRY();
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* row = logits + (size_t)r * V;
+    if (slot_ids[r] < 0) {                                            // a padding row of a fixed-size batch: no request, no draw
+        if (tid == 0) out[r] = 0;
+        return;
+    }
     int* st = state + (size_t)slot_ids[r] * 8;
     const unsigned seed_lo = (unsigned)st[0], seed_hi = (unsigned)st[1], draws = (unsigned)st[2];
     const int top_k = st[3];

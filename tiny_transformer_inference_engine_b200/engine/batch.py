@@ -153,7 +153,7 @@ class BatchPacker:
             slots.append(mgr.slot_of[en.rid])
             rows.extend(base + int(w) for w in en.want)
         for i in range(N_real, N):
-            tok.append(0); pos.append(0); tseq.append(i); rows.append(qsl[-1]); qsl.append(qsl[-1] + 1); seql.append(1); slots.append(0)
+            tok.append(0); pos.append(0); tseq.append(i); rows.append(qsl[-1]); qsl.append(qsl[-1] + 1); seql.append(1); slots.append(-1)
         R = len(rows)
         tables, widths = [], []
         for gi, g in enumerate(mgr.groups):

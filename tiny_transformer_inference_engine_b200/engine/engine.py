@@ -100,16 +100,18 @@ class Engine:
         for r in sched.running:
             if r.rid not in before or r.num_cached == 0:
                 self.sampler.set_request(self.manager.slot_of[r.rid], r.params, draws_so_far=len(r.output))
-        logits = self.stepper.step(entries)
-        slots = [self.manager.slot_of[e.rid] for e in entries if e.want]
-        if slots:
-            key = tuple(slots)
-            if self._slot_ids is None or self._slot_ids[0] != key:          # the same requests step after step: one upload
-                self._slot_ids = (key, torch.tensor(slots, dtype=torch.int32).to(self.device))
-            slot_ids = self._slot_ids[1]
-            tokens = self.sampler.sample(logits[:len(slots)], slot_ids).tolist()       # one device-to-host read
+        logits = self.stepper.step(entries, self.sampler)
+        if self.stepper.last_tokens is not None:                                        # a captured decode step sampled in its graph
+            tokens = self.stepper.last_tokens.tolist()                                  # one device-to-host read
         else:
-            tokens = []
+            slots = [self.manager.slot_of[e.rid] for e in entries if e.want]
+            if slots:
+                key = tuple(slots)
+                if self._slot_ids is None or self._slot_ids[0] != key:                  # the same requests step after step: one upload
+                    self._slot_ids = (key, torch.tensor(slots, dtype=torch.int32).to(self.device))
+                tokens = self.sampler.sample(logits[:len(slots)], self._slot_ids[1]).tolist()
+            else:
+                tokens = []
         if hasattr(self.ops, "check_tc"):
             self.ops.check_tc()
         return sched.update(entries, tokens)

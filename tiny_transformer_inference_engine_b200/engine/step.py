@@ -23,8 +23,9 @@ from ..models.model import Model
 
 
 class _DecodeGraph:
-    def __init__(self, bucket, host, dev, graph, logits, ctx, launches):
+    def __init__(self, bucket, host, dev, graph, logits, tokens, ctx, launches):
         self.bucket, self.host, self.dev, self.graph, self.logits, self.ctx = bucket, host, dev, graph, logits, ctx
+        self.tokens = tokens                # sampled tokens [bucket] if the graph samples, else None
         self.launches = launches            # kernels of this package inside the graph (counted while capturing)
 
 
@@ -35,13 +36,17 @@ class Stepper:
         self.device = torch.device(device)
         self.packer = BatchPacker(manager, ops, dtype, device, model.spec.vocab_size, model.spec.max_seq_len)
         self.graph_batch_sizes = sorted(graph_batch_sizes or [])
-        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graphs: Dict[tuple, _DecodeGraph] = {}
         self.counters = {"steps": 0, "tokens": 0, "graph_replays": 0}
+        self.last_tokens: Optional[torch.Tensor] = None      # tokens sampled inside the last step's graph, or None
 
     # ---------------------------------------------------------------- plain step
     @torch.no_grad()
-    def step(self, entries: List[StepEntry]) -> torch.Tensor:
-        """Logits (float32, [sum of wants, vocab]) in the order of the entries and of ``want``."""
+    def step(self, entries: List[StepEntry], sampler=None) -> torch.Tensor:
+        """Logits (float32, [sum of wants, vocab]) in the order of the entries and of ``want``.
+        With a ``sampler`` a captured decode step also samples (the kernel is part of the graph) and leaves the
+        tokens in ``last_tokens``; any other step leaves None there and the caller samples from the logits."""
+        self.last_tokens = None
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
         self.counters["steps"] += 1
@@ -49,7 +54,7 @@ class Stepper:
         if self.graph_batch_sizes and self._is_decode(entries):
             bucket = next((b for b in self.graph_batch_sizes if b >= len(entries)), None)
             if bucket is not None:
-                return self._step_graph(entries, bucket)
+                return self._step_graph(entries, bucket, sampler)
         ctx = self.packer.pack(entries)
         views = self.manager.views(ctx.block_tables)
         return self.model.forward(ctx, views)
@@ -62,9 +67,9 @@ class Stepper:
     def _fixed_pages(self) -> Dict[int, int]:
         return {gi: -(-self.model.spec.max_seq_len // g.page_size) for gi, g in enumerate(self.manager.groups)}
 
-    def _step_graph(self, entries, bucket: int) -> torch.Tensor:
+    def _step_graph(self, entries, bucket: int, sampler=None) -> torch.Tensor:
         n = len(entries)
-        g = self._graphs.get(bucket)
+        g = self._graphs.get((bucket, sampler is not None))
         pages = self._fixed_pages()
         if g is None:
             words = 8 * (bucket + 4) + sum(bucket * w + 4 for w in pages.values()) + 64
@@ -79,13 +84,16 @@ class Stepper:
             ctx.step_cache.clear()                              # what parts computed once per step is computed again inside the graph
             graph = torch.cuda.CUDAGraph()
             before = getattr(self.ops, "launches", 0)
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph):                       # (capturing runs nothing: no draw is counted here)
                 logits = self.model.forward(ctx, views)
-            g = _DecodeGraph(bucket, host, dev, graph, logits, ctx, getattr(self.ops, "launches", 0) - before)
-            self._graphs[bucket] = g
+                tokens = sampler.sample(logits, ctx.slot_ids) if sampler is not None else None
+            g = _DecodeGraph(bucket, host, dev, graph, logits, tokens, ctx, getattr(self.ops, "launches", 0) - before)
+            self._graphs[(bucket, sampler is not None)] = g
         self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(g.host, g.dev), copy_only=True)
         g.graph.replay()
         if hasattr(self.ops, "launches"):
             self.ops.launches += g.launches
         self.counters["graph_replays"] += 1
+        if g.tokens is not None:
+            self.last_tokens = g.tokens[:n]
         return g.logits[:n]

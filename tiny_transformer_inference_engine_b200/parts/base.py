@@ -127,7 +127,7 @@ class StepContext:
     token_seq: torch.Tensor            # [T] index of the token's request in this step
     query_start_loc: torch.Tensor      # [N+1]
     seq_lens: torch.Tensor             # [N] keys visible to the request's last token (cache length after the step)
-    slot_ids: torch.Tensor             # [N] state slot of each request
+    slot_ids: torch.Tensor             # [N] state slot of each request; -1 for the padding rows of a fixed-size (captured) batch
     logit_rows: torch.Tensor           # [R] flat token indices whose logits are wanted
     num_logit_rows: int
     block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)   # cache group -> [N, max_pages]
