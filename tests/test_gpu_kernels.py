@@ -299,7 +299,7 @@ def sampler_state(rows):
     return st
 
 
-@pytest.mark.parametrize("V", [256, 1000, 32000, 65024])
+@pytest.mark.parametrize("V", [256, 515, 1000, 32000, 65024])
 def test_sampling_distribution_and_draw(ops, V):
     g = torch.Generator().manual_seed(V)
     rows = [(1, 0, 0, 1.0, 1.0, 0), (2, 5, 32, 0.8, 1.0, 0), (3, 1, 0, 0.7, 0.9, 0), (4, 9, 50, 1.3, 0.5, 0),
@@ -329,6 +329,18 @@ def test_sampling_distribution_and_draw(ops, V):
         lo = cdf[tok - 1].item() if tok else 0.0
         assert lo - 1e-5 <= u <= cdf[tok].item() + 1e-5, (r, u, lo, cdf[tok].item())
     assert out[4] == int(torch.argmax(logits[4]))                 # top_k = 1 is argmax (tests/test_sampling.py:6-12)
+
+
+def test_sampling_skips_padding_rows(ops):
+    """A row whose slot id is -1 (padding of a fixed-size batch) yields token 0 and touches no state."""
+    V = 300
+    logits = torch.randn(3, V, generator=torch.Generator().manual_seed(2)).to(DEV)
+    state = sampler_state([(5, 4, 0, 1.0, 1.0, 1), (6, 9, 0, 1.0, 1.0, 1)]).to(DEV)
+    before = state.clone()
+    out = torch.full((3,), 77, dtype=torch.int32, device=DEV)
+    ops.sample(logits, torch.tensor([-1, 1, -1], dtype=torch.int32, device=DEV), state, out)
+    assert out.tolist() == [0, int(torch.argmax(logits[1])), 0]
+    assert torch.equal(state[0], before[0]) and int(state[1, 2]) == 10
 
 
 def test_sampling_frequencies(ops):
