@@ -58,7 +58,8 @@ def test_sampling_does_not_depend_on_batch():
 
 def test_graph_replays_match_whole_prompts_bfloat16():
     """Captured decode steps in bfloat16 against the same engine without graphs running every request whole.
-    Requests of different lengths end at different steps (the batch shrinks and changes its graph bucket),
+    Requests of different lengths end at different steps (the batch shrinks and changes its graph bucket; the
+    longest context leaves first, then the next, so the context bucket of the graphs changes too),
     contexts cross page boundaries while steps are replayed (the incremental repacking of a steady decode
     step), and with 16 heads of size 64 on one kv head both decode attention kernels run inside graphs: the
     kernels of a graph are planned for the longest context, 4,096 keys, which is the tcgen05 kernel with
@@ -70,7 +71,7 @@ def test_graph_replays_match_whole_prompts_bfloat16():
                eos_token_id=None, dtype="bfloat16")
     g = torch.Generator().manual_seed(5)
     prefix = {"a": 2300, "b": 40, "c": 700, "d": 9}
-    tail = {"a": 70, "b": 33, "c": 50, "d": 12}
+    tail = {"a": 12, "b": 70, "c": 33, "d": 50}
     reqs = {r: torch.randint(0, 300, (prefix[r] + tail[r],), generator=g).tolist() for r in prefix}
     eager, w = make_engine(cfg, 3, 64, 80, "bfloat16", max_seqs=4, budget=4096, graphs=False)
     ref = run_steps(eager, whole(reqs))
@@ -88,6 +89,7 @@ def test_graph_replays_match_whole_prompts_bfloat16():
     graphs, _ = make_engine(cfg, 3, 64, 80, "bfloat16", max_seqs=4, budget=4096, graphs=True, weights=w, cudagraph_batch_sizes=[1, 2, 4])
     got = run_steps(graphs, steps)
     assert graphs.stats()["step_graph_replays"] == 70
+    assert {k[:2] for k in graphs.stepper._graphs} == {(4, 4096), (4, 2048), (2, 512), (1, 512)}
     assert {graphs.ops.attention_plan(torch.bfloat16, 4, 16, 1, 64, 1, n, 64)[0] for n in (300, 4096)} == {"mma_c4", "tc"}
     worst, where = worst_relative(got, expected)
     assert worst < TOL["bfloat16"], (worst, where)

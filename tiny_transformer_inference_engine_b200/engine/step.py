@@ -8,8 +8,10 @@ returns 32-bit logits only where asked (the reference returns the last token of 
 span).  The cache must already cover the new positions (``CacheManager.extend``).
 
 Decode-only steps (one token per request, one wanted row each) can run from a captured
-CUDA graph per batch-size bucket: the metadata buffer keeps its address and layout, so a
-replay needs only the one host-to-device copy.
+CUDA graph per batch-size bucket and context-length bucket: the metadata buffer keeps its
+address and layout, so a replay needs only the one host-to-device copy.  The kernels of a
+graph are planned for the longest context of its bucket (512, 2048, 8192, ... keys, at most
+the model's ``max_seq_len``), so short contexts do not run kernels cut for long ones.
 """
 from __future__ import annotations
 
@@ -67,17 +69,26 @@ class Stepper:
     def _fixed_pages(self) -> Dict[int, int]:
         return {gi: -(-self.model.spec.max_seq_len // g.page_size) for gi, g in enumerate(self.manager.groups)}
 
+    def _context_bucket(self, entries) -> int:
+        need = max(e.start for e in entries) + 1
+        limit, b = self.model.spec.max_seq_len, 512
+        while b < need and b < limit:
+            b *= 4
+        return min(b, limit)
+
     def _step_graph(self, entries, bucket: int, sampler=None) -> torch.Tensor:
         n = len(entries)
-        g = self._graphs.get((bucket, sampler is not None))
+        keys = self._context_bucket(entries)
+        key = (bucket, keys, sampler is not None)
+        g = self._graphs.get(key)
         pages = self._fixed_pages()
         if g is None:
             words = 8 * (bucket + 4) + sum(bucket * w + 4 for w in pages.values()) + 64
             host = torch.empty(words, dtype=torch.int32, pin_memory=True)
             dev = torch.zeros(words, dtype=torch.int32, device=self.device)
             ctx = self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(host, dev))
-            # the captured kernels must cover any context length: size them for the longest
-            ctx.max_kv_len = self.model.spec.max_seq_len
+            # the captured kernels must cover every context length of the bucket: size them for the longest
+            ctx.max_kv_len = keys
             views = self.manager.views(ctx.block_tables)
             self.model.forward(ctx, views)                       # warm-up outside the capture
             torch.cuda.synchronize(self.device)
@@ -88,7 +99,7 @@ class Stepper:
                 logits = self.model.forward(ctx, views)
                 tokens = sampler.sample(logits, ctx.slot_ids) if sampler is not None else None
             g = _DecodeGraph(bucket, host, dev, graph, logits, tokens, ctx, getattr(self.ops, "launches", 0) - before)
-            self._graphs[(bucket, sampler is not None)] = g
+            self._graphs[key] = g
         self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(g.host, g.dev), copy_only=True)
         g.graph.replay()
         if hasattr(self.ops, "launches"):
