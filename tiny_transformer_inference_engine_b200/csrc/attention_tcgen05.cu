@@ -6,13 +6,15 @@
 //   warp 0      TMA: key and value tiles straight from the pages (one box per page and 64-column
 //               block, 128-byte swizzle) into a two-stage ring
 //   warp 1      one thread issues  S = Q K^T  (tcgen05.mma, both operands K-major in shared memory,
-//               S in tensor memory, two buffers) and  O_tile = P V  (P from shared memory, V as an
-//               MN-major operand, O_tile in tensor memory, two buffers)
+//               S in tensor memory, two buffers) and  O_tile = P V  (P from tensor memory, where it
+//               replaced the tile's scores; V as an MN-major operand from shared memory; O_tile in
+//               tensor memory, two buffers)
 //   warps 2-17  softmax, four threads per row (each one quarter of the columns): tcgen05.ld the row of S,
-//               scale, mask, running maximum and sum in float32, P rounded to bfloat16 into shared memory
-//               in the operand layout; one iteration later the same threads take O_tile out of tensor
-//               memory and add it to their part of the output row, rescaled - the running output lives
-//               in registers, so nothing in tensor memory is ever rescaled.
+//               scale, mask, running maximum and sum in float32, P rounded to bfloat16 and stored back into
+//               tensor memory over the scores (tcgen05.st; no trip through shared memory, no proxy fence);
+//               one iteration later the same threads take O_tile out of tensor memory and add it to their
+//               part of the output row, rescaled - the running output lives in registers, so nothing in
+//               tensor memory is ever rescaled.
 // Mask, scale and table lookup are those of kernels/pagedattn/pagedattn.cu:196-207,256 of the reference.
 // Every mbarrier wait is bounded; a wait that runs out records a code and the CTA winds down.
 #include "common.cuh"
@@ -88,6 +90,18 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t da, uint64_t
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
                  ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
+// The same with the A operand in tensor memory (lane = row, 32-bit columns hold two consecutive bfloat16 of K).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmem_c), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -131,7 +145,7 @@ struct AttnTcParams {
 };
 
 // Barrier slots
-enum { KF = 0, KE = 2, VF = 4, VE = 6, SF = 8, SE = 10, OF = 12, OE = 14, PF = 16, PE = 17, XB = 18, XL = 20, NBARS = 21 };
+enum { KF = 0, KE = 2, VF = 4, VE = 6, SF = 8, SE = 10, OF = 12, OE = 14, PF = 16, XB = 17, XL = 19, NBARS = 20 };
 
 constexpr int NP = 4;                                            // softmax threads per query row
 constexpr int NTHREADS = 64 + NP * 128;
@@ -142,14 +156,13 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
     constexpr int CB = D / 64;                                   // 64-column blocks of the head dimension
     constexpr uint32_t QBLK = BM * 128, KVBLK = BN * 128;        // bytes of one 64-column block
-    constexpr uint32_t Q_BYTES = CB * QBLK, P_BYTES = (BN / 64) * QBLK, KV_BYTES = CB * KVBLK;
+    constexpr uint32_t Q_BYTES = CB * QBLK, KV_BYTES = CB * KVBLK;
     constexpr uint32_t TMEM_COLS = 512;                          // 2 x 128 (S) + 2 x D (O_tile), rounded to a power of two
     constexpr uint32_t S_COL = 0, O_COL = 256;
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = smem;
-    unsigned char* Ps = Qs + Q_BYTES;
-    unsigned char* Ks = Ps + P_BYTES;                            // [2 stages]
+    unsigned char* Ks = Qs + Q_BYTES;                            // [2 stages]
     unsigned char* Vs = Ks + 2 * KV_BYTES;                       // [2 stages]
     __shared__ __align__(8) unsigned long long bars[NBARS];
     __shared__ uint32_t tmem_slot;
@@ -196,7 +209,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NBARS; ++i) {
-            const bool many = (i >= SE && i < SE + 2) || (i >= OE && i < OE + 2) || i == PF || i >= XB;
+            const bool many = (i >= OE && i < OE + 2) || i == PF || i >= XB;      // arrivals of the softmax threads; the rest: one commit or copy
             mbar_init(BAR(i), many ? softmax_threads : 1u);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -336,16 +349,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 if (!mbar_wait(BAR(OE + ob), ((j >> 1) & 1) ^ 1, 6)) { ok = false; break; }
                 if (!mbar_wait(BAR(PF), j & 1, 7)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v_addr = smem_u32(Vs + st * KV_BYTES), p_addr = smem_u32(Ps);
+                const uint32_t v_addr = smem_u32(Vs + st * KV_BYTES);
+                const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)(j & 1) * BN;     // P sits where the tile's scores sat
 #pragma unroll
-                for (int kb = 0; kb < BN / 64; ++kb)
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_base + O_COL + ob * D, desc_kmajor(p_addr + kb * QBLK) + (uint64_t)(k * 2),
-                                  desc_mnmajor(v_addr + (kb * 64 + k * 16) * 128, KVBLK), idesc_o, (kb | k) != 0);
+                for (int k = 0; k < BN / 16; ++k)
+                    umma_bf16_ts(tmem_base + O_COL + ob * D, p_tmem + (uint32_t)(k * 8),
+                                 desc_mnmajor(v_addr + (k * 16) * 128, KVBLK), idesc_o, k != 0);
                 umma_commit(BAR(OF + ob));
                 umma_commit(BAR(VE + st));
-                umma_commit(BAR(PE));
+                umma_commit(BAR(SE + (j & 1)));                         // scores / P buffer of this tile is free again
             }
         }
     } else if ((warp & 3) < nquarters) {
@@ -384,7 +396,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 tmem_ld32(lane_addr + S_COL + sb * BN + part * SC, sv);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(BAR(SE + sb));                              // the scores are in registers: the buffer is free
                 if (!tile_full) {
 #pragma unroll
                     for (int i = 0; i < SC; ++i) {
@@ -409,16 +420,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 const float m_new = fmaxf(m_run, mx);
                 const float msub = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);
-                // the single P buffer must have been read by the previous tile's second product
-                if (j > 0) {
-                    ok = mbar_wait(BAR(PE), (j - 1) & 1, 9);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                }
                 // probabilities, rounded to bfloat16 into the operand layout; their sum in float32
                 float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-                // this part's 32 keys are one half of 64-key block part / 2: chunks (part & 1) * 4 .. + 3 of the row
-                unsigned char* prow = Ps + (part >> 1) * QBLK + r * 128;
                 uint32_t packed[SC / 2];
 #pragma unroll
                 for (int i = 0; i < SC; i += 2) {
@@ -428,16 +431,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                     __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
                 }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int cin = (part & 1) * 4 + q4;
-                    *reinterpret_cast<uint4*>(prow + ((cin ^ (r & 7)) << 4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
+                // P over the scores of this tile: every thread of the row has its scores in registers (the exchange
+                // above came after the loads), so the columns can be overwritten; 32 keys = 16 packed columns
+                tmem_st16(lane_addr + S_COL + sb * BN + part * (SC / 2), packed);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
                 m_run = m_new;
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(BAR(PF));                                   // P is in shared memory
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(BAR(PF));                                   // P is in tensor memory
                 // rescale what has been summed so far to the new maximum
                 if (alpha != 1.f) {
 #pragma unroll
@@ -535,7 +536,7 @@ int make_page_map(CUtensorMap* map, const void* base, long long rows, int D, int
 
 template <int D, bool AHEAD>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, cudaStream_t s) {
-    const size_t smem = (size_t)(D / 64) * BM * 128 + (size_t)(BN / 64) * BM * 128 + 4 * (size_t)(D / 64) * BN * 128 + 1024;
+    const size_t smem = (size_t)(D / 64) * BM * 128 + 4 * (size_t)(D / 64) * BN * 128 + 1024;
     auto k = attn_tc_kernel<D, AHEAD>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
