@@ -93,3 +93,44 @@ def test_graph_replays_match_whole_prompts_bfloat16():
     assert {graphs.ops.attention_plan(torch.bfloat16, 4, 16, 1, 64, 1, n, 64)[0] for n in (300, 4096)} == {"mma_c4", "tc"}
     worst, where = worst_relative(got, expected)
     assert worst < TOL["bfloat16"], (worst, where)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pipelined_decode_changes_nothing(dtype):
+    """Launching the next captured decode step before the host has read the last one's tokens gives the same
+    tokens as reading every step first: requests that end by length and by EOS (which the host learns one
+    step late: the step already in flight for them is dropped), requests that arrive while others decode,
+    and every page back at the end."""
+    cfg = dict(TINY_A, max_seq_len=256, eos_token_id=None)
+    lens, news = (5, 17, 33, 9, 21, 40), (30, 12, 25, 40, 6, 18)
+    prompts = list(requests_for(cfg, lens, 9).values())
+    params = [SamplingParams(max_new_tokens=n, temperature=1.3, seed=40 + i) for i, n in enumerate(news)]
+    # the EOS id is chosen from what an engine without one generates: the ninth token of the fourth request
+    probe, _ = make_engine(cfg, SEEDS["A"], PAGE["A"], 40, dtype, max_seqs=4, budget=64, graphs=True, cudagraph_batch_sizes=[1, 2, 4])
+    cfg = dict(cfg, eos_token_id=probe.generate(prompts[3:4], params[3:4])[0][8])
+    del probe
+    outs, ends = [], []
+    for pipelined in (False, True):
+        eng, _ = make_engine(cfg, SEEDS["A"], PAGE["A"], 40, dtype, max_seqs=4, budget=64, graphs=True, cudagraph_batch_sizes=[1, 2, 4])
+        eng.engine_config.pipelined_decode = pipelined
+        got = {}
+        rids = [eng.add_request(p, q) for p, q in zip(prompts[:4], params[:4])]
+        calls = 0
+        while eng.scheduler.has_work or eng._inflight is not None:
+            for rid, tok, done in eng.step():
+                got.setdefault(rid, []).append(tok)
+            calls += 1
+            if calls == 7:                                                          # two more arrive while the first four decode
+                rids += [eng.add_request(p, q) for p, q in zip(prompts[4:], params[4:])]
+            assert calls < 400
+        assert eng.manager.num_free_pages == eng.manager.num_usable_pages
+        eng.manager.check()
+        outs.append([got[r] for r in rids])
+        ends.append([eng._requests[r].finish_reason for r in rids])
+        if pipelined:
+            assert eng.stats()["step_graph_replays"] > 20
+    assert outs[0] == outs[1]
+    assert ends[0] == ends[1]
+    assert any(e == "eos" for e in ends[0]) and any(e == "length" for e in ends[0])
+    for o, n in zip(outs[0], news):
+        assert 1 <= len(o) <= n

@@ -56,6 +56,7 @@ class EngineConfig:
     cache: CacheConfig = field(default_factory=CacheConfig)
     sched: SchedulerConfig = field(default_factory=SchedulerConfig)
     use_cuda_graphs: bool = True
+    pipelined_decode: bool = True              # launch the next captured decode step before the host has read this one's tokens
     device: str = "cuda:0"
 
     def __post_init__(self):

@@ -121,6 +121,15 @@ class BatchPacker:
             self._copied.record()
         return True
 
+    def feed_tokens(self, tokens: torch.Tensor) -> None:
+        """Overwrites the token ids of the fixed-layout decode step packed last with ``tokens`` (int32, on the
+        device, one per request in the step's order): the step then runs on tokens the host has not seen yet.
+        Ordered on the stream after the step's host-to-device copy."""
+        st = self._last
+        if st is None:
+            raise RuntimeError("no fixed-layout decode step is packed")
+        st["dev"][st["o_tok"]:st["o_tok"] + tokens.shape[0]].copy_(tokens)
+
     def pack(self, entries: List[StepEntry], pad_seqs: int = 0, pages_per_seq: Optional[Dict[int, int]] = None,
              buffers=None, copy_only: bool = False) -> Optional[StepContext]:
         """``pad_seqs``/``pages_per_seq``/``buffers`` give a fixed layout (for a captured

@@ -17,6 +17,7 @@ import torch
 
 from .. import models as _models  # noqa: F401  (registers the architecture)
 from ..cache import CacheManager
+from ..cache.allocator import OutOfPages
 from ..config import ModelConfig, EngineConfig, CacheConfig, SchedulerConfig
 from ..models.model import Model
 from ..registry import model_spec
@@ -27,6 +28,14 @@ from .scheduler import Scheduler
 from .step import Stepper
 
 _TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+class _Pending:
+    """A launched decode step whose sampled tokens the host has not read yet."""
+    __slots__ = ("entries", "tokens_dev", "host", "event")
+
+    def __init__(self, entries, tokens_dev, host, event):
+        self.entries, self.tokens_dev, self.host, self.event = entries, tokens_dev, host, event
 
 
 class Engine:
@@ -62,6 +71,11 @@ class Engine:
         self.stepper = Stepper(self.model, self.manager, ops, self.dtype, self.device, graphs)
         self.sampler = Sampler(ops, ec.sched.max_num_seqs, config.vocab_size, self.device)
         self._slot_ids = None
+        self._inflight: Optional[_Pending] = None
+        if self.device.type == "cuda":
+            self._pinned = [torch.zeros(ec.sched.max_num_seqs, dtype=torch.int32).pin_memory() for _ in range(2)]
+            self._events = [torch.cuda.Event() for _ in range(2)]
+        self._pin_turn = 0
         self.scheduler = Scheduler(self.manager, ec.sched, config.max_seq_len, config.eos_token_id)
         self._requests: Dict[int, object] = {}
 
@@ -91,7 +105,25 @@ class Engine:
 
     @torch.no_grad()
     def step(self) -> List[Tuple[int, int, bool]]:
-        """One scheduler step: plan, run the batch, sample on the device, read the tokens."""
+        """One scheduler step: plan, run the batch, sample on the device, read the tokens.
+
+        With ``pipelined_decode`` a captured decode step is followed at once by its successor - the same
+        requests one position on, fed on the device with the tokens just sampled - before the host reads
+        its tokens, so the GPU does not wait while the host reads, updates and plans.  The results returned
+        are then those of the older of the two steps; a call that finds a step in flight and cannot follow it
+        up (a request about to end, requests waiting, pages short) only reads it."""
+        pending = self._inflight
+        self._inflight = None
+        if pending is None:
+            pending = self._plan_and_launch()
+            if not isinstance(pending, _Pending):
+                return pending                                                          # results of a step that was read at once
+        follow = self._follow_up(pending) if self.engine_config.pipelined_decode else None
+        results = self._read(pending)
+        self._inflight = follow
+        return results
+
+    def _plan_and_launch(self):
         sched = self.scheduler
         before = {r.rid for r in sched.running}
         entries = sched.plan()
@@ -102,19 +134,61 @@ class Engine:
                 self.sampler.set_request(self.manager.slot_of[r.rid], r.params, draws_so_far=len(r.output))
         logits = self.stepper.step(entries, self.sampler)
         if self.stepper.last_tokens is not None:                                        # a captured decode step sampled in its graph
-            tokens = self.stepper.last_tokens.tolist()                                  # one device-to-host read
+            return self._pend(entries, self.stepper.last_tokens)
+        slots = [self.manager.slot_of[e.rid] for e in entries if e.want]
+        if slots:
+            key = tuple(slots)
+            if self._slot_ids is None or self._slot_ids[0] != key:                      # the same requests step after step: one upload
+                self._slot_ids = (key, torch.tensor(slots, dtype=torch.int32).to(self.device))
+            tokens = self.sampler.sample(logits[:len(slots)], self._slot_ids[1]).tolist()   # one device-to-host read
         else:
-            slots = [self.manager.slot_of[e.rid] for e in entries if e.want]
-            if slots:
-                key = tuple(slots)
-                if self._slot_ids is None or self._slot_ids[0] != key:                  # the same requests step after step: one upload
-                    self._slot_ids = (key, torch.tensor(slots, dtype=torch.int32).to(self.device))
-                tokens = self.sampler.sample(logits[:len(slots)], self._slot_ids[1]).tolist()
-            else:
-                tokens = []
+            tokens = []
         if hasattr(self.ops, "check_tc"):
             self.ops.check_tc()
         return sched.update(entries, tokens)
+
+    def _pend(self, entries, tokens_dev: torch.Tensor) -> "_Pending":
+        """Starts the copy of a launched step's tokens into pinned memory; the host reads them later."""
+        n = tokens_dev.shape[0]
+        self._pin_turn ^= 1
+        host = self._pinned[self._pin_turn]
+        host[:n].copy_(tokens_dev, non_blocking=True)
+        event = self._events[self._pin_turn]
+        event.record()
+        return _Pending(entries, tokens_dev, host, event)
+
+    def _follow_up(self, pending: "_Pending") -> Optional["_Pending"]:
+        """Launches the decode step after ``pending`` for the same requests, or returns None where that step is not
+        certain to be wanted as it stands: a request may reach its last token, may have ended already, requests
+        wait for admission, or pages run short (the scheduler then decides, after the host has caught up)."""
+        sched = self.scheduler
+        if sched.waiting:
+            return None
+        running = {r.rid: r for r in sched.running}
+        for e in pending.entries:
+            r = running.get(e.rid)
+            # its output does not hold the token of the step in flight yet: that one and the next must both be wanted
+            if r is None or len(r.output) + 2 > r.params.max_new_tokens or e.start + 2 > self.config.max_seq_len:
+                return None
+        if len(pending.entries) != len(running):
+            return None
+        try:
+            for e in pending.entries:
+                self.manager.extend(e.rid, e.start + 1, e.start + 2)
+        except OutOfPages:
+            return None                                                                 # (pages taken so far are the requests' next ones anyway)
+        entries = [StepEntry(e.rid, e.start + 1, [0], [0]) for e in pending.entries]
+        self.stepper.step(entries, self.sampler, feed=pending.tokens_dev)
+        if self.stepper.last_tokens is None:
+            raise RuntimeError("the step after a captured decode step did not run from a graph")
+        return self._pend(entries, self.stepper.last_tokens)
+
+    def _read(self, pending: "_Pending") -> List[Tuple[int, int, bool]]:
+        pending.event.synchronize()
+        tokens = pending.host[:len(pending.entries)].tolist()
+        if hasattr(self.ops, "check_tc"):
+            self.ops.check_tc()
+        return self.scheduler.update(pending.entries, tokens)
 
     # ---------------------------------------------------------------- whole generations
     def generate(self, prompts_ids: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None

@@ -212,7 +212,10 @@ class Scheduler:
         by_rid = {r.rid: r for r in self.running}
         results, k = [], 0
         for en in entries:
-            req = by_rid[en.rid]
+            req = by_rid.get(en.rid)
+            if req is None:                 # it ended while this step, launched ahead of the host, was in flight
+                k += len(en.want)
+                continue
             n = len(en.tokens)
             if req.num_cached < len(req.prompt):
                 self.counters["prefill_tokens"] += n

@@ -44,10 +44,12 @@ class Stepper:
 
     # ---------------------------------------------------------------- plain step
     @torch.no_grad()
-    def step(self, entries: List[StepEntry], sampler=None) -> torch.Tensor:
+    def step(self, entries: List[StepEntry], sampler=None, feed: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Logits (float32, [sum of wants, vocab]) in the order of the entries and of ``want``.
         With a ``sampler`` a captured decode step also samples (the kernel is part of the graph) and leaves the
-        tokens in ``last_tokens``; any other step leaves None there and the caller samples from the logits."""
+        tokens in ``last_tokens``; any other step leaves None there and the caller samples from the logits.
+        ``feed`` (captured decode steps only): token ids on the device, one per entry, that replace the entries'
+        tokens - the step before this one sampled them and the host has not read them yet."""
         self.last_tokens = None
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
@@ -56,7 +58,9 @@ class Stepper:
         if self.graph_batch_sizes and self._is_decode(entries):
             bucket = next((b for b in self.graph_batch_sizes if b >= len(entries)), None)
             if bucket is not None:
-                return self._step_graph(entries, bucket, sampler)
+                return self._step_graph(entries, bucket, sampler, feed)
+        if feed is not None:
+            raise ValueError("tokens can be fed on the device only into a captured decode step")
         ctx = self.packer.pack(entries)
         views = self.manager.views(ctx.block_tables)
         return self.model.forward(ctx, views)
@@ -76,7 +80,7 @@ class Stepper:
             b *= 4
         return min(b, limit)
 
-    def _step_graph(self, entries, bucket: int, sampler=None) -> torch.Tensor:
+    def _step_graph(self, entries, bucket: int, sampler=None, feed=None) -> torch.Tensor:
         n = len(entries)
         keys = self._context_bucket(entries)
         key = (bucket, keys, sampler is not None)
@@ -101,6 +105,8 @@ class Stepper:
             g = _DecodeGraph(bucket, host, dev, graph, logits, tokens, ctx, getattr(self.ops, "launches", 0) - before)
             self._graphs[key] = g
         self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(g.host, g.dev), copy_only=True)
+        if feed is not None:
+            self.packer.feed_tokens(feed)
         g.graph.replay()
         if hasattr(self.ops, "launches"):
             self.ops.launches += g.launches
