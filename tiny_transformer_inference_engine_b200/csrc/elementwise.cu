@@ -304,7 +304,8 @@ __global__ void swiglu_vec8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bf
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-            o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+            // the result is rounded to bfloat16 (2^-9): the fast exponential and division (about 2^-21) do not show
+            o2[k] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
         }
         *reinterpret_cast<uint4*>(out + i * 8) = o4;
     }
