@@ -207,29 +207,47 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const uint32_t bar0 = smem_u32(&bars[0]);
 #define BAR(i) (bar0 + 8u * (uint32_t)(i))
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < NBARS; ++i) {
-            const bool many = (i >= OE && i < OE + 2) || i == PF || i >= XB;      // arrivals of the softmax threads; the rest: one commit or copy
-            mbar_init(BAR(i), many ? softmax_threads : 1u);
+    // The start of a CTA, side by side (a decode step's CTA walks only a tile or two, so this counts): warp 1 sets up
+    // the barriers, warp 0 allocates tensor memory and looks up the pages of the first two tiles (the small loads
+    // only - their copies go out after the queries, or the queries would queue behind 128 KB of tiles), and the
+    // softmax warps stage the queries.
+    int y_first = 0;                                              // warp 0, lane = tile * boxes + box: first row of that box in the page matrix
+    if (warp == 1) {
+        if (lane == 0) {
+            for (int i = 0; i < NBARS; ++i) {
+                const bool many = (i >= OE && i < OE + 2) || i == PF || i >= XB;      // arrivals of the softmax threads; the rest: one commit or copy
+                mbar_init(BAR(i), many ? softmax_threads : 1u);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (warp == 0) {
+    } else if (warp == 0) {
+        if (!AHEAD) {
+            const int ps = p.page_size;
+            const int box_rows = ps < BN ? ps : BN, nboxes = BN / box_rows;            // at most 16 boxes per tile
+            const int jt = lane / nboxes, bx = lane - jt * nboxes;
+            if (jt < 2 && jt < ntiles) {
+                const int key = (t_begin + jt) * BN + bx * box_rows;
+                const int pg = key / ps;
+                const int page = pg < p.table_width ? p.block_table[(size_t)seq * p.table_width + pg] : 0;
+                y_first = (page * p.Hkv + kvh) * ps + (key - pg * ps);
+            }
+        }
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    // queries of the tile -> shared memory in the K-major swizzled operand layout (all 192 threads help)
-    for (int c = threadIdx.x; c < BM * (D / 8); c += blockDim.x) {
-        const int r = c / (D / 8), chunk = c - r * (D / 8);      // chunk: 8 bfloat16 = 16 bytes
-        const int row = row0 + r;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (row < nrows) {
-            const int tok = row / G, g = row - tok * G;
-            v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)(kvh * G + g) * D + chunk * 8);
+    } else {
+        // queries of the tile -> shared memory in the K-major swizzled operand layout
+        for (int c = threadIdx.x - 64; c < BM * (D / 8); c += blockDim.x - 64) {
+            const int r = c / (D / 8), chunk = c - r * (D / 8);      // chunk: 8 bfloat16 = 16 bytes
+            const int row = row0 + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (row < nrows) {
+                const int tok = row / G, g = row - tok * G;
+                v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)(kvh * G + g) * D + chunk * 8);
+            }
+            const int blk = chunk >> 3, cin = chunk & 7;
+            *reinterpret_cast<uint4*>(Qs + blk * QBLK + r * 128 + ((cin ^ (r & 7)) << 4)) = v;
         }
-        const int blk = chunk >> 3, cin = chunk & 7;
-        *reinterpret_cast<uint4*>(Qs + blk * QBLK + r * 128 + ((cin ^ (r & 7)) << 4)) = v;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes of Q become visible to the tensor core
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -287,11 +305,36 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     } else if (warp == 0 && !AHEAD) {
         // Few rows (decode steps, where the softmax threads set the pace): one thread looks pages up as it goes,
         // which spaces the copies out; measured faster there than asking for both stages at once.
+        {
+            // the first two tiles (both stages are free): their pages were looked up while the queries were staged
+            const int ps0 = p.page_size;
+            const int box_rows0 = ps0 < BN ? ps0 : BN, nboxes0 = BN / box_rows0;
+            for (int j = 0; j < 2 && j < ntiles; ++j) {
+                if (lane == 0) mbar_expect_tx(BAR(KF + j), KV_BYTES);
+                for (int b = 0; b < nboxes0; ++b) {
+                    const int yy = __shfl_sync(0xffffffffu, y_first, j * nboxes0 + b);
+                    if (lane == 0) {
+#pragma unroll
+                        for (int cb = 0; cb < CB; ++cb)
+                            tma_load_2d(smem_u32(Ks + j * KV_BYTES + cb * KVBLK + b * box_rows0 * 128), &tmK, BAR(KF + j), cb * 64, yy);
+                    }
+                }
+                if (lane == 0) mbar_expect_tx(BAR(VF + j), KV_BYTES);
+                for (int b = 0; b < nboxes0; ++b) {
+                    const int yy = __shfl_sync(0xffffffffu, y_first, j * nboxes0 + b);
+                    if (lane == 0) {
+#pragma unroll
+                        for (int cb = 0; cb < CB; ++cb)
+                            tma_load_2d(smem_u32(Vs + j * KV_BYTES + cb * KVBLK + b * box_rows0 * 128), &tmV, BAR(VF + j), cb * 64, yy);
+                    }
+                }
+            }
+        }
         if (lane == 0) {
             const int ps = p.page_size;
             const int box_rows = ps < BN ? ps : BN;
             const int* table = p.block_table + (size_t)seq * p.table_width;
-            for (int j = 0; j < ntiles; ++j) {
+            for (int j = 2; j < ntiles; ++j) {
                 const int st = j & 1;
                 const uint32_t par = ((j >> 1) & 1) ^ 1;
                 const int key0 = (t_begin + j) * BN;
