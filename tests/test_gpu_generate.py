@@ -101,17 +101,17 @@ def test_pipelined_decode_changes_nothing(dtype):
     tokens as reading every step first: requests that end by length and by EOS (which the host learns one
     step late: the step already in flight for them is dropped), requests that arrive while others decode,
     and every page back at the end."""
-    cfg = dict(TINY_A, max_seq_len=256, eos_token_id=None)
-    lens, news = (5, 17, 33, 9, 21, 40), (30, 12, 25, 40, 6, 18)
+    cfg = dict(TINY_A, max_seq_len=1100, eos_token_id=None)
+    lens, news = (505, 17, 33, 9, 21, 40), (30, 12, 25, 40, 6, 18)      # the first one crosses 512 keys: another context bucket of graphs
     prompts = list(requests_for(cfg, lens, 9).values())
     params = [SamplingParams(max_new_tokens=n, temperature=1.3, seed=40 + i) for i, n in enumerate(news)]
     # the EOS id is chosen from what an engine without one generates: the ninth token of the fourth request
-    probe, _ = make_engine(cfg, SEEDS["A"], PAGE["A"], 40, dtype, max_seqs=4, budget=64, graphs=True, cudagraph_batch_sizes=[1, 2, 4])
+    probe, _ = make_engine(cfg, SEEDS["A"], PAGE["A"], 80, dtype, max_seqs=4, budget=64, graphs=True, cudagraph_batch_sizes=[1, 2, 4])
     cfg = dict(cfg, eos_token_id=probe.generate(prompts[3:4], params[3:4])[0][8])
     del probe
     outs, ends = [], []
     for pipelined in (False, True):
-        eng, _ = make_engine(cfg, SEEDS["A"], PAGE["A"], 40, dtype, max_seqs=4, budget=64, graphs=True, cudagraph_batch_sizes=[1, 2, 4])
+        eng, _ = make_engine(cfg, SEEDS["A"], PAGE["A"], 80, dtype, max_seqs=4, budget=64, graphs=True, cudagraph_batch_sizes=[1, 2, 4])
         eng.engine_config.pipelined_decode = pipelined
         got = {}
         rids = [eng.add_request(p, q) for p, q in zip(prompts[:4], params[:4])]
@@ -129,6 +129,7 @@ def test_pipelined_decode_changes_nothing(dtype):
         ends.append([eng._requests[r].finish_reason for r in rids])
         if pipelined:
             assert eng.stats()["step_graph_replays"] > 20
+            assert {k[1] for k in eng.stepper._graphs} >= {512, 1100}
     assert outs[0] == outs[1]
     assert ends[0] == ends[1]
     assert any(e == "eos" for e in ends[0]) and any(e == "length" for e in ends[0])
