@@ -14,7 +14,8 @@ from gpu_util import TOL
 from tiny_transformer_inference_engine_b200 import Engine, ModelConfig, EngineConfig, CacheConfig, SchedulerConfig
 from tiny_transformer_inference_engine_b200 import register_model, register_part
 from tiny_transformer_inference_engine_b200.parts.base import (PartSpec, LayerSpec, RunEntry, ModelSpec, Mixer, ParamSpec,
-                                                                FixedStateNeed, StepContext, PagedKVView)
+                                                                FeedForward, PositionEncoding, FixedStateNeed, StepContext,
+                                                                PagedKVView)
 from tiny_transformer_inference_engine_b200.registry import build_part, unregister_model, unregister_part
 from tiny_transformer_inference_engine_b200.weights import random_tensors
 
@@ -225,4 +226,139 @@ def test_toy_architecture_is_built_and_stepped(toy_registered, dtype, mode):
     exp = {rid: toy_plain_forward(cfg, w, toks) for rid, toks in reqs.items()}
     got = tu.run_steps(eng, steps)
     bad = tu.first_wrong(got, exp, TOL[dtype])
+    assert bad is None, f"first wrong place {bad}"
+
+
+# ------------------------------------------------------------------------------------------ more toy parts
+class ToyRoutedFFN(FeedForward):
+    """A feed-forward with routing: a router picks one of E small two-layer experts per token (router logits and
+    their softmax in 32-bit); the output is the chosen expert's, scaled by its probability."""
+
+    def __init__(self, prefix, d_model, hidden, experts):
+        super().__init__(prefix)
+        self.d, self.h, self.E = d_model, hidden, experts
+
+    def param_specs(self):
+        specs = {"router.weight": ParamSpec((self.E, self.d))}
+        for e in range(self.E):
+            specs[f"experts.{e}.up.weight"] = ParamSpec((self.h, self.d))
+            specs[f"experts.{e}.down.weight"] = ParamSpec((self.d, self.h))
+        return specs
+
+    def load(self, params):
+        self.router = params["router.weight"]
+        self.up = [params[f"experts.{e}.up.weight"] for e in range(self.E)]
+        self.down = [params[f"experts.{e}.down.weight"] for e in range(self.E)]
+
+    def forward(self, x, ctx):
+        probs = torch.softmax(x.float() @ self.router.float().T, -1)
+        gate, choice = probs.max(-1)
+        y = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+        for e in range(self.E):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                h = torch.relu(self.ops.linear(x[rows].contiguous(), self.up[e], None))
+                y[rows] = self.ops.linear(h, self.down[e], None).float() * gate[rows, None]
+        return y.to(x.dtype)
+
+
+class ToyOffsetPosition(PositionEncoding):
+    """A position encoding that is no rotation: queries and keys get a fixed sinusoid of their position added
+    (the general ``apply`` path of the attention part: no fused rotate-and-store)."""
+
+    def __init__(self, prefix, dim, period):
+        super().__init__(prefix)
+        self.dim, self.period = dim, period
+
+    def offsets(self, positions):
+        i = torch.arange(self.dim, device=positions.device, dtype=torch.float32)
+        return 0.3 * torch.sin(positions.float()[:, None] / self.period + i[None, :])
+
+    def apply(self, q, k, positions):
+        off = self.offsets(positions)[:, None, :]
+        q.copy_((q.float() + off).to(q.dtype))
+        if k is not None:
+            k.copy_((k.float() + off).to(k.dtype))
+
+
+def routed_spec(config):
+    d, D = config.d_model, config.head_dim
+    norm = lambda p: PartSpec("rmsnorm", p, {"dim": d, "eps": config.rms_norm_eps})
+    pos = PartSpec("toy_offset", "", {"dim": D, "period": config.extra["period"]})
+    layers = []
+    for i in range(config.num_layers):
+        attn = PartSpec("attention", f"layers.{i}.attn", {"d_model": d, "num_heads": config.num_heads,
+                                                           "num_kv_heads": config.num_kv_heads, "head_dim": D, "position": pos})
+        ffn = (PartSpec("toy_routed", f"layers.{i}.moe", {"d_model": d, "hidden": config.hidden_size, "experts": config.extra["experts"]})
+               if i % 2 == 0 else PartSpec("swiglu", f"layers.{i}.mlp", {"d_model": d, "hidden": config.hidden_size, "bias": False}))
+        layers.append(LayerSpec(PartSpec("pre_norm", f"layers.{i}", {"mixer_norm": norm(f"layers.{i}.n1"), "mixer": attn,
+                                                                      "ffn_norm": norm(f"layers.{i}.n2"), "ffn": ffn})))
+    return ModelSpec(d_model=d, vocab_size=config.vocab_size, max_seq_len=config.max_seq_len,
+                     embedding=PartSpec("token", "emb", {"vocab_size": config.vocab_size, "dim": d}),
+                     layers=tuple(layers), run_order=tuple(RunEntry(i) for i in range(config.num_layers)),
+                     final_norm=norm("final_norm"), head=PartSpec("linear", "lm_head", {"dim": d, "vocab_size": config.vocab_size}))
+
+
+def routed_plain_forward(cfg, w, tokens):
+    """The routed toy architecture written out plainly, whole sequence, no cache."""
+    w = {k: v.float() for k, v in w.items()}
+    S, d, Hq, Hkv, E = len(tokens), cfg["d_model"], cfg["num_heads"], cfg["num_kv_heads"], cfg["experts"]
+    D, eps = d // Hq, cfg["rms_norm_eps"]
+    x = w["emb.weight"][torch.tensor(tokens)]
+    i = torch.arange(D, dtype=torch.float32)
+    off = (0.3 * torch.sin(torch.arange(S).float()[:, None] / cfg["period"] + i[None, :]))[:, None, :]
+    for li in range(cfg["num_layers"]):
+        h = pm.plain_rmsnorm(x, w[f"layers.{li}.n1.weight"], eps)
+        p = f"layers.{li}.attn"
+        q = (h @ w[f"{p}.q_proj.weight"].T).view(S, Hq, D) + off
+        k = (h @ w[f"{p}.k_proj.weight"].T).view(S, Hkv, D) + off
+        v = (h @ w[f"{p}.v_proj.weight"].T).view(S, Hkv, D)
+        x = x + pm.plain_attention(q, k, v, 1 / math.sqrt(D), None).reshape(S, d) @ w[f"{p}.out.weight"].T
+        h = pm.plain_rmsnorm(x, w[f"layers.{li}.n2.weight"], eps)
+        if li % 2 == 0:
+            p = f"layers.{li}.moe"
+            probs = torch.softmax(h @ w[f"{p}.router.weight"].T, -1)
+            gate, choice = probs.max(-1)
+            y = torch.stack([torch.relu(h[t] @ w[f"{p}.experts.{int(choice[t])}.up.weight"].T)
+                             @ w[f"{p}.experts.{int(choice[t])}.down.weight"].T * gate[t] for t in range(S)])
+            x = x + y
+        else:
+            x = x + pm.plain_swiglu(h, w, f"layers.{li}.mlp")
+    return pm.plain_rmsnorm(x, w["final_norm.weight"], eps) @ w["lm_head.weight"].T
+
+
+@pytest.fixture
+def routed_registered():
+    register_part("ffn", "toy_routed")(ToyRoutedFFN)
+    register_part("position", "toy_offset")(ToyOffsetPosition)
+    register_model("toy_routed_model")(routed_spec)
+    yield
+    unregister_model("toy_routed_model")
+    unregister_part("position", "toy_offset")
+    unregister_part("ffn", "toy_routed")
+
+
+@pytest.mark.parametrize("mode", ["whole", "decode", "portions", "mixed"])
+def test_routed_ffn_and_other_position_encoding(routed_registered, mode):
+    """A feed-forward with routing in every other layer and a position encoding that is no rotation, both defined
+    here and registered without a change to the package: built from config.json keys, random weights by their
+    tensor names, and stepped in every way of cutting against the architecture written out plainly.  (float32:
+    a router's choice between near-equal experts must not depend on rounding.)"""
+    cfg = dict(architecture="toy_routed_model", vocab_size=211, d_model=96, num_layers=3, num_heads=6, num_kv_heads=2,
+               hidden_size=40, max_seq_len=200, rms_norm_eps=1e-5, rope_theta=1.0, experts=3, period=7.5)
+    mc = ModelConfig.from_dict(cfg)
+    assert mc.extra == {"experts": 3, "period": 7.5}
+    w = random_tensors(mc, 4, std=0.1, perturb_norms=True)
+    assert "layers.0.moe.experts.2.down.weight" in w and "layers.1.mlp.gate_proj.weight" in w and "layers.1.moe.router.weight" not in w
+    g = torch.Generator().manual_seed(3)
+    reqs = {f"r{i}": torch.randint(0, 211, (n,), generator=g).tolist() for i, n in enumerate((60, 133, 17, 200, 75))}
+    steps = {"whole": tu.whole, "decode": tu.prefill_then_decode, "portions": tu.portions, "mixed": tu.mixed}[mode](reqs)
+    page = 16
+    ec = EngineConfig(dtype="float32", device=DEV, use_cuda_graphs=False,
+                      cache=CacheConfig(block_size=page, num_gpu_blocks=tu.max_live_tokens(steps) // page + 1),
+                      sched=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64))
+    eng = Engine(mc, w, ec)
+    exp = {rid: routed_plain_forward(cfg, w, toks) for rid, toks in reqs.items()}
+    got = tu.run_steps(eng, steps)
+    bad = tu.first_wrong(got, exp, TOL["float32"])
     assert bad is None, f"first wrong place {bad}"
