@@ -505,7 +505,7 @@ def test_decode_form_is_planned(ops):
     assert kernel == "tc" and n * split_len >= 32768 and split_len % 128 == 0 and 8 * n <= 148
     assert ops.attention_plan(torch.bfloat16, 8, 32, 1, 96, 1, 32768, 64)[0] == "mma"       # a head size the tcgen05 kernel does not take
     assert ops.attention_plan(torch.bfloat16, 8, 32, 8, 128, 1, 32768, 64)[0] == "mma"      # four rows per kv head
-    assert ops.attention_plan(torch.bfloat16, 1, 32, 1, 128, 2048, 2048, 64)[0] == "tc"
+    assert ops.attention_plan(torch.bfloat16, 1, 32, 1, 128, 2048, 2048, 64)[0] == "tcpp"
     assert ops.attention_plan(torch.bfloat16, 2, 8, 2, 48, 200, 200, 16)[0] == "mma"
 
 
@@ -533,26 +533,56 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n):
 TC_SHAPES = [(32, 1, 128, 64), (32, 1, 128, 16), (8, 2, 64, 8), (3, 1, 64, 128), (71, 1, 64, 64), (4, 2, 128, 32), (5, 5, 64, 256)]
 
 
+TC_KERNELS = ["tc", "tcpp"]                                       # one 128-row query tile per CTA; two tiles taken in turns
+
+
+@pytest.mark.parametrize("kernel", TC_KERNELS)
 @pytest.mark.parametrize("scenario", ["prefill", "chunked", "mixed", "decode"])
 @pytest.mark.parametrize("Hq,Hkv,D,page", TC_SHAPES)
-def test_tcgen05_attention(ops, scenario, Hq, Hkv, D, page):
+def test_tcgen05_attention(ops, kernel, scenario, Hq, Hkv, D, page):
     seqs = SCENARIOS[scenario] + [(700, 700)]
-    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=("tc", 1, 0))
+    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=(kernel, 1, 0))
     assert ops.tc_error() == 0
     assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("kernel", TC_KERNELS)
 @pytest.mark.parametrize("window", [1, 5, 100, 129, 300])
-def test_tcgen05_attention_window(ops, window):
-    out, exp, _, _ = attention_case(ops, "bfloat16", 4, 2, 64, 16, [(450, 450), (90, 1), (300, 40)], window=window, plan=("tc", 1, 0))
+def test_tcgen05_attention_window(ops, kernel, window):
+    out, exp, _, _ = attention_case(ops, "bfloat16", 4, 2, 64, 16, [(450, 450), (90, 1), (300, 40)], window=window, plan=(kernel, 1, 0))
     assert ops.tc_error() == 0 and rel(out, exp) < TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("split_len", [128, 512])
+@pytest.mark.parametrize("Hq,Hkv,D,page", [(32, 1, 128, 64), (8, 2, 64, 8), (5, 5, 64, 256)])
+def test_tcgen05_two_tile_attention_with_splits(ops, Hq, Hkv, D, page, split_len):
+    """The two-tile kernel with the key range cut over CTAs (a long context behind a short portion): partial results
+    relative to a maximum that may lag the true one, merged by the merge kernel; splits without a visible key."""
+    seqs = [(1500, 200), (300, 300), (900, 1), (64, 64)]
+    n = -(-1500 // split_len)
+    for window in (0, 200):
+        out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=("tcpp", n, split_len), window=window)
+        assert ops.tc_error() == 0
+        assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
+
+
+def test_tcgen05_two_tile_attention_rescales(ops):
+    """Keys whose scores grow along the sequence, so that the running maximum of every row passes the rescale
+    threshold several times, and a row whose output is decided by one late key after large earlier ones."""
+    for kpos in (5, 300, 1023):
+        out, exp, dense, qsl = attention_case(ops, "bfloat16", 8, 1, 128, 64, [(1024, 1024), (700, 64)], plan=("tcpp", 1, 0),
+                                              spike=(0, 1023, kpos))
+        assert ops.tc_error() == 0
+        assert (out[qsl[0] + 1023].view(8, 128) - dense[0][1][kpos, 0]).abs().max() < 2e-2
+        assert rel(out, exp) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("kernel", TC_KERNELS)
 @pytest.mark.parametrize("kpos", [0, 63, 64, 127, 128, 447, 599])
-def test_tcgen05_attention_one_key_decides(ops, kpos):
+def test_tcgen05_attention_one_key_decides(ops, kernel, kpos):
     seqs = [(50, 1), (600, 1), (64, 3), (600, 600)]
     for spike_q in ((1, 0), (3, 599)):
-        out, exp, dense, qsl = attention_case(ops, "bfloat16", 4, 1, 64, 64, seqs, plan=("tc", 1, 0), spike=(spike_q[0], spike_q[1], kpos))
+        out, exp, dense, qsl = attention_case(ops, "bfloat16", 4, 1, 64, 64, seqs, plan=(kernel, 1, 0), spike=(spike_q[0], spike_q[1], kpos))
         row = out[qsl[spike_q[0]] + spike_q[1]].view(4, 64)
         assert (row - dense[spike_q[0]][1][kpos, 0]).abs().max() < 2e-2
         assert rel(out, exp) < TOL["bfloat16"]

@@ -549,6 +549,366 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Two query tiles per CTA, taken in turns ("ping-pong"): the form for prompt portions.
+//
+// A CTA owns 256 query rows as two 128-row tiles that share every key/value tile.  While the softmax threads of one
+// tile work on its scores, the tensor core computes the other tile's products, so neither waits for the other:
+//   warps 0-3    softmax of tile 0, ONE thread per row: the 128 scores of a key tile come out of tensor memory into
+//                registers, so row maximum and sum need no exchange between threads; P goes back over the scores
+//   warps 4-7    the same for tile 1
+//   warps 8-11   correction: the running output stays in tensor memory (O += P V accumulates there); when a row's
+//                maximum has grown by more than 2^8 since its output was last scaled, these warps scale the row of O
+//                (tcgen05.ld / st).  Below that threshold the old maximum stays in use - P is then at most 2^8, which
+//                costs bfloat16 nothing - so after the first tiles O is rarely touched.  At the end they divide by
+//                the row sum and store.
+//   warp 12      TMA producer: key and value tiles alternate through one ring of four stages
+//   warp 13      one thread issues  S0, S1, then per key tile  O0 += P0 V, S0(next), O1 += P1 V, S1(next)
+// Register budgets follow the roles (setmaxnreg): the softmax threads hold a whole row of scores.
+namespace pp {
+constexpr int NS = 4;                                            // stages of the key/value ring
+enum { PP_FULL = 0, PP_EMPTY = NS, PP_SF = 2 * NS, PP_PF = PP_SF + 2, PP_SC = PP_PF + 2, PP_OF = PP_SC + 2, PP_OC = PP_OF + 2, PP_LF = PP_OC + 2, PP_NBARS = PP_LF + 2 };
+constexpr int PP_NTHREADS = 512;
+constexpr float RESCALE_LOG2 = 8.f;                              // a row's output is rescaled when its maximum grew by more
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(pp::PP_NTHREADS, 1)
+attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
+    using namespace pp;
+    constexpr int CB = D / 64;
+    constexpr uint32_t QBLK = BM * 128, KVBLK = BN * 128;        // bytes of one 64-column block of a 128-row tile
+    constexpr uint32_t QT_BYTES = CB * QBLK, KV_BYTES = CB * KVBLK;
+    constexpr uint32_t TMEM_COLS = 512;                          // S0, S1 (128 columns each), O0, O1 (D each)
+    constexpr uint32_t S_COL = 0, O_COL = 256;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = smem;                                    // [2 tiles]
+    unsigned char* ring = Qs + 2 * QT_BYTES;                     // [NS stages]
+    __shared__ __align__(8) unsigned long long bars[PP_NBARS];
+    __shared__ uint32_t tmem_slot;
+    __shared__ float alpha_s[2][BM];                             // factor by which a row of O has to be scaled before the next product
+    __shared__ float lsum_s[2][BM], mrun_s[2][BM];               // a row's sum and the maximum it is relative to, at the end
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.Hq / p.Hkv;
+    int tile = blockIdx.x;
+    const int rt = p.row_tiles - 1 - tile % p.row_tiles;         // long (late) tiles first
+    tile /= p.row_tiles;
+    const int kvh = tile % p.Hkv, seq = tile / p.Hkv;
+    const int q0 = p.qsl[seq], q_len = p.qsl[seq + 1] - q0, kv_len = p.seq_lens[seq];
+    const int nrows = q_len * G, row0 = rt * (2 * BM);
+    if (row0 >= nrows) return;                                   // uniform over the CTA, before anything is allocated
+    const int ctx = kv_len - q_len;
+    const int rows_here = min(2 * BM, nrows - row0);
+    const int tok_lo = row0 / G, tok_hi = (row0 + rows_here - 1) / G;
+    int key_hi = ctx + tok_hi + 1;                               // exclusive
+    int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    const int split = blockIdx.y;
+    if (p.num_splits > 1) {
+        key_lo = max(key_lo, split * p.split_len);
+        key_hi = min(key_hi, (split + 1) * p.split_len);
+    }
+    const int t_begin = key_lo / BN, t_end = (key_hi + BN - 1) / BN;
+    const int ntiles = t_end - t_begin;
+    if (ntiles <= 0) {
+        // (only with splits) no key of this split is visible: an empty partial result, nothing allocated
+        for (int e = threadIdx.x; e < rows_here * D; e += blockDim.x) {
+            const int r = e / D, row = row0 + r;
+            const int tok = row / G, g = row - tok * G;
+            const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
+            p.ws_o[(grow * p.num_splits + split) * D + (e - r * D)] = 0.f;
+            if (e - r * D == 0) { p.ws_ml[(grow * p.num_splits + split) * 2] = -INFINITY; p.ws_ml[(grow * p.num_splits + split) * 2 + 1] = 0.f; }
+        }
+        return;
+    }
+    const int ntq = rows_here > BM ? 2 : 1;                      // query tiles in use
+    const uint32_t bar0 = smem_u32(&bars[0]);
+#define BAR(i) (bar0 + 8u * (uint32_t)(i))
+
+    if (warp == 13 && lane == 0) {
+        for (int i = 0; i < PP_NBARS; ++i) mbar_init(BAR(i), (i >= PP_PF && i < PP_OF) || i >= PP_OC ? 128u : 1u);   // thread arrivals; the rest: one commit or copy
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 12) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // queries of both tiles -> shared memory in the K-major swizzled operand layout (rows past the end: zeros)
+    for (int c = threadIdx.x; c < ntq * BM * (D / 8); c += PP_NTHREADS) {
+        const int r = c / (D / 8), chunk = c - r * (D / 8);      // chunk: 8 bfloat16 = 16 bytes
+        const int row = row0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < nrows) {
+            const int tok = row / G, g = row - tok * G;
+            v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + tok) * p.q_stride + (size_t)(kvh * G + g) * D + chunk * 8);
+        }
+        const int qt = r >> 7, rr = r & 127, blk = chunk >> 3, cin = chunk & 7;
+        *reinterpret_cast<uint4*>(Qs + qt * QT_BYTES + blk * QBLK + rr * 128 + ((cin ^ (rr & 7)) << 4)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes of Q become visible to the tensor core
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp < 8) {
+        // ---------------------------------------------------------------- softmax of tile t, one thread per row
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 192;" ::: "memory");
+        const int t = warp >> 2;
+        if (t < ntq) {
+            const int quarter = warp & 3, r = quarter * 32 + lane;
+            const int row = row0 + t * BM + r;
+            const bool valid = row < nrows;
+            const int tok = valid ? row / G : 0;
+            const int pos = valid ? ctx + tok : -1;
+            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            const uint32_t s_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + S_COL + (uint32_t)t * BN;
+            const float sl2 = p.scale_log2;
+            float m_run = -INFINITY, l_run = 0.f;
+            bool ok = true;
+            for (int j = 0; j < ntiles; ++j) {
+                ok = mbar_wait(BAR(PP_SF + t), j & 1, 8);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t sv[BN];
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) tmem_ld32(s_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int key0 = (t_begin + j) * BN;
+                const int hi_col = valid ? pos - key0 : -1, lo_col = lo - key0;
+                const bool tile_full = __all_sync(0xffffffffu, valid && hi_col >= BN - 1 && lo_col <= 0);
+                if (!tile_full) {
+#pragma unroll
+                    for (int i = 0; i < BN; ++i)
+                        if (!(i <= hi_col && i >= lo_col)) sv[i] = 0xff800000u;                   // -inf
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // -inf stays -inf (the scale is positive)
+                // The maximum in use moves only when it has grown by more than the threshold (or was -inf): then the
+                // row of O is scaled by alpha before this tile's product is added.
+                const float m_cand = fmaxf(m_run, mx);
+                const bool up = (m_cand - m_run) > RESCALE_LOG2;             // false for -inf - -inf (NaN)
+                const float alpha = up ? ex2(m_run - m_cand) : 1.f;
+                m_run = up ? m_cand : m_run;
+                if (j > 0) {
+                    alpha_s[t][r] = alpha;
+                    mbar_arrive(BAR(PP_SC + t));
+                }
+                const float msub = m_run == -INFINITY ? 0.f : m_run;
+                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2(fmaf(__uint_as_float(sv[c * 32 + i]), sl2, -msub));
+                        const float p1 = ex2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sl2, -msub));
+                        ls4[(i >> 1) & 3] += p0 + p1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    tmem_st16(s_addr + c * 16, packed);                  // P over the scores: 32 keys = 16 packed columns
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(BAR(PP_PF + t));                                // P is in tensor memory
+                l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
+            }
+            if (ok) {
+                lsum_s[t][r] = l_run;
+                mrun_s[t][r] = m_run;
+                mbar_arrive(BAR(PP_LF + t));
+            }
+        }
+    } else if (warp < 12) {
+        // ---------------------------------------------------------------- correction and epilogue
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::: "memory");
+        const int quarter = warp & 3, r = quarter * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        bool ok = true;
+        for (int j = 1; j < ntiles && ok; ++j) {
+            for (int t = 0; t < ntq; ++t) {
+                ok = mbar_wait(BAR(PP_SC + t), (j - 1) & 1, 9);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const float a = alpha_s[t][r];
+                if (__any_sync(0xffffffffu, a != 1.f)) {
+                    ok = mbar_wait(BAR(PP_OF + t), (j - 1) & 1, 10);        // the product of the tile before has landed
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t ov[32];
+                        tmem_ld32(lane_addr + O_COL + t * D + c * 32, ov);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * a);
+                        tmem_st32(lane_addr + O_COL + t * D + c * 32, ov);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(BAR(PP_OC + t));
+            }
+        }
+        for (int t = 0; t < ntq && ok; ++t) {
+            ok = mbar_wait(BAR(PP_LF + t), 0, 12);
+            if (ok) ok = mbar_wait(BAR(PP_OF + t), (ntiles - 1) & 1, 13);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = row0 + t * BM + r;
+            const bool valid = row < nrows;
+            const int tok = valid ? row / G : 0, g = valid ? row - tok * G : 0;
+            const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
+            const float l_tot = lsum_s[t][r];
+            const bool partial = p.num_splits > 1;
+            const float inv = partial ? 1.f : (l_tot > 0.f ? 1.f / l_tot : 0.f);
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t ov[32];
+                tmem_ld32(lane_addr + O_COL + t * D + c * 32, ov);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (!valid) continue;
+                if (partial) {
+                    float* dst = p.ws_o + (grow * p.num_splits + split) * D + c * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1]),
+                                                                          __uint_as_float(ov[i + 2]), __uint_as_float(ov[i + 3]));
+                } else {
+                    __nv_bfloat16* dst = p.out + grow * D + c * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[i + 2 * k]) * inv, __uint_as_float(ov[i + 2 * k + 1]) * inv);
+                            w[k] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        *reinterpret_cast<uint4*>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+            if (valid && partial) {
+                float* ml = p.ws_ml + (grow * p.num_splits + split) * 2;
+                ml[0] = mrun_s[t][r] * 0.6931471805599453f;          // natural-log units for the merge
+                ml[1] = l_tot;
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory");
+        if (warp == 12) {
+            // ------------------------------------------------------------ copy producer: K_0 V_0 K_1 V_1 ... through the ring.
+            // Lane b looks up the page of box b (a tile is 128 / box_rows boxes) one tile ahead; lane 0 waits and copies.
+            const int ps = p.page_size;
+            const int box_rows = ps < BN ? ps : BN, nboxes = BN / box_rows;
+            const int* table = p.block_table + (size_t)seq * p.table_width;
+            auto box_row = [&](int j) -> int {                  // first row of this lane's box of tile j in the page matrix
+                int y = 0;
+                if (lane < nboxes && j < ntiles) {
+                    const int key = (t_begin + j) * BN + lane * box_rows;
+                    const int pg = key / ps;
+                    const int page = pg < p.table_width ? table[pg] : 0;
+                    y = (page * p.Hkv + kvh) * ps + (key - pg * ps);
+                }
+                return y;
+            };
+            int y_cur = box_row(0);
+            bool go = true;
+            for (int j = 0; j < ntiles && go; ++j) {
+                const int y_next = box_row(j + 1);
+                for (int which = 0; which < 2; ++which) {
+                    const int i = 2 * j + which, st = i % NS;
+                    int ok = 1;
+                    if (lane == 0) ok = mbar_wait_relaxed(BAR(PP_EMPTY + st), ((i / NS) & 1) ^ 1, 1 + which);
+                    if (!__shfl_sync(0xffffffffu, ok, 0)) { go = false; break; }
+                    if (lane == 0) mbar_expect_tx(BAR(PP_FULL + st), KV_BYTES);
+                    for (int b = 0; b < nboxes; ++b) {
+                        const int y = __shfl_sync(0xffffffffu, y_cur, b);
+                        if (lane == 0) {
+#pragma unroll
+                            for (int cb = 0; cb < CB; ++cb)
+                                tma_load_2d(smem_u32(ring + st * KV_BYTES + cb * KVBLK + b * box_rows * 128), which ? &tmV : &tmK,
+                                            BAR(PP_FULL + st), cb * 64, y);
+                        }
+                    }
+                }
+                y_cur = y_next;
+            }
+        } else if (warp == 13 && lane == 0) {
+            // ------------------------------------------------------------ product issuer
+            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            auto issue_s = [&](int t, int st) {
+                const uint32_t k_addr = smem_u32(ring + st * KV_BYTES), q_addr = smem_u32(Qs + t * QT_BYTES);
+#pragma unroll
+                for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + S_COL + t * BN, desc_kmajor(q_addr + cb * QBLK) + (uint64_t)(k * 2),
+                                  desc_kmajor(k_addr + cb * KVBLK) + (uint64_t)(k * 2), idesc_s, (cb | k) != 0);
+                umma_commit(BAR(PP_SF + t));
+            };
+            bool ok = mbar_wait(BAR(PP_FULL + 0), 0, 3);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int t = 0; t < ntq; ++t) issue_s(t, 0);
+                umma_commit(BAR(PP_EMPTY + 0));
+            }
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int iv = 2 * j + 1, stv = iv % NS, ik = 2 * j + 2, stk = ik % NS;
+                const bool has_next = j + 1 < ntiles;
+                if (!mbar_wait(BAR(PP_FULL + stv), (iv / NS) & 1, 5)) { ok = false; break; }
+                for (int t = 0; t < ntq; ++t) {
+                    if (!mbar_wait(BAR(PP_PF + t), j & 1, 7)) { ok = false; break; }
+                    if (j > 0 && !mbar_wait(BAR(PP_OC + t), (j - 1) & 1, 6)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t v_addr = smem_u32(ring + stv * KV_BYTES);
+                    const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)t * BN;        // P sits where the tile's scores sat
+#pragma unroll
+                    for (int k = 0; k < BN / 16; ++k)
+                        umma_bf16_ts(tmem_base + O_COL + t * D, p_tmem + (uint32_t)(k * 8),
+                                     desc_mnmajor(v_addr + (k * 16) * 128, KVBLK), idesc_o, (j | k) != 0);
+                    umma_commit(BAR(PP_OF + t));
+                    if (t == ntq - 1) umma_commit(BAR(PP_EMPTY + stv));
+                    if (has_next) {
+                        // the next scores of this tile go over its P: products of one thread run in the order issued
+                        if (t == 0) {
+                            if (!mbar_wait(BAR(PP_FULL + stk), (ik / NS) & 1, 3)) { ok = false; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        issue_s(t, stk);
+                        if (t == ntq - 1) umma_commit(BAR(PP_EMPTY + stk));
+                    }
+                }
+            }
+        }
+    }
+#undef BAR
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 12) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -587,6 +947,16 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, 
     TTIE_CHECK_LAUNCH("attention_tc");
     return 0;
 }
+template <int D>
+int launch_pp(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, cudaStream_t s) {
+    const size_t smem = 2 * (size_t)(D / 64) * BM * 128 + pp::NS * (size_t)(D / 64) * BN * 128 + 1024;
+    auto k = attn_tc_pp_kernel<D>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    k<<<dim3(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits), pp::PP_NTHREADS, smem, s>>>(mk, mv, p);
+    TTIE_CHECK_LAUNCH("attention_tc (two query tiles)");
+    return 0;
+}
 }  // namespace
 
 // A word of pinned host memory (device-accessible) that also receives the failure code, so the host can look at it
@@ -608,13 +978,15 @@ extern "C" int ttie_attn_tc_supported(int D, int page_size) {
     return (D == 64 || D == 128) && page_size >= 8 && page_size % 8 == 0 && (128 % page_size == 0 || page_size % 128 == 0) && page_size <= 256;
 }
 
+// two_tiles: 0 = a CTA owns one 128-row query tile (any number of rows; decode steps), 1 = a CTA owns 256 rows as two
+// tiles taken in turns (prompt portions).
 // num_splits > 1: the key range is cut into pieces of split_len keys (a multiple of 128) over grid y; the partial
 // results go to `scratch` (ttie_attn_scratch_floats) and a merge kernel writes `out`.
 extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                        int num_pages, const int* block_table, int table_width, int page_size, const int* qsl,
                                        const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
                                        int max_q_len, float scale, int window, int num_splits, int split_len, float* scratch,
-                                       void* stream) {
+                                       int two_tiles, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (!ttie_attn_tc_supported(D, page_size)) TTIE_FAIL("attention_tc: head size %d with pages of %d keys is not supported", D, page_size);
     if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("attention_tc: %d heads are not a multiple of %d kv heads", Hq, Hkv);
@@ -633,13 +1005,14 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.block_table = block_table; p.table_width = table_width;
     p.page_size = page_size; p.qsl = qsl; p.seq_lens = seq_lens; p.out = (__nv_bfloat16*)out;
     p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
-    p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), BM);
+    p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), two_tiles ? 2 * BM : BM);
     p.num_splits = num_splits; p.split_len = split_len;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("attention_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
     const bool ahead = max_q_len * (Hq / Hkv) >= BM;             // full row tiles: a prompt portion
-    const int rc = D == 64 ? (ahead ? launch<64, true>(mk, mv, p, s) : launch<64, false>(mk, mv, p, s))
+    const int rc = two_tiles ? (D == 64 ? launch_pp<64>(mk, mv, p, s) : launch_pp<128>(mk, mv, p, s))
+                 : D == 64 ? (ahead ? launch<64, true>(mk, mv, p, s) : launch<64, false>(mk, mv, p, s))
                            : (ahead ? launch<128, true>(mk, mv, p, s) : launch<128, false>(mk, mv, p, s));
     if (rc) return rc;
     if (num_splits > 1) return attn_merge_bf16(p.ws_o, p.ws_ml, out, T * Hq, num_splits, D, s);

@@ -49,7 +49,8 @@ _SIGNATURES = {
                                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
                                       _c_void, _c_int, _c_void],
     "ttie_paged_attention_tc": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_void],
+                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_int,
+                                _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
 }
@@ -303,7 +304,7 @@ class CudaOps:
         rows = max_q_len * G
         if (dtype == torch.bfloat16 and page_size is not None and rows >= self.attn_tc_min_rows
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
-            return "tc", 1, 0                                   # prompt portions: the tcgen05 kernel
+            return "tcpp", 1, 0                                 # prompt portions: the tcgen05 kernel, two query tiles per CTA
         if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
             plan = self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
             if plan is not None:
@@ -374,7 +375,7 @@ class CudaOps:
         T = qkv.shape[0]
         kernel, num_splits, split_len = plan if plan is not None else self.attention_plan(
             qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
-        if kernel == "tc":
+        if kernel in ("tc", "tcpp"):
             scratch = None
             if num_splits > 1:
                 scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
@@ -382,7 +383,7 @@ class CudaOps:
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                 block_table.shape[1], page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads,
                 num_kv_heads, head_dim, max_q_len, float(scale), int(window), num_splits, split_len, _ptr(scratch),
-                self._stream(qkv)), "paged_attention_tc")
+                1 if kernel == "tcpp" else 0, self._stream(qkv)), "paged_attention_tc")
             self.launches += 2 if num_splits > 1 else 1
             return
         form = {"mma": 0, "mma_c2": 2, "mma_c4": 4}.get(kernel)

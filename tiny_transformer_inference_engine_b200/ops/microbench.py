@@ -148,9 +148,15 @@ def prefill(ops, a):
     qsl = torch.tensor([0, T], dtype=torch.int32, device=DEV)
     sl = torch.tensor([T], dtype=torch.int32, device=DEV)
     o = torch.empty(T, Hq * D, device=DEV, dtype=torch.bfloat16)
-    plan = ops.attention_plan(torch.bfloat16, 1, Hq, Hkv, D, T, T, page)
-    line(f"causal paged attention {plan}", timeit(lambda i: ops.paged_attention(qkv, Hq, Hkv, D, kp, vp, table, page, qsl, sl, 1, T, T, 1 / math.sqrt(D), 0, o), iters=4),
-         flops=4 * Hq * D * T * (T + 1) // 2)
+    planned = ops.attention_plan(torch.bfloat16, 1, Hq, Hkv, D, T, T, page)
+    for plan in dict.fromkeys([planned, ("tcpp", 1, 0), ("tc", 1, 0), ("mma", 1, 0)]):
+        if plan[0].startswith("tc") and not ops.lib.ttie_attn_tc_supported(D, page):
+            continue
+        line(f"causal paged attention {plan}", timeit(lambda i: ops.paged_attention(qkv, Hq, Hkv, D, kp, vp, table, page, qsl, sl, 1, T, T, 1 / math.sqrt(D), 0, o, plan=plan), iters=4),
+             flops=4 * Hq * D * T * (T + 1) // 2)
+    err = ops.tc_error()
+    if err:
+        raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
 
 
 def attention(ops, a):
