@@ -550,26 +550,53 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// Two query tiles per CTA, taken in turns ("ping-pong"): the form for prompt portions.
+// Two query tiles per CTA: the form for prompt portions.
 //
-// A CTA owns 256 query rows as two 128-row tiles that share every key/value tile.  While the softmax threads of one
-// tile work on its scores, the tensor core computes the other tile's products, so neither waits for the other:
-//   warps 0-3    softmax of tile 0, ONE thread per row: the 128 scores of a key tile come out of tensor memory into
-//                registers, so row maximum and sum need no exchange between threads; P goes back over the scores
+// A CTA owns 256 query rows as two 128-row tiles that share every key/value tile, and walks the keys 64 at a time.
+// Each query tile has TWO score buffers in tensor memory, so the scores of key step j+1 are computed while the
+// softmax threads work on step j; and there are two query tiles, so the tensor core always has the other tile's
+// products to do.  Tensor memory: 2 tiles x 2 buffers x 64 columns of scores, 2 x D columns of output.
+//   warps 0-3    softmax of tile 0, ONE thread per row: the 64 scores of a key step come out of tensor memory into
+//                registers, so row maximum and sum need no exchange between threads; P (bfloat16) goes back over
+//                the scores and is the tensor-memory A operand of O += P V
 //   warps 4-7    the same for tile 1
 //   warps 8-11   correction: the running output stays in tensor memory (O += P V accumulates there); when a row's
 //                maximum has grown by more than 2^8 since its output was last scaled, these warps scale the row of O
 //                (tcgen05.ld / st).  Below that threshold the old maximum stays in use - P is then at most 2^8, which
-//                costs bfloat16 nothing - so after the first tiles O is rarely touched.  At the end they divide by
+//                costs bfloat16 nothing - so after the first steps O is rarely touched.  At the end they divide by
 //                the row sum and store.
-//   warp 12      TMA producer: key and value tiles alternate through one ring of four stages
-//   warp 13      one thread issues  S0, S1, then per key tile  O0 += P0 V, S0(next), O1 += P1 V, S1(next)
-// Register budgets follow the roles (setmaxnreg): the softmax threads hold a whole row of scores.
+//   warp 12      TMA producer: key and value tiles through one ring, in the order the products need them
+//                (K0 K1 V0 K2 V1 K3 ...)
+//   warps 13-14  one thread each issues  O += P(j) V(j)  of one tile
+//   warp 15      one thread issues the scores  S(j) = Q K(j)^T  of both tiles, as soon as K(j) is there and P(j-2) is used up
+// Register budgets follow the roles (setmaxnreg).  Threads of one role run up to two steps apart, so every barrier
+// that counts thread arrivals exists twice (by step parity).
 namespace pp {
-constexpr int NS = 4;                                            // stages of the key/value ring
-enum { PP_FULL = 0, PP_EMPTY = NS, PP_SF = 2 * NS, PP_PF = PP_SF + 2, PP_SC = PP_PF + 2, PP_OF = PP_SC + 2, PP_OC = PP_OF + 2, PP_LF = PP_OC + 2, PP_NBARS = PP_LF + 2 };
+constexpr int BNK = 64;                                          // keys per step
+constexpr int NS = 8;                                            // stages of the key/value ring
+enum { PP_FULL = 0, PP_EMPTY = NS, PP_SF = 2 * NS, PP_PF = PP_SF + 4, PP_SC = PP_PF + 4, PP_OC = PP_SC + 4, PP_OF = PP_OC + 4,
+       PP_LF = PP_OF + 4, PP_NBARS = PP_LF + 2 };                // SF, PF, SC, OC, OF: [tile][step parity]
 constexpr int PP_NTHREADS = 512;
 constexpr float RESCALE_LOG2 = 8.f;                              // a row's output is rescaled when its maximum grew by more
+}
+
+// Shared-memory operand descriptors in two words.  The upper word is the same for every operand here: 8-row groups
+// 1024 bytes apart, descriptor version of sm_100, 128-byte swizzle.  The lower word holds the address (in units of 16
+// bytes) and the leading offset: 1 (unused) for a K-major operand, the distance between 64-column blocks for an
+// MN-major one.
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16); }
+template <bool ACC>
+__device__ __forceinline__ void umma_ss_lean(uint32_t tmem_c, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+                 ::"r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ts_lean(uint32_t tmem_c, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+                 ::"r"(tmem_c), "r"(tmem_a), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
 }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -587,17 +614,17 @@ __global__ void __launch_bounds__(pp::PP_NTHREADS, 1)
 attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
     using namespace pp;
     constexpr int CB = D / 64;
-    constexpr uint32_t QBLK = BM * 128, KVBLK = BN * 128;        // bytes of one 64-column block of a 128-row tile
+    constexpr uint32_t QBLK = BM * 128, KVBLK = BNK * 128;       // bytes of one 64-column block of a query / key tile
     constexpr uint32_t QT_BYTES = CB * QBLK, KV_BYTES = CB * KVBLK;
-    constexpr uint32_t TMEM_COLS = 512;                          // S0, S1 (128 columns each), O0, O1 (D each)
-    constexpr uint32_t S_COL = 0, O_COL = 256;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t S_COL = 0, O_COL = 256;                   // scores of (tile t, buffer b) at t * 128 + b * 64; output of tile t at 256 + t * D
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = smem;                                    // [2 tiles]
     unsigned char* ring = Qs + 2 * QT_BYTES;                     // [NS stages]
     __shared__ __align__(8) unsigned long long bars[PP_NBARS];
     __shared__ uint32_t tmem_slot;
-    __shared__ float alpha_s[2][BM];                             // factor by which a row of O has to be scaled before the next product
+    __shared__ float alpha_s[2][2][BM];                          // [step parity][tile]: factor for a row of O before the step's product is added
     __shared__ float lsum_s[2][BM], mrun_s[2][BM];               // a row's sum and the maximum it is relative to, at the end
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -619,9 +646,9 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         key_lo = max(key_lo, split * p.split_len);
         key_hi = min(key_hi, (split + 1) * p.split_len);
     }
-    const int t_begin = key_lo / BN, t_end = (key_hi + BN - 1) / BN;
-    const int ntiles = t_end - t_begin;
-    if (ntiles <= 0) {
+    const int t_begin = key_lo / BNK, t_end = (key_hi + BNK - 1) / BNK;
+    const int nsteps = t_end - t_begin;
+    if (nsteps <= 0) {
         // (only with splits) no key of this split is visible: an empty partial result, nothing allocated
         for (int e = threadIdx.x; e < rows_here * D; e += blockDim.x) {
             const int r = e / D, row = row0 + r;
@@ -637,7 +664,8 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 #define BAR(i) (bar0 + 8u * (uint32_t)(i))
 
     if (warp == 13 && lane == 0) {
-        for (int i = 0; i < PP_NBARS; ++i) mbar_init(BAR(i), (i >= PP_PF && i < PP_OF) || i >= PP_OC ? 128u : 1u);   // thread arrivals; the rest: one commit or copy
+        for (int i = 0; i < PP_NBARS; ++i)                       // PF, SC, OC, LF count thread arrivals, EMPTY the issuers; the rest one commit or copy
+            mbar_init(BAR(i), (i >= PP_PF && i < PP_OF) || i >= PP_LF ? 128u : (i >= PP_EMPTY && i < PP_SF) ? (uint32_t)ntq : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -674,45 +702,51 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             const int tok = valid ? row / G : 0;
             const int pos = valid ? ctx + tok : -1;
             const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-            const uint32_t s_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + S_COL + (uint32_t)t * BN;
+            const uint32_t s_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + S_COL + (uint32_t)t * 128;
             const float sl2 = p.scale_log2;
             float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
-            for (int j = 0; j < ntiles; ++j) {
-                ok = mbar_wait(BAR(PP_SF + t), j & 1, 8);
+            for (int j = 0; j < nsteps; ++j) {
+                const int b = j & 1;
+                const uint32_t par = (j >> 1) & 1;
+                const uint32_t s_addr = s_base + (uint32_t)b * BNK;
+                ok = mbar_wait(BAR(PP_SF + 2 * t + b), par, 8);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t sv[BN];
+                uint32_t sv[BNK];
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) tmem_ld32(s_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+                for (int c = 0; c < BNK / 32; ++c) tmem_ld32(s_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int key0 = (t_begin + j) * BN;
+                const int key0 = (t_begin + j) * BNK;
                 const int hi_col = valid ? pos - key0 : -1, lo_col = lo - key0;
-                const bool tile_full = __all_sync(0xffffffffu, valid && hi_col >= BN - 1 && lo_col <= 0);
+                const bool tile_full = __all_sync(0xffffffffu, valid && hi_col >= BNK - 1 && lo_col <= 0);
                 if (!tile_full) {
 #pragma unroll
-                    for (int i = 0; i < BN; ++i)
+                    for (int i = 0; i < BNK; ++i)
                         if (!(i <= hi_col && i >= lo_col)) sv[i] = 0xff800000u;                   // -inf
                 }
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                float mx8[8];
 #pragma unroll
-                for (int i = 0; i < BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
-                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // -inf stays -inf (the scale is positive)
+                for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(sv[i]), __uint_as_float(sv[i + 8]));
+#pragma unroll
+                for (int i = 16; i < BNK; i += 16)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) mx8[k] = fmaxf(mx8[k], fmaxf(__uint_as_float(sv[i + k]), __uint_as_float(sv[i + 8 + k])));
+                const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                       fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * sl2;   // -inf stays -inf (the scale is positive)
                 // The maximum in use moves only when it has grown by more than the threshold (or was -inf): then the
-                // row of O is scaled by alpha before this tile's product is added.
+                // row of O is scaled by alpha before this step's product is added.
                 const float m_cand = fmaxf(m_run, mx);
                 const bool up = (m_cand - m_run) > RESCALE_LOG2;             // false for -inf - -inf (NaN)
                 const float alpha = up ? ex2(m_run - m_cand) : 1.f;
                 m_run = up ? m_cand : m_run;
-                if (j > 0) {
-                    alpha_s[t][r] = alpha;
-                    mbar_arrive(BAR(PP_SC + t));
-                }
+                alpha_s[b][t][r] = j > 0 ? alpha : 1.f;                      // nothing to scale before the first product
+                mbar_arrive(BAR(PP_SC + 2 * t + b));
                 const float msub = m_run == -INFINITY ? 0.f : m_run;
                 float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < BNK / 32; ++c) {
                     uint32_t packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
@@ -726,7 +760,7 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(BAR(PP_PF + t));                                // P is in tensor memory
+                mbar_arrive(BAR(PP_PF + 2 * t + b));                     // P is in tensor memory
                 l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
             }
             if (ok) {
@@ -741,15 +775,23 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const int quarter = warp & 3, r = quarter * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         bool ok = true;
-        for (int j = 1; j < ntiles && ok; ++j) {
+        // A parity wait tells "phase k is over" from "phase k is running" only.  The softmax - hence this warp - may be
+        // two steps ahead of the products, and this warp does not look at every product, so the products of a tile
+        // signal two barriers in turn (by step parity): whoever waits for product j is then at most one phase of
+        // that barrier away from it.
+        auto product_done = [&](int t, int j) -> bool {         // waits until product j of tile t has landed
+            return __all_sync(0xffffffffu, mbar_wait(BAR(PP_OF + 2 * t + (j & 1)), (j >> 1) & 1, 10));
+        };
+        for (int j = 0; j < nsteps && ok; ++j) {
+            const int b = j & 1;
+            const uint32_t par = (j >> 1) & 1;
             for (int t = 0; t < ntq; ++t) {
-                ok = mbar_wait(BAR(PP_SC + t), (j - 1) & 1, 9);
+                ok = mbar_wait(BAR(PP_SC + 2 * t + b), par, 9);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const float a = alpha_s[t][r];
-                if (__any_sync(0xffffffffu, a != 1.f)) {
-                    ok = mbar_wait(BAR(PP_OF + t), (j - 1) & 1, 10);        // the product of the tile before has landed
-                    ok = __all_sync(0xffffffffu, ok);
+                const float a = alpha_s[b][t][r];
+                if (__any_sync(0xffffffffu, a != 1.f)) {                // never in step 0
+                    ok = product_done(t, j - 1);                        // the product of the step before has landed
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -764,13 +806,13 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(BAR(PP_OC + t));
+                mbar_arrive(BAR(PP_OC + 2 * t + b));
             }
         }
         for (int t = 0; t < ntq && ok; ++t) {
             ok = mbar_wait(BAR(PP_LF + t), 0, 12);
-            if (ok) ok = mbar_wait(BAR(PP_OF + t), (ntiles - 1) & 1, 13);
             ok = __all_sync(0xffffffffu, ok);
+            if (ok) ok = product_done(t, nsteps - 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = row0 + t * BM + r;
@@ -815,88 +857,116 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory");
         if (warp == 12) {
-            // ------------------------------------------------------------ copy producer: K_0 V_0 K_1 V_1 ... through the ring.
-            // Lane b looks up the page of box b (a tile is 128 / box_rows boxes) one tile ahead; lane 0 waits and copies.
+            // ------------------------------------------------------------ copy producer: K0 K1 V0 K2 V1 K3 ... through the ring.
+            // Lane x looks up the page of box x of a tile (a tile is 64 / box_rows boxes) ahead of its use; lane 0 waits
+            // for the stage and issues the copies.
             const int ps = p.page_size;
-            const int box_rows = ps < BN ? ps : BN, nboxes = BN / box_rows;
+            const int box_rows = ps < BNK ? ps : BNK, nboxes = BNK / box_rows;
             const int* table = p.block_table + (size_t)seq * p.table_width;
             auto box_row = [&](int j) -> int {                  // first row of this lane's box of tile j in the page matrix
                 int y = 0;
-                if (lane < nboxes && j < ntiles) {
-                    const int key = (t_begin + j) * BN + lane * box_rows;
+                if (lane < nboxes && j < nsteps) {
+                    const int key = (t_begin + j) * BNK + lane * box_rows;
                     const int pg = key / ps;
                     const int page = pg < p.table_width ? table[pg] : 0;
                     y = (page * p.Hkv + kvh) * ps + (key - pg * ps);
                 }
                 return y;
             };
-            int y_cur = box_row(0);
-            bool go = true;
-            for (int j = 0; j < ntiles && go; ++j) {
-                const int y_next = box_row(j + 1);
-                for (int which = 0; which < 2; ++which) {
-                    const int i = 2 * j + which, st = i % NS;
-                    int ok = 1;
-                    if (lane == 0) ok = mbar_wait_relaxed(BAR(PP_EMPTY + st), ((i / NS) & 1) ^ 1, 1 + which);
-                    if (!__shfl_sync(0xffffffffu, ok, 0)) { go = false; break; }
-                    if (lane == 0) mbar_expect_tx(BAR(PP_FULL + st), KV_BYTES);
-                    for (int b = 0; b < nboxes; ++b) {
-                        const int y = __shfl_sync(0xffffffffu, y_cur, b);
-                        if (lane == 0) {
+            int it = 0;                                         // tiles copied so far
+            auto emit = [&](const CUtensorMap* map, int y_lane, int code) -> bool {
+                const int st = it % NS;
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait_relaxed(BAR(PP_EMPTY + st), ((it / NS) & 1) ^ 1, code);
+                if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
+                if (lane == 0) mbar_expect_tx(BAR(PP_FULL + st), KV_BYTES);
+                for (int x = 0; x < nboxes; ++x) {
+                    const int y = __shfl_sync(0xffffffffu, y_lane, x);
+                    if (lane == 0) {
 #pragma unroll
-                            for (int cb = 0; cb < CB; ++cb)
-                                tma_load_2d(smem_u32(ring + st * KV_BYTES + cb * KVBLK + b * box_rows * 128), which ? &tmV : &tmK,
-                                            BAR(PP_FULL + st), cb * 64, y);
-                        }
+                        for (int cb = 0; cb < CB; ++cb)
+                            tma_load_2d(smem_u32(ring + st * KV_BYTES + cb * KVBLK + x * box_rows * 128), map, BAR(PP_FULL + st), cb * 64, y);
                     }
                 }
-                y_cur = y_next;
-            }
-        } else if (warp == 13 && lane == 0) {
-            // ------------------------------------------------------------ product issuer
-            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            auto issue_s = [&](int t, int st) {
-                const uint32_t k_addr = smem_u32(ring + st * KV_BYTES), q_addr = smem_u32(Qs + t * QT_BYTES);
-#pragma unroll
-                for (int cb = 0; cb < CB; ++cb)
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_base + S_COL + t * BN, desc_kmajor(q_addr + cb * QBLK) + (uint64_t)(k * 2),
-                                  desc_kmajor(k_addr + cb * KVBLK) + (uint64_t)(k * 2), idesc_s, (cb | k) != 0);
-                umma_commit(BAR(PP_SF + t));
+                ++it;
+                return true;
             };
-            bool ok = mbar_wait(BAR(PP_FULL + 0), 0, 3);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int t = 0; t < ntq; ++t) issue_s(t, 0);
-                umma_commit(BAR(PP_EMPTY + 0));
+            int y0 = box_row(0), y1 = box_row(1), y2 = box_row(2);   // tiles j, j+1, j+2
+            bool go = emit(&tmK, y0, 1);
+            if (go && nsteps > 1) go = emit(&tmK, y1, 1);
+            for (int j = 0; j < nsteps && go; ++j) {
+                const int y3 = box_row(j + 3);
+                go = emit(&tmV, y0, 2);
+                if (go && j + 2 < nsteps) go = emit(&tmK, y2, 1);
+                y0 = y1; y1 = y2; y2 = y3;
             }
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const int iv = 2 * j + 1, stv = iv % NS, ik = 2 * j + 2, stk = ik % NS;
-                const bool has_next = j + 1 < ntiles;
-                if (!mbar_wait(BAR(PP_FULL + stv), (iv / NS) & 1, 5)) { ok = false; break; }
-                for (int t = 0; t < ntq; ++t) {
-                    if (!mbar_wait(BAR(PP_PF + t), j & 1, 7)) { ok = false; break; }
-                    if (j > 0 && !mbar_wait(BAR(PP_OC + t), (j - 1) & 1, 6)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t v_addr = smem_u32(ring + stv * KV_BYTES);
-                    const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)t * BN;        // P sits where the tile's scores sat
+        } else if (lane == 0) {
+            // ------------------------------------------------------------ product issuers
+            // Measured on this part: after a thread has issued tcgen05.mma, its next instruction that touches memory
+            // or a barrier - an mbarrier wait, a flag poll, a named barrier; tcgen05.commit itself costs 46 clocks -
+            // does not complete until those products have finished, 160-260 clocks after the tensor core is done with
+            // them.  One issuing thread therefore leaves the tensor core idle for that long between batches.  Three
+            // threads issue here, each blocked only behind its own batch: warp 15 the scores of both tiles, warps 13
+            // and 14 the P V products of one tile each.  Between threads nothing is ordered by issue: S(j+2) goes over
+            // P(j) only after the barrier of O += P(j) V(j) has completed.
+            // A product of 48-64 clocks leaves its thread a dozen instructions: the descriptors' upper words are
+            // constants, the lower words are one addition away from values kept in registers.
+            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BNK >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // position of a tile in the ring's order K0 K1 V0 K2 V1 K3 ... V(n-2) V(n-1)
+            auto k_index = [&](int j) { return j < 2 ? j : 2 * j - 1; };
+            auto v_index = [&](int j) { return j == nsteps - 1 ? 2 * nsteps - 1 : 2 * j + 2; };
+            if (warp == 15) {
+                uint32_t q_lo[2][CB];                           // lower descriptor words of the query blocks
 #pragma unroll
-                    for (int k = 0; k < BN / 16; ++k)
-                        umma_bf16_ts(tmem_base + O_COL + t * D, p_tmem + (uint32_t)(k * 8),
-                                     desc_mnmajor(v_addr + (k * 16) * 128, KVBLK), idesc_o, (j | k) != 0);
-                    umma_commit(BAR(PP_OF + t));
-                    if (t == ntq - 1) umma_commit(BAR(PP_EMPTY + stv));
-                    if (has_next) {
-                        // the next scores of this tile go over its P: products of one thread run in the order issued
-                        if (t == 0) {
-                            if (!mbar_wait(BAR(PP_FULL + stk), (ik / NS) & 1, 3)) { ok = false; break; }
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int cb = 0; cb < CB; ++cb) q_lo[t][cb] = desc_lo(smem_u32(Qs + t * QT_BYTES + cb * QBLK), 16);
+                const uint32_t ring_k_lo = desc_lo(smem_u32(ring), 16);
+                for (int j = 0; j < nsteps; ++j) {
+                    const int b = j & 1, idx = k_index(j), st = idx % NS;
+                    if (!mbar_wait(BAR(PP_FULL + st), (idx / NS) & 1, 3)) break;
+                    const uint32_t k_lo = ring_k_lo + (uint32_t)st * (KV_BYTES >> 4);
+                    bool ok = true;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (t < ntq) {
+                            // the buffer holds P(j-2) until its product with V has finished
+                            if (j >= 2 && !mbar_wait(BAR(PP_OF + 2 * t + b), ((j - 2) >> 1) & 1, 4)) { ok = false; break; }
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            const uint32_t d = tmem_base + S_COL + (uint32_t)t * 128 + (uint32_t)b * BNK;
+#pragma unroll
+                            for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    if (cb | k) umma_ss_lean<true>(d, q_lo[t][cb] + 2 * k, k_lo + cb * (KVBLK >> 4) + 2 * k, idesc_s);
+                                    else umma_ss_lean<false>(d, q_lo[t][cb] + 2 * k, k_lo + cb * (KVBLK >> 4) + 2 * k, idesc_s);
+                                }
+                            umma_commit(BAR(PP_SF + 2 * t + b));
+                            umma_commit(BAR(PP_EMPTY + st));           // one arrival per tile in use
                         }
-                        issue_s(t, stk);
-                        if (t == ntq - 1) umma_commit(BAR(PP_EMPTY + stk));
                     }
+                    if (!ok) break;
+                }
+            } else if (warp - 13 < ntq) {
+                const int t = warp - 13;
+                const uint32_t ring_v_lo = desc_lo(smem_u32(ring), KVBLK);
+                const uint32_t s_tmem = tmem_base + S_COL + (uint32_t)t * 128, o_tmem = tmem_base + O_COL + (uint32_t)t * D;
+                for (int j = 0; j < nsteps; ++j) {
+                    const int b = j & 1, idx = v_index(j), st = idx % NS;
+                    const uint32_t par = (j >> 1) & 1;
+                    if (!mbar_wait(BAR(PP_FULL + st), (idx / NS) & 1, 5)) break;
+                    if (!mbar_wait(BAR(PP_PF + 2 * t + b), par, 7)) break;
+                    if (!mbar_wait(BAR(PP_OC + 2 * t + b), par, 6)) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t v_lo = ring_v_lo + (uint32_t)st * (KV_BYTES >> 4);
+                    const uint32_t p_tmem = s_tmem + (uint32_t)b * BNK;      // P sits where the step's scores sat
+                    if (j) umma_ts_lean<true>(o_tmem, p_tmem, v_lo, idesc_o);
+                    else umma_ts_lean<false>(o_tmem, p_tmem, v_lo, idesc_o);
+#pragma unroll
+                    for (int k = 1; k < BNK / 16; ++k) umma_ts_lean<true>(o_tmem, p_tmem + (uint32_t)(k * 8), v_lo + k * 128, idesc_o);   // 16 keys = 2048 bytes on
+                    umma_commit(BAR(PP_OF + 2 * t + b));
+                    umma_commit(BAR(PP_EMPTY + st));
                 }
             }
         }
@@ -949,7 +1019,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, 
 }
 template <int D>
 int launch_pp(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, cudaStream_t s) {
-    const size_t smem = 2 * (size_t)(D / 64) * BM * 128 + pp::NS * (size_t)(D / 64) * BN * 128 + 1024;
+    const size_t smem = 2 * (size_t)(D / 64) * BM * 128 + pp::NS * (size_t)(D / 64) * pp::BNK * 128 + 1024;
     auto k = attn_tc_pp_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
@@ -998,7 +1068,8 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     if (num_splits > 65535) TTIE_FAIL("attention_tc: too many splits (%d)", num_splits);
     CUtensorMap mk, mv;
     const long long rows = (long long)num_pages * Hkv * page_size;
-    const int box_rows = page_size < BN ? page_size : BN;
+    const int tile_keys = two_tiles ? pp::BNK : BN;              // keys per copy tile of the kernel
+    const int box_rows = page_size < tile_keys ? page_size : tile_keys;
     if (make_page_map(&mk, k_pages, rows, D, box_rows)) return -1;
     if (make_page_map(&mv, v_pages, rows, D, box_rows)) return -1;
     AttnTcParams p;
