@@ -580,6 +580,16 @@ constexpr int PP_NTHREADS = 512;
 constexpr float RESCALE_LOG2 = 8.f;                              // a row's output is rescaled when its maximum grew by more
 }
 
+// Two float32 operations in one instruction (fma.rn.f32x2 / add.rn.f32x2 of sm_100): the softmax threads are short of
+// issue slots, not of arithmetic.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}" : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {      // (d0, d1) += (a0, a1)
+    asm("{\n\t.reg .b64 ra, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\tadd.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
 // Shared-memory operand descriptors in two words.  The upper word is the same for every operand here: 8-row groups
 // 1024 bytes apart, descriptor version of sm_100, 128-byte swizzle.  The lower word holds the address (in units of 16
 // bytes) and the leading offset: 1 (unused) for a K-major operand, the distance between 64-column blocks for an
@@ -745,14 +755,16 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 mbar_arrive(BAR(PP_SC + 2 * t + b));
                 const float msub = m_run == -INFINITY ? 0.f : m_run;
                 float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+                const float nmsub = -msub;
 #pragma unroll
                 for (int c = 0; c < BNK / 32; ++c) {
                     uint32_t packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float p0 = ex2(fmaf(__uint_as_float(sv[c * 32 + i]), sl2, -msub));
-                        const float p1 = ex2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sl2, -msub));
-                        ls4[(i >> 1) & 3] += p0 + p1;
+                        float x0, x1;
+                        fma2(x0, x1, __uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1]), sl2, nmsub);
+                        const float p0 = ex2(x0), p1 = ex2(x1);
+                        add2(ls4[(i >> 1) & 1], ls4[2 + ((i >> 1) & 1)], p0, p1);
                         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
                     }

@@ -91,6 +91,7 @@ class CudaOps:
         self.attn_cluster_tiles_per_warp = 1    # ... and only while a warp walks at most this many 64-key tiles
         self._cluster_max = {}
         self.attn_tc_min_split = 256            # keys per CTA from which the tcgen05 kernel splits a decode step's key range
+        self.attn_tcpp_min_split = 1024         # keys per CTA below which a prompt portion's key range is not cut
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
         self.lib.ttie_attn_tc_supported.restype = _c_int
@@ -304,7 +305,14 @@ class CudaOps:
         rows = max_q_len * G
         if (dtype == torch.bfloat16 and page_size is not None and rows >= self.attn_tc_min_rows
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
-            return "tcpp", 1, 0                                 # prompt portions: the tcgen05 kernel, two query tiles per CTA
+            # prompt portions: the tcgen05 kernel with two query tiles per CTA; a short portion behind a long context
+            # fills the GPU only if the key range is cut as well
+            base = num_seqs * num_kv_heads * math.ceil(rows / 256)
+            n = max(1, min(NUM_SMS // base, max_kv_len // self.attn_tcpp_min_split)) if base <= NUM_SMS // 2 else 1
+            if n > 1:
+                split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
+                n = math.ceil(max_kv_len / split_len)
+            return ("tcpp", n, split_len) if n > 1 else ("tcpp", 1, 0)
         if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
             plan = self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
             if plan is not None:
