@@ -530,6 +530,25 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n):
     assert ops.tc_error() == 0
 
 
+def test_tcgen05_issue_probe(ops):
+    """The issue probe (the measurement the tensor-core kernels' thread layout rests on) runs, every wait in it ends,
+    and a wait after a batch of products costs the issuing thread more than the products themselves."""
+    out = torch.zeros(2, dtype=torch.int64, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    took = {}
+    for n, tm, after in ((64, 0, 0), (64, 0, 3), (64, 0, 6), (128, 0, 0), (256, 0, 0), (64, 1, 0), (128, 1, 0)):
+        ops._check(ops.lib.ttie_probe_mma_issue(n, tm, after, 32, out.data_ptr(), stream), "issue probe")
+        torch.cuda.synchronize()
+        issued, finished = out.tolist()
+        assert 0 < issued <= finished, (n, tm, after, issued, finished)
+        took[n, tm, after] = finished / 32
+    assert took[256, 0, 0] > 900                                  # 8 products of 128 clocks cannot take less
+    assert took[64, 0, 3] > took[64, 0, 0] + 100                  # the wait does not return before the products have finished
+    from tiny_transformer_inference_engine_b200.ops import KernelError
+    with pytest.raises(KernelError, match="64-wide"):
+        ops._check(ops.lib.ttie_probe_mma_issue(128, 0, 3, 32, out.data_ptr(), stream), "issue probe")
+
+
 # ------------------------------------------------------------------------------------------ tcgen05 attention
 TC_SHAPES = [(32, 1, 128, 64), (32, 1, 128, 16), (8, 2, 64, 8), (3, 1, 64, 128), (71, 1, 64, 64), (4, 2, 128, 32), (5, 5, 64, 256)]
 

@@ -41,8 +41,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 //   0 nothing   1 tcgen05.commit   2 commit + wait for that commit   3 commit + wait on a barrier that completed long ago
 //   4 commit + tcgen05.fence::after_thread_sync   5 commit + poll of a shared-memory flag that is set
 //   6 as 3, with a second thread (another warp) doing the same into an accumulator of its own
-template <int N, bool ATMEM>
-__global__ void __launch_bounds__(128, 1) issue_probe_kernel(int after, int batches, long long* out) {
+template <int N, bool ATMEM, int AFTER>
+__global__ void __launch_bounds__(128, 1) issue_probe_kernel(int batches, long long* out) {
+    constexpr int after = AFTER;
     extern __shared__ unsigned char dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) unsigned long long bars[5];
@@ -99,13 +100,13 @@ __global__ void __launch_bounds__(128, 1) issue_probe_kernel(int after, int batc
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tm), "r"(512) : "memory");
 }
 
-template <int N, bool ATMEM>
-int launch_probe(int after, int batches, long long* out, cudaStream_t s) {
+template <int N, bool ATMEM, int AFTER>
+int launch_probe(int batches, long long* out, cudaStream_t s) {
     const size_t smem = 98 * 1024;
-    auto k = issue_probe_kernel<N, ATMEM>;
+    auto k = issue_probe_kernel<N, ATMEM, AFTER>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TTIE_FAIL("issue probe: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-    k<<<148, 128, smem, s>>>(after, batches, out);
+    k<<<148, 128, smem, s>>>(batches, out);
     TTIE_CHECK_LAUNCH("issue probe");
     return 0;
 }
@@ -113,18 +114,29 @@ int launch_probe(int after, int batches, long long* out, cudaStream_t s) {
 
 // Runs `batches` batches of 8 products [128 x N x 16] (A from shared or tensor memory) on every SM and writes, for
 // the first CTA, out[0] = clocks until the last product was issued and out[1] = clocks until all had finished
-// (-1 if a wait ran out).  out: two 64-bit integers in device memory.
+// (-1 if a wait ran out).  out: two 64-bit integers in device memory.  `after` other than 0 is built for 64-wide
+// products from shared memory.
 extern "C" int ttie_probe_mma_issue(int n, int a_in_tmem, int after, int batches, long long* out, void* stream) {
     if (after < 0 || after > 6 || batches <= 0) TTIE_FAIL("issue probe: after must be 0..6 and batches positive");
-    if (after == 6 && (n != 64 || a_in_tmem)) TTIE_FAIL("issue probe: the two-thread form is built for 64-wide products from shared memory");
+    if (after && (n != 64 || a_in_tmem)) TTIE_FAIL("issue probe: what follows a batch is varied only for 64-wide products from shared memory");
     cudaStream_t s = (cudaStream_t)stream;
     if (a_in_tmem) {
-        if (n == 64) return launch_probe<64, true>(after, batches, out, s);
-        if (n == 128) return launch_probe<128, true>(after, batches, out, s);
+        if (n == 64) return launch_probe<64, true, 0>(batches, out, s);
+        if (n == 128) return launch_probe<128, true, 0>(batches, out, s);
     } else {
-        if (n == 64) return launch_probe<64, false>(after, batches, out, s);
-        if (n == 128) return launch_probe<128, false>(after, batches, out, s);
-        if (n == 256) return launch_probe<256, false>(after, batches, out, s);
+        if (n == 64) {
+            switch (after) {
+                case 0: return launch_probe<64, false, 0>(batches, out, s);
+                case 1: return launch_probe<64, false, 1>(batches, out, s);
+                case 2: return launch_probe<64, false, 2>(batches, out, s);
+                case 3: return launch_probe<64, false, 3>(batches, out, s);
+                case 4: return launch_probe<64, false, 4>(batches, out, s);
+                case 5: return launch_probe<64, false, 5>(batches, out, s);
+                default: return launch_probe<64, false, 6>(batches, out, s);
+            }
+        }
+        if (n == 128) return launch_probe<128, false, 0>(batches, out, s);
+        if (n == 256) return launch_probe<256, false, 0>(batches, out, s);
     }
     TTIE_FAIL("issue probe: products %d wide with A in %s memory are not built", n, a_in_tmem ? "tensor" : "shared");
 }

@@ -216,14 +216,16 @@ def issue(ops, a):
              "+ commit + tcgen05.fence::after_thread_sync", "+ commit + poll of a shared-memory flag that is set",
              "+ commit + finished-barrier wait, two issuing threads (clocks per pair of batches)"]
     stream = torch.cuda.current_stream().cuda_stream
+    def run(n, tm, after):
+        for _ in range(2):
+            ops._check(ops.lib.ttie_probe_mma_issue(n, tm, after, batches, out.data_ptr(), stream), "issue probe")
+            torch.cuda.synchronize()
+        return [v / batches for v in out.tolist()]
+
     for n, tm in ((64, 0), (128, 0), (256, 0), (64, 1), (128, 1)):
         for after in (range(7) if (n, tm) == (64, 0) else (0,)):
-            for _ in range(2):
-                ops._check(ops.lib.ttie_probe_mma_issue(n, tm, after, batches, out.data_ptr(), stream), "issue probe")
-                torch.cuda.synchronize()
-            t = out.tolist()
-            print(f"N={n:3d} A in {'tensor' if tm else 'shared'} memory, {names[after]:82s} issued {t[0] / batches:7.1f}  finished {t[1] / batches:7.1f}  (tensor core: {8 * n // 2})",
-                  flush=True)
+            t = run(n, tm, after)
+            print(f"N={n:3d} A in {'tensor' if tm else 'shared'} memory, {names[after]:82s} issued {t[0]:7.1f}  finished {t[1]:7.1f}  (tensor core: {8 * n // 2})", flush=True)
 
 
 def main(argv=None):
