@@ -76,26 +76,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
 }
-// K-major operand: rows of 64 bfloat16 (128 bytes), 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// MN-major operand (value tile as B: N = head dimension contiguous, K = keys are the 128-byte rows):
-// 8-key groups 1024 bytes apart (stride offset), 64-column blocks `lbo_bytes` apart (leading offset).
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo_bytes) {
-    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// The same with the A operand in tensor memory (lane = row, 32-bit columns hold two consecutive bfloat16 of K).
-__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(tmem_c), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
                  "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -130,6 +110,29 @@ __device__ __forceinline__ float ex2(float x) {                // 2^x, one instr
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Shared-memory operand descriptors in two words.  The upper word is the same for every operand here: 8-row groups
+// 1024 bytes apart, descriptor version of sm_100, 128-byte swizzle.  The lower word holds the address (in units of 16
+// bytes) and the leading offset.  K-major operand (queries, keys): rows of 64 bfloat16 = 128 bytes, leading offset
+// unused (1).  MN-major operand (the value tile as B: the head dimension is contiguous, the keys are the 128-byte
+// rows): leading offset = distance between 64-column blocks.  An operand's next K step is 32 bytes (K-major) or 16
+// rows = 2048 bytes (MN-major) further on: one addition to the lower word.
+// The products' A operand comes from shared memory (umma_ss_lean) or from tensor memory (umma_ts_lean: lane = row,
+// 32-bit columns hold two consecutive bfloat16 of K).
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16); }
+template <bool ACC>
+__device__ __forceinline__ void umma_ss_lean(uint32_t tmem_c, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+                 ::"r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ts_lean(uint32_t tmem_c, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+                 ::"r"(tmem_c), "r"(tmem_a), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
 }
 
 struct AttnTcParams {
@@ -368,18 +371,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             // O_tile = P V: B (values) MN-major, N = D
             constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // the issuing thread's own instructions count (a product takes 64 clocks): descriptor words one addition away
+            uint32_t q_lo[CB];
+#pragma unroll
+            for (int cb = 0; cb < CB; ++cb) q_lo[cb] = desc_lo(smem_u32(Qs + cb * QBLK), 16);
+            const uint32_t ks_lo = desc_lo(smem_u32(Ks), 16), vs_lo = desc_lo(smem_u32(Vs), KVBLK);
             auto issue_s = [&](int j) -> bool {
                 const int st = j & 1, sb = j & 1;
                 if (!mbar_wait(BAR(KF + st), (j >> 1) & 1, 3)) return false;
                 if (!mbar_wait(BAR(SE + sb), ((j >> 1) & 1) ^ 1, 4)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t k_addr = smem_u32(Ks + st * KV_BYTES), q_addr = smem_u32(Qs);
+                const uint32_t k_lo = ks_lo + (uint32_t)st * (KV_BYTES >> 4), d = tmem_base + S_COL + (uint32_t)sb * BN;
 #pragma unroll
                 for (int cb = 0; cb < CB; ++cb)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_base + S_COL + sb * BN, desc_kmajor(q_addr + cb * QBLK) + (uint64_t)(k * 2),
-                                  desc_kmajor(k_addr + cb * KVBLK) + (uint64_t)(k * 2), idesc_s, (cb | k) != 0);
+                    for (int k = 0; k < 4; ++k) {
+                        if (cb | k) umma_ss_lean<true>(d, q_lo[cb] + 2 * k, k_lo + cb * (KVBLK >> 4) + 2 * k, idesc_s);
+                        else umma_ss_lean<false>(d, q_lo[cb] + 2 * k, k_lo + cb * (KVBLK >> 4) + 2 * k, idesc_s);
+                    }
                 umma_commit(BAR(SF + sb));
                 umma_commit(BAR(KE + st));
                 return true;
@@ -392,12 +401,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 if (!mbar_wait(BAR(OE + ob), ((j >> 1) & 1) ^ 1, 6)) { ok = false; break; }
                 if (!mbar_wait(BAR(PF), j & 1, 7)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v_addr = smem_u32(Vs + st * KV_BYTES);
+                const uint32_t v_lo = vs_lo + (uint32_t)st * (KV_BYTES >> 4), o_tmem = tmem_base + O_COL + (uint32_t)ob * D;
                 const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)(j & 1) * BN;     // P sits where the tile's scores sat
+                umma_ts_lean<false>(o_tmem, p_tmem, v_lo, idesc_o);
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k)
-                    umma_bf16_ts(tmem_base + O_COL + ob * D, p_tmem + (uint32_t)(k * 8),
-                                 desc_mnmajor(v_addr + (k * 16) * 128, KVBLK), idesc_o, k != 0);
+                for (int k = 1; k < BN / 16; ++k) umma_ts_lean<true>(o_tmem, p_tmem + (uint32_t)(k * 8), v_lo + k * 128, idesc_o);   // 16 keys = 2048 bytes on
                 umma_commit(BAR(OF + ob));
                 umma_commit(BAR(VE + st));
                 umma_commit(BAR(SE + (j & 1)));                         // scores / P buffer of this tile is free again
@@ -590,25 +598,6 @@ __device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {
     asm("{\n\t.reg .b64 ra, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\tadd.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
         : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
 }
-// Shared-memory operand descriptors in two words.  The upper word is the same for every operand here: 8-row groups
-// 1024 bytes apart, descriptor version of sm_100, 128-byte swizzle.  The lower word holds the address (in units of 16
-// bytes) and the leading offset: 1 (unused) for a K-major operand, the distance between 64-column blocks for an
-// MN-major one.
-constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16); }
-template <bool ACC>
-__device__ __forceinline__ void umma_ss_lean(uint32_t tmem_c, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
-    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-                 ::"r"(tmem_c), "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
-}
-template <bool ACC>
-__device__ __forceinline__ void umma_ts_lean(uint32_t tmem_c, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc) {
-    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
-                 ::"r"(tmem_c), "r"(tmem_a), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
-}
-
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
