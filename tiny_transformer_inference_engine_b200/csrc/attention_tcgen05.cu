@@ -1,8 +1,11 @@
-// Causal paged attention on tcgen05 tensor cores (bfloat16, head size 64 or 128): prompt portions, and
-// decode steps with the key range cut over CTAs (partial results for the merge kernel).
+// Causal paged attention on tcgen05 tensor cores (bfloat16, head size 64 or 128).  Two kernels:
+//   attn_tc_kernel     one 128-row query tile per CTA: decode steps with the key range cut over CTAs (partial
+//                      results for the merge kernel), and any step with few query rows per request
+//   attn_tc_pp_kernel  two 128-row query tiles per CTA: prompt portions (described where it stands, below)
+// Query rows are (token, head of a kv head's group) pairs, so with multi-query attention 4 tokens x 32 heads
+// share every key/value tile of a 128-row tile.
 //
-// A CTA owns 128 query rows - (token, head of a kv head's group) pairs, so with multi-query attention
-// 4 tokens x 32 heads share every key/value tile - and walks over 128-key tiles:
+// attn_tc_kernel: a CTA owns 128 query rows and walks over 128-key tiles:
 //   warp 0      TMA: key and value tiles straight from the pages (one box per page and 64-column
 //               block, 128-byte swizzle) into a two-stage ring
 //   warp 1      one thread issues  S = Q K^T  (tcgen05.mma, both operands K-major in shared memory,
