@@ -507,6 +507,8 @@ def test_decode_form_is_planned(ops):
     assert ops.attention_plan(torch.bfloat16, 8, 32, 8, 128, 1, 32768, 64)[0] == "mma"      # four rows per kv head
     assert ops.attention_plan(torch.bfloat16, 1, 32, 1, 128, 2048, 2048, 64) == ("tcpp", 1, 0)
     assert ops.attention_plan(torch.bfloat16, 1, 32, 1, 128, 512, 6144, 64) == ("tcpp", 2, 3072)    # a short portion behind a long context
+    assert ops.attention_plan(torch.bfloat16, 1, 32, 1, 128, 512, 512, 64) == ("tc", 1, 0)          # a short portion without one
+    assert ops.attention_plan(torch.bfloat16, 4, 32, 1, 128, 512, 512, 64) == ("tcpp", 1, 0)
     assert ops.attention_plan(torch.bfloat16, 2, 8, 2, 48, 200, 200, 16)[0] == "mma"
 
 

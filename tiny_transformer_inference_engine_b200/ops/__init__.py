@@ -306,14 +306,18 @@ class CudaOps:
         rows = max_q_len * G
         if (dtype == torch.bfloat16 and page_size is not None and rows >= self.attn_tc_min_rows
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
-            # prompt portions: the tcgen05 kernel with two query tiles per CTA; a short portion behind a long context
-            # fills the GPU only if the key range is cut as well
+            # prompt portions: the tcgen05 kernel with two query tiles per CTA.  Where its CTAs fill less than half of
+            # the GPU, a short portion behind a long context has its key range cut as well, and a short portion
+            # without one goes to the one-tile kernel, which has twice the CTAs (measured at 512 tokens x 32 heads:
+            # 16.4 against 21.6 us; the last 512 of 8,192 tokens: 105 us cut in two, 147 us uncut)
             base = num_seqs * num_kv_heads * math.ceil(rows / 256)
-            n = max(1, min(NUM_SMS // base, max_kv_len // self.attn_tcpp_min_split)) if base <= NUM_SMS // 2 else 1
+            if base > NUM_SMS // 2:
+                return "tcpp", 1, 0
+            n = max(1, min(NUM_SMS // base, max_kv_len // self.attn_tcpp_min_split))
             if n > 1:
                 split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
                 n = math.ceil(max_kv_len / split_len)
-            return ("tcpp", n, split_len) if n > 1 else ("tcpp", 1, 0)
+            return ("tcpp", n, split_len) if n > 1 else ("tc", 1, 0)
         if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
             plan = self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
             if plan is not None:

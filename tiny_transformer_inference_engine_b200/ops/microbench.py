@@ -1,6 +1,6 @@
 """Per-kernel timings against their rooflines, at the sizes of a model configuration.
 
-    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|issue|all]
+    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|prefill_attention|issue|all]
                                                                     [--batch 8] [--ctx 4096] [--tokens 2048]
 
 Every kernel is timed alone inside a captured CUDA graph of ``--iters`` launches (so the host's launch
@@ -159,6 +159,42 @@ def prefill(ops, a):
         raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
 
 
+def prefill_attention(ops, a):
+    """Causal attention over prompt lengths and two head layouts (32 heads of 128, 71 heads of 64, one kv head each;
+    pages of 64 and of 16 keys): the two-tile tcgen05 kernel beside the one-tile one, and a 512-token portion behind a
+    long context with the planned split of the key range."""
+    print("== causal attention of one prompt: two-tile tcgen05 kernel | one-tile tcgen05 kernel")
+    for Hq, D, page in ((32, 128, 64), (71, 64, 64), (32, 128, 16)):
+        for T in (512, 2048, 8192):
+            nb = T // page + 2
+            kp = torch.randn(nb, 1, page, D, device=DEV).bfloat16()
+            vp = torch.randn(nb, 1, page, D, device=DEV).bfloat16()
+            table = (torch.arange(nb - 1, device=DEV, dtype=torch.int32) + 1).view(1, -1)
+            qkv = torch.randn(T, (Hq + 2) * D, device=DEV).bfloat16()
+            qsl = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+            sl = torch.tensor([T], dtype=torch.int32, device=DEV)
+            o = torch.empty(T, Hq * D, device=DEV, dtype=torch.bfloat16)
+            for plan in (("tcpp", 1, 0), ("tc", 1, 0)):
+                us = timeit(lambda i: ops.paged_attention(qkv, Hq, 1, D, kp, vp, table, page, qsl, sl, 1, T, T, 1 / math.sqrt(D), 0, o, plan=plan), iters=4)
+                line(f"{Hq} heads of {D}, pages of {page}, {T:5d} tokens {plan}", us, flops=4 * Hq * D * T * (T + 1) // 2)
+    Hq, D, page, T, ctx = 32, 128, 64, 512, 8192
+    nb = ctx // page + 2
+    kp = torch.randn(nb, 1, page, D, device=DEV).bfloat16()
+    vp = torch.randn(nb, 1, page, D, device=DEV).bfloat16()
+    table = (torch.arange(nb - 1, device=DEV, dtype=torch.int32) + 1).view(1, -1)
+    qkv = torch.randn(T, (Hq + 2) * D, device=DEV).bfloat16()
+    qsl = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    sl = torch.tensor([ctx], dtype=torch.int32, device=DEV)
+    o = torch.empty(T, Hq * D, device=DEV, dtype=torch.bfloat16)
+    flops = 4 * Hq * D * (T * (ctx - T) + T * (T + 1) // 2)
+    for plan in dict.fromkeys([ops.attention_plan(torch.bfloat16, 1, Hq, 1, D, T, ctx, page), ("tcpp", 1, 0), ("tc", 1, 0)]):
+        us = timeit(lambda i: ops.paged_attention(qkv, Hq, 1, D, kp, vp, table, page, qsl, sl, 1, T, ctx, 1 / math.sqrt(D), 0, o, plan=plan), iters=4)
+        line(f"last {T} tokens of {ctx} {plan}", us, flops=flops)
+    err = ops.tc_error()
+    if err:
+        raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
+
+
 def attention(ops, a):
     """Decode attention over batch sizes and context lengths: the planned kernel beside the mma.sync tile loop
     with split keys (the plan before the decode form and the tcgen05 splits existed)."""
@@ -230,7 +266,7 @@ def issue(ops, a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "issue", "all"))
+    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "prefill_attention", "issue", "all"))
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -251,6 +287,8 @@ def main(argv=None):
         gemm_tc(ops, a)
     if a.what in ("attention", "all"):
         attention(ops, a)
+    if a.what in ("prefill_attention", "all"):
+        prefill_attention(ops, a)
     if a.what == "issue":
         issue(ops, a)
     return 0
