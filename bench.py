@@ -171,6 +171,84 @@ def decode_kernel_path(eng, batch, start_len, steps, warmup, vocab, synthetic_fi
     return ms, pos[0], eng.ops.launches - l0
 
 
+WORKLOADS = {
+    # BASELINE.json configs[3]: Falcon-7B widths in Llama style, a mixed batch of 32 requests
+    "falcon_mixed": dict(
+        cfg=dict(architecture="mqa_gpt", vocab_size=65024, d_model=4544, num_layers=32, num_heads=71, num_kv_heads=1,
+                 hidden_size=18176, max_seq_len=2048, rope_theta=10000.0, rms_norm_eps=1e-5, bias=False, dtype="bfloat16"),
+        requests=32, prompt_lo=64, prompt_hi=1024, new_tokens=128, token_budget=2048, page=64),
+    # BASELINE.json configs[4]: Gemma-2B layer sizes, 6,144-token prompts in 512-token portions beside decode
+    "gemma_chunked": dict(
+        cfg=dict(architecture="mqa_gpt", vocab_size=256000, d_model=2048, num_layers=18, num_heads=8, num_kv_heads=1,
+                 hidden_size=16384, max_seq_len=8192, rope_theta=10000.0, rms_norm_eps=1e-6, bias=False, dtype="bfloat16"),
+        requests=16, prompt_lo=6144, prompt_hi=6144, new_tokens=256, token_budget=512, page=64),
+}
+
+
+def run_workload(name, pk, layers=None):
+    """One of BASELINE.json's serving workloads through ``Engine.generate`` (host token lists in and out): requests are
+    admitted, their prompts cut into portions under the token budget and run beside the decoded tokens of the others.
+    Timed by the host's clock around the whole call, after one untimed run of the same workload.  ``frac`` is the sum
+    over the steps of the time each would need at the roofline (the larger of bytes / HBM peak and flops / bf16 peak)
+    divided by the time taken."""
+    import torch
+    from tiny_transformer_inference_engine_b200 import Engine, ModelConfig, EngineConfig, CacheConfig, SchedulerConfig, SamplingParams
+    from tiny_transformer_inference_engine_b200.weights import random_tensors
+    w = WORKLOADS[name]
+    cfg, n_req, page = w["cfg"], w["requests"], w["page"]
+    full_layers = cfg["num_layers"]
+    layers = layers or full_layers
+    mc = ModelConfig.from_dict({**cfg, "num_layers": layers})
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(w["prompt_lo"], w["prompt_hi"] + 1, (n_req,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    pages = sum(-(-(n + w["new_tokens"]) // page) for n in lens) + 2 * n_req + 2
+    ec = EngineConfig(dtype="bfloat16", device="cuda:0", use_cuda_graphs=True,
+                      cache=CacheConfig(block_size=page, num_gpu_blocks=pages),
+                      sched=SchedulerConfig(max_num_seqs=n_req, max_num_batched_tokens=w["token_budget"],
+                                            cudagraph_batch_sizes=[1, 2, 4, 8, 16, 32]))
+    eng = Engine(mc, random_tensors(mc, 0, store_dtype="bfloat16", device="cuda:0"), ec)
+    torch.cuda.empty_cache()
+    nums = model_numbers(cfg, layers)
+    params = SamplingParams(max_new_tokens=w["new_tokens"], temperature=0.8, ignore_eos=True)
+    log = []
+    inner = eng.stepper.step
+
+    def logged(entries, *a, **k):                                  # what each step ran, for the roofline sum
+        log.append([(e.start, len(e.tokens)) for e in entries])
+        return inner(entries, *a, **k)
+
+    eng.stepper.step = logged
+    eng.generate(prompts, params)                                   # untimed: graphs captured, kernels loaded
+    log.clear()
+    l0 = eng.ops.launches
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = eng.generate(prompts, params)
+    torch.cuda.synchronize()
+    sec = time.perf_counter() - t0
+    assert all(len(o) == w["new_tokens"] for o in out)
+    ideal, mixed_steps = 0.0, 0
+    Hq, D = cfg["num_heads"], nums["head_dim"]
+    for step in log:
+        T = sum(n for _, n in step)
+        keys = sum(s + n for s, n in step)
+        flops = 2 * T * nums["matmul_params"] + 2 * len(step) * nums["lm_head_params"] \
+            + layers * 4 * Hq * D * sum(n * s + n * (n + 1) // 2 for s, n in step)
+        bytes_ = nums["weights_bytes"] + keys * nums["kv_bytes_per_token"]
+        ideal += max(bytes_ / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12))
+        mixed_steps += any(n == 1 for _, n in step) and any(n > 1 for _, n in step)
+    gen = n_req * w["new_tokens"]
+    res = {"value": gen / sec, "unit": "generated tokens/s", "seconds": sec, "prompt_tokens": sum(lens), "generated_tokens": gen,
+           "all_tokens_per_s": (sum(lens) + gen) / sec, "steps": len(log), "mixed_steps": int(mixed_steps),
+           "roofline_frac": ideal / sec, "layers": layers, "layers_in_config": full_layers,
+           "requests": n_req, "token_budget": w["token_budget"], "page_size": page, "gpu_launches": eng.ops.launches - l0,
+           "preemptions": eng.stats()["preemptions"]}
+    del eng
+    torch.cuda.empty_cache()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -180,6 +258,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the Falcon-width and Gemma-size serving workloads")
+    ap.add_argument("--only-workload", default=None, choices=sorted(WORKLOADS), help="run one serving workload and print its record")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -194,7 +274,9 @@ def main():
         args.warmup = 3
 
     import torch
-    base = load_json("BASELINE.json")
+    if args.only_workload:
+        print(json.dumps({args.only_workload: run_workload(args.only_workload, peaks(), args.layers)}))
+        return 0
     cfg = dict(architecture="mqa_gpt", vocab_size=32000, d_model=4096, num_layers=32, num_heads=32, num_kv_heads=1,
                hidden_size=11008, max_seq_len=4096, rope_theta=10000.0, rms_norm_eps=1e-5, bias=False, dtype="bfloat16")
     full_layers = cfg["num_layers"]
@@ -258,14 +340,7 @@ def main():
     def e2e_step(_):
         got[0] += len(eng.step())
 
-    if os.environ.get("TTIE_BENCH_PROFILE"):
-        import cProfile, pstats
-        pr = cProfile.Profile(); pr.enable()
     e_ms = timed(e2e_step, n_e2e)
-    if os.environ.get("TTIE_BENCH_PROFILE"):
-        pr.disable()
-        pstats.Stats(pr, stream=sys.stderr).sort_stats("tottime").print_stats(12)
-        print(eng.stats(), file=sys.stderr)
     assert got[0] == batch * n_e2e, (got[0], batch, n_e2e)
     for r in list(eng.scheduler.running):
         eng.manager.release(r.rid)
@@ -276,9 +351,9 @@ def main():
 
     # ---- other batch sizes
     points = {}
+    eng = None
+    torch.cuda.empty_cache()
     if not args.no_points:
-        del eng
-        torch.cuda.empty_cache()
         for b in (1, 64):
             e2 = build_engine(cfg, layers, b, ctx, [b])
             k2 = min(K, 32)
@@ -286,6 +361,11 @@ def main():
             points[f"decode_b{b}"] = b * k2 / (m2 / 1e3)
             del e2
             torch.cuda.empty_cache()
+
+    workloads = {}
+    if not args.no_workloads:
+        for name in WORKLOADS:
+            workloads[name] = run_workload(name, pk)
 
     out = {
         "metric": "decode tokens/s (batch 8, context 4096)", "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K,
@@ -296,7 +376,7 @@ def main():
                    "kv_heads": cfg["num_kv_heads"], "head_dim": nums["head_dim"], "ffn_hidden": cfg["hidden_size"],
                    "vocab": vocab, "page_size": 64, "prompt_len": start_len, "l2": "inputs larger than L2 (weights 11 GB per step)",
                    "cuda_graph": True, "sampling": "temperature 0.8 on device"},
-        "e2e": e2e, "gpu_launches": launches, "e2e_prompt_len": e2e_prompt, "prefill": prefill, "roofline": roofline, "points": points, "clocks": clock_rec,
+        "e2e": e2e, "gpu_launches": launches, "e2e_prompt_len": e2e_prompt, "prefill": prefill, "roofline": roofline, "points": points, "workloads": workloads, "clocks": clock_rec,
         "impl": "ours",
     }
     print(json.dumps(out))

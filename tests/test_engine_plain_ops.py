@@ -97,3 +97,33 @@ def test_steady_decode_steps_repack_to_the_same_buffer():
     far = [StepEntry(nxt[0].rid, nxt[0].start + 9, [5], [0])] + nxt[1:]
     with pytest.raises(ValueError):
         packer.pack(far, pad_seqs=4, pages_per_seq=pages, buffers=fast, copy_only=True)
+
+
+def test_mixed_step_is_packed_in_two_classes():
+    """One-token requests are packed first, the others after them in the order given; wanted rows keep the
+    order of the entries; the second class counts its tokens from its own first one."""
+    from tiny_transformer_inference_engine_b200.engine.batch import StepEntry
+    eng, _ = make(TINY_A, SEEDS["A"], 4, 40)
+    mgr, packer = eng.manager, eng.stepper.packer
+    spans = {"p": (0, [1, 2, 3, 4, 5]), "a": (9, [6]), "q": (2, [7, 8, 9]), "b": (4, [10])}
+    for rid, (start, toks) in spans.items():
+        mgr.admit(rid)
+        mgr.extend(rid, 0, start + len(toks))
+    entries = [StepEntry("p", 0, spans["p"][1], [4, 0]), StepEntry("a", 9, [6], [0]),
+               StepEntry("q", 2, spans["q"][1], []), StepEntry("b", 4, [10], [0])]
+    ctx = packer.pack(entries)
+    assert ctx.token_ids.tolist() == [6, 10, 1, 2, 3, 4, 5, 7, 8, 9]
+    assert ctx.positions.tolist() == [9, 4, 0, 1, 2, 3, 4, 2, 3, 4]
+    assert ctx.token_seq.tolist() == [0, 1, 2, 2, 2, 2, 2, 3, 3, 3]
+    assert ctx.query_start_loc.tolist() == [0, 1, 2, 7, 10]
+    assert ctx.seq_lens.tolist() == [10, 5, 5, 5]
+    assert ctx.slot_ids.tolist() == [mgr.slot_of[r] for r in ("a", "b", "p", "q")]
+    assert ctx.logit_rows.tolist() == [6, 2, 0, 1]                     # p's place 4, p's place 0, a, b
+    assert ctx.block_tables[0].tolist()[0][:3] == mgr.table(0, "a")
+    single, rest = ctx.classes()
+    assert (single.seq_lo, single.seq_hi, single.tok_lo, single.tok_hi, single.max_q_len, single.max_kv_len) == (0, 2, 0, 2, 1, 10)
+    assert (rest.seq_lo, rest.seq_hi, rest.tok_lo, rest.tok_hi, rest.max_q_len, rest.max_kv_len) == (2, 4, 2, 10, 5, 5)
+    assert single.query_start_loc.tolist() == [0, 1, 2] and rest.query_start_loc.tolist() == [0, 5, 8]
+    # a step of one kind is one class: the step itself
+    only = packer.pack(entries[1::2])
+    assert only.seq_classes is None and len(only.classes()) == 1 and only.classes()[0].tok_hi == 2

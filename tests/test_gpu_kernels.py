@@ -156,9 +156,11 @@ def test_rope_store(ops, dtype, Hq, Hkv, D, page, style, base):
 
 
 # ------------------------------------------------------------------------------------------ attention
-def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed=0, spike=None):
+def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed=0, spike=None, split_at=None, plans_seen=None):
     """seqs: list of (kv_len, q_len).  spike=(seq, query index, key position): that query and that
-    key are made parallel and large so the key decides the row's output."""
+    key are made parallel and large so the key decides the row's output.  split_at: the first
+    ``split_at`` requests and the others run as two launches over views of the same step, as the
+    attention part runs the two classes of a mixed step."""
     g = torch.Generator().manual_seed(seed)
     dt = DT[dtype]
     N = len(seqs)
@@ -193,8 +195,18 @@ def attention_case(ops, dtype, Hq, Hkv, D, page, seqs, window=0, plan=None, seed
     scale = 1.0 / math.sqrt(D)
     out = torch.full((T, Hq * D), 5.0, dtype=dt, device=DEV)
     max_q, max_kv = max(n for _, n in seqs), max(L for L, _ in seqs)
-    ops.paged_attention(qkv.to(DEV), Hq, Hkv, D, kp.to(DEV), vp.to(DEV), table.to(DEV), page, qsl_t.to(DEV),
-                        seq_lens.to(DEV), N, max_q, max_kv, scale, window, out, plan=plan)
+    if split_at is None:
+        ops.paged_attention(qkv.to(DEV), Hq, Hkv, D, kp.to(DEV), vp.to(DEV), table.to(DEV), page, qsl_t.to(DEV),
+                            seq_lens.to(DEV), N, max_q, max_kv, scale, window, out, plan=plan)
+    else:
+        q_d, kp_d, vp_d, table_d, lens_d = qkv.to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV), seq_lens.to(DEV)
+        for lo, hi in ((0, split_at), (split_at, N)):
+            t0, t1 = qsl[lo], qsl[hi]
+            mq, mk = max(n for _, n in seqs[lo:hi]), max(L for L, _ in seqs[lo:hi])
+            if plans_seen is not None:
+                plans_seen.append(ops.attention_plan(dt, hi - lo, Hq, Hkv, D, mq, mk, page))
+            ops.paged_attention(q_d[t0:t1], Hq, Hkv, D, kp_d, vp_d, table_d[lo:hi], page, (qsl_t[lo:hi + 1] - t0).to(DEV),
+                                lens_d[lo:hi], hi - lo, mq, mk, scale, window, out[t0:t1], plan=plan)
     exp = torch.empty(T, Hq * D)
     G = Hq // Hkv
     for i, (L, n) in enumerate(seqs):
@@ -228,6 +240,21 @@ def test_paged_attention(ops, dtype, scenario, Hq, Hkv, D, page):
     out, exp, _, _ = attention_case(ops, dtype, Hq, Hkv, D, page, SCENARIOS[scenario])
     assert torch.isfinite(out).all()
     assert rel(out, exp) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("Hq,Hkv,D,page", [(32, 1, 128, 64), (71, 1, 64, 16), (8, 1, 256, 16), (6, 2, 48, 8)])
+def test_mixed_step_in_two_classes(ops, dtype, Hq, Hkv, D, page):
+    """Decoded tokens with long contexts beside prompt portions, as two launches over one step's buffers:
+    each class is planned as if it were alone, and every row equals the float32 reference."""
+    seqs = [(4096, 1), (3000, 1), (65, 1), (512, 512), (2600, 512), (130, 2)]
+    plans = []
+    out, exp, _, _ = attention_case(ops, dtype, Hq, Hkv, D, page, seqs, split_at=3, plans_seen=plans)
+    assert torch.isfinite(out).all()
+    assert rel(out, exp) < TOL[dtype]
+    if dtype == "bfloat16" and D in (64, 128):
+        assert plans[0][0] in ("tc", "mma", "mma_c4") and plans[0][1] > 1       # one-token requests: their key range is cut
+        assert plans[1][0] in ("tc", "tcpp")
 
 
 @pytest.mark.parametrize("dtype,kernel,unit", [("float32", "simt", 32), ("bfloat16", "simt", 32), ("bfloat16", "mma", 64)])

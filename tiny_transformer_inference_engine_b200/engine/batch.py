@@ -14,7 +14,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..parts.base import StepContext
+from ..parts.base import SeqClass, StepContext
 
 
 @dataclass
@@ -148,21 +148,31 @@ class BatchPacker:
         mgr = self.manager
         N_real = len(entries)
         N = max(N_real, pad_seqs)
-        q_lens = [len(e.tokens) for e in entries] + [1] * (N - N_real)
-        T = sum(q_lens)
-        tok, pos, tseq, qsl, seql, slots, rows = [], [], [], [0], [], [], []
-        for i, en in enumerate(entries):
+        # requests that bring one token are packed first: the two classes of a mixed step (decoded tokens, prompt
+        # portions) are then contiguous ranges of requests and of tokens, and a mixer can run each with the kernel
+        # that suits it.  Wanted rows keep the order of the entries as given.
+        order = sorted(range(N_real), key=lambda i: len(entries[i].tokens) != 1)
+        num_single = sum(1 for en in entries if len(en.tokens) == 1)
+        tok, pos, tseq, qsl, seql, slots = [], [], [], [0], [], []
+        base_of = [0] * N_real
+        for i, src in enumerate(order):
+            en = entries[src]
             n = len(en.tokens)
-            base = qsl[-1]
+            base_of[src] = qsl[-1]
             tok.extend(int(t) for t in en.tokens)
             pos.extend(range(en.start, en.start + n))
             tseq.extend([i] * n)
-            qsl.append(base + n)
+            qsl.append(qsl[-1] + n)
             seql.append(en.start + n)
             slots.append(mgr.slot_of[en.rid])
-            rows.extend(base + int(w) for w in en.want)
+        rows = [base_of[i] + int(w) for i, en in enumerate(entries) for w in en.want]
         for i in range(N_real, N):
             tok.append(0); pos.append(0); tseq.append(i); rows.append(qsl[-1]); qsl.append(qsl[-1] + 1); seql.append(1); slots.append(-1)
+        q_lens = [qsl[i + 1] - qsl[i] for i in range(N)]
+        T = qsl[-1]
+        # a mixed step: the second class's query_start_loc counted from its own first token
+        mixed = 0 < num_single < N_real
+        qsl_tail = [q - num_single for q in qsl[num_single:]] if mixed else []
         R = len(rows)
         tables, widths = [], []
         for gi, g in enumerate(mgr.groups):
@@ -171,10 +181,10 @@ class BatchPacker:
                 if width > pages_per_seq[gi]:
                     raise ValueError("block table wider than the fixed layout")
                 width = pages_per_seq[gi]
-            tables.append([g.tables[en.rid] for en in entries])
+            tables.append([g.tables[entries[src].rid] for src in order])
             widths.append(width)
 
-        sizes = [T, T, T, N + 1, N, N, max(R, 1)] + [N * w for w in widths]
+        sizes = [T, T, T, N + 1, N, N, max(R, 1), len(qsl_tail)] + [N * w for w in widths]
         offs, total = [], 0
         for s in sizes:
             offs.append(total)
@@ -189,9 +199,9 @@ class BatchPacker:
         if self._copied is not None:
             self._copied.synchronize()
         hn = host.numpy()
-        for off, data in zip(offs[:7], (tok, pos, tseq, qsl, seql, slots, rows)):
+        for off, data in zip(offs[:8], (tok, pos, tseq, qsl, seql, slots, rows, qsl_tail)):
             hn[off:off + len(data)] = data
-        for off, rows_, w in zip(offs[7:], tables, widths):
+        for off, rows_, w in zip(offs[8:], tables, widths):
             block = hn[off:off + N * w].reshape(N, w)
             block[:] = 0
             for i, t in enumerate(rows_):
@@ -203,7 +213,7 @@ class BatchPacker:
             self._copied.record()
         if key is not None:
             self._last = {"key": key, "hn": hn, "host": host, "dev": dev, "total": total, "o_tok": offs[0], "o_pos": offs[1],
-                          "o_seql": offs[4], "o_tab": offs[7:], "widths": widths,
+                          "o_seql": offs[4], "o_tab": offs[8:], "widths": widths,
                           "tlen": [[len(t) for t in rows_] for rows_ in tables]}
         if copy_only:
             return None
@@ -217,8 +227,14 @@ class BatchPacker:
             token_ids=view(0, T), positions=view(1, T), token_seq=view(2, T),
             query_start_loc=view(3, N + 1), seq_lens=view(4, N), slot_ids=view(5, N),
             logit_rows=view(6, R), num_logit_rows=R,
-            block_tables={gi: dev[offs[7 + gi]:offs[7 + gi] + N * w].view(N, w) for gi, w in enumerate(widths)},
+            block_tables={gi: dev[offs[8 + gi]:offs[8 + gi] + N * w].view(N, w) for gi, w in enumerate(widths)},
             host={"q_lens": q_lens, "seq_lens": seql, "query_start_loc": qsl, "positions": pos,
                   "num_real_seqs": N_real},
         )
+        if mixed:
+            ns = num_single
+            ctx.seq_classes = [
+                SeqClass(0, ns, 0, ns, 1, max(seql[:ns]), view(3, ns + 1)),
+                SeqClass(ns, N, ns, T, max(q_lens[ns:]), max(seql[ns:]), view(7, N - ns + 1)),
+            ]
         return ctx

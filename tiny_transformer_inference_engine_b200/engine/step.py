@@ -92,7 +92,7 @@ class Stepper:
             dev = torch.zeros(words, dtype=torch.int32, device=self.device)
             ctx = self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(host, dev))
             # the captured kernels must cover every context length of the bucket: size them for the longest
-            ctx.max_kv_len = keys
+            ctx.max_kv_len = keys                                # (a decode step is one class: nothing else carries a length)
             views = self.manager.views(ctx.block_tables)
             self.model.forward(ctx, views)                       # warm-up outside the capture
             torch.cuda.synchronize(self.device)

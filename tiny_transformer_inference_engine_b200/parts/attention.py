@@ -101,7 +101,10 @@ class PagedAttention(Mixer):
                        cache.k_pages, cache.v_pages, cache.block_table, cache.page_size, write,
                        q_out=q if qkv.dim() == 3 else None, cs_table=cs_table)
         out = torch.empty((T, Hq * D), dtype=x.dtype, device=x.device)
-        ops.paged_attention(q, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
-                            ctx.query_start_loc, ctx.seq_lens, ctx.num_seqs, ctx.max_q_len, ctx.max_kv_len,
-                            self.scale, self.window or 0, out)
+        # one launch per class of requests (decoded tokens; prompt portions), each planned as if it were alone
+        for c in ctx.classes():
+            ops.paged_attention(q[c.tok_lo:c.tok_hi], Hq, Hkv, D, cache.k_pages, cache.v_pages,
+                                cache.block_table[c.seq_lo:c.seq_hi], cache.page_size, c.query_start_loc,
+                                ctx.seq_lens[c.seq_lo:c.seq_hi], c.seq_hi - c.seq_lo, c.max_q_len, c.max_kv_len,
+                                self.scale, self.window or 0, out[c.tok_lo:c.tok_hi])
         return ops.linear(out, self.w_out, self.b_out, partial_ok=True)

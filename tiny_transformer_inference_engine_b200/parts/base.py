@@ -107,6 +107,24 @@ class FixedStateView:
 
 # --------------------------------------------------------------------------- step metadata
 @dataclass
+class SeqClass:
+    """A contiguous range of a step's requests (and of their tokens) that bring alike numbers of tokens.
+
+    A step that mixes decoded tokens with prompt portions is packed with the one-token requests first, and
+    carries two classes; a mixer may run each class with the kernel that suits it (a decode step's form for
+    the first, a prompt portion's for the second) instead of sizing one launch for the longest portion.
+    ``query_start_loc`` counts from the class's first token, so the class reads like a step of its own:
+    tokens ``tok_lo:tok_hi``, requests ``seq_lo:seq_hi`` of the step's per-request arrays."""
+    seq_lo: int
+    seq_hi: int
+    tok_lo: int
+    tok_hi: int
+    max_q_len: int
+    max_kv_len: int
+    query_start_loc: torch.Tensor      # int32 [seq_hi - seq_lo + 1]
+
+
+@dataclass
 class StepContext:
     """What one step brings: the packed tokens and where each sits.
 
@@ -133,6 +151,13 @@ class StepContext:
     block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)   # cache group -> [N, max_pages]
     host: Dict[str, Any] = field(default_factory=dict)                    # the same numbers as Python lists
     step_cache: Dict[Any, Any] = field(default_factory=dict)              # device values parts compute once per step
+    seq_classes: Optional[List[SeqClass]] = None                          # None: one class, the whole step
+
+    def classes(self) -> List[SeqClass]:
+        """The step's request classes; a step without a division is one class."""
+        if self.seq_classes:
+            return self.seq_classes
+        return [SeqClass(0, self.num_seqs, 0, self.num_tokens, self.max_q_len, self.max_kv_len, self.query_start_loc)]
 
 
 class ResidualStream:
