@@ -559,30 +559,49 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n):
     assert ops.tc_error() == 0
 
 
-def test_tcgen05_issue_probe(ops):
-    """The issue probe (the measurement the tensor-core kernels' thread layout rests on) runs, every wait in it ends,
-    and a wait after a batch of products costs the issuing thread more than the products themselves."""
-    out = torch.zeros(2, dtype=torch.int64, device=DEV)
-    stream = torch.cuda.current_stream().cuda_stream
-    took = {}
-    for n, tm, after in ((64, 0, 0), (64, 0, 3), (64, 0, 6), (128, 0, 0), (256, 0, 0), (64, 1, 0), (128, 1, 0)):
-        ops._check(ops.lib.ttie_probe_mma_issue(n, tm, after, 32, out.data_ptr(), stream), "issue probe")
-        torch.cuda.synchronize()
-        issued, finished = out.tolist()
-        assert 0 < issued <= finished, (n, tm, after, issued, finished)
-        took[n, tm, after] = finished / 32
-    assert took[256, 0, 0] > 900                                  # 8 products of 128 clocks cannot take less
-    assert took[64, 0, 3] > took[64, 0, 0] + 100                  # the wait does not return before the products have finished
-    from tiny_transformer_inference_engine_b200.ops import KernelError
-    with pytest.raises(KernelError, match="64-wide"):
-        ops._check(ops.lib.ttie_probe_mma_issue(128, 0, 3, 32, out.data_ptr(), stream), "issue probe")
-
-
 # ------------------------------------------------------------------------------------------ tcgen05 attention
 TC_SHAPES = [(32, 1, 128, 64), (32, 1, 128, 16), (8, 2, 64, 8), (3, 1, 64, 128), (71, 1, 64, 64), (4, 2, 128, 32), (5, 5, 64, 256)]
 
 
 TC_KERNELS = ["tc", "tcpp"]                                       # one 128-row query tile per CTA; two tiles taken in turns
+TC_WIDE_SHAPES = [(8, 1, 256, 16), (8, 1, 256, 64), (3, 3, 256, 128)]   # head size 256: the second kernel with one tile per CTA
+
+
+@pytest.mark.parametrize("scenario", ["prefill", "chunked", "mixed", "decode"])
+@pytest.mark.parametrize("Hq,Hkv,D,page", TC_WIDE_SHAPES)
+def test_tcgen05_attention_head_size_256(ops, scenario, Hq, Hkv, D, page):
+    seqs = SCENARIOS[scenario] + [(700, 700)]
+    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=("tcpp", 1, 0))
+    assert ops.tc_error() == 0
+    assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
+    # and it is what the planner picks at this head size, whatever the step
+    assert ops.attention_plan(torch.bfloat16, len(seqs), Hq, Hkv, D, max(n for _, n in seqs), 700, page)[0] == "tcpp"
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page", TC_WIDE_SHAPES[:2])
+def test_tcgen05_attention_head_size_256_windows_splits_and_one_key(ops, Hq, Hkv, D, page):
+    for window in (1, 5, 100, 129, 300):
+        out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, [(450, 450), (90, 1), (300, 40)], window=window, plan=("tcpp", 1, 0))
+        assert rel(out, exp) < TOL["bfloat16"], window
+    for split_len in (128, 512):
+        n = -(-1500 // split_len)
+        for window in (0, 200):
+            out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, [(1500, 200), (300, 300), (900, 1), (64, 64)],
+                                            plan=("tcpp", n, split_len), window=window)
+            assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"], (split_len, window)
+    seqs = [(50, 1), (600, 1), (64, 3), (600, 600)]
+    for kpos in (0, 63, 64, 127, 128, 447, 599):
+        for sq, qi in ((1, 0), (3, 599)):
+            out, exp, dense, qsl = attention_case(ops, "bfloat16", Hq, Hkv, D, page, seqs, plan=("tcpp", 1, 0), spike=(sq, qi, kpos))
+            row = out[qsl[sq] + qi].view(Hq, D)
+            assert (row - dense[sq][1][kpos, 0]).abs().max() < 2e-2, (kpos, sq)
+            assert rel(out, exp) < TOL["bfloat16"]
+    # the planner's own choice for decoded tokens with long contexts: the key range cut over CTAs
+    plan = ops.attention_plan(torch.bfloat16, 4, Hq, Hkv, D, 1, 3000, page)
+    assert plan[0] == "tcpp" and plan[1] > 1
+    out, exp, _, _ = attention_case(ops, "bfloat16", Hq, Hkv, D, page, [(3000, 1), (2000, 1), (1, 1), (129, 1)])
+    assert rel(out, exp) < TOL["bfloat16"]
+    assert ops.tc_error() == 0
 
 
 @pytest.mark.parametrize("kernel", TC_KERNELS)
@@ -644,3 +663,5 @@ def test_tcgen05_attention_refuses(ops):
         attention_case(ops, "bfloat16", 4, 1, 32, 16, [(40, 40)], plan=("tc", 1, 0))
     with pytest.raises(KernelError, match="not supported"):
         attention_case(ops, "bfloat16", 4, 1, 64, 24, [(40, 40)], plan=("tc", 1, 0))
+    with pytest.raises(KernelError, match="prompt-portion form only"):
+        attention_case(ops, "bfloat16", 4, 1, 256, 16, [(40, 40)], plan=("tc", 1, 0))

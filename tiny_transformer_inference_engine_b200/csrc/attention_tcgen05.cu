@@ -1,7 +1,8 @@
-// Causal paged attention on tcgen05 tensor cores (bfloat16, head size 64 or 128).  Two kernels:
+// Causal paged attention on tcgen05 tensor cores (bfloat16, head size 64, 128 or 256).  Two kernels:
 //   attn_tc_kernel     one 128-row query tile per CTA: decode steps with the key range cut over CTAs (partial
 //                      results for the merge kernel), and any step with few query rows per request
-//   attn_tc_pp_kernel  two 128-row query tiles per CTA: prompt portions (described where it stands, below)
+//   attn_tc_pp_kernel  two 128-row query tiles per CTA (one at head size 256, where tensor memory holds one output
+//                      tile): prompt portions, and every step at head size 256 (described where it stands, below)
 // Query rows are (token, head of a kv head's group) pairs, so with multi-query attention 4 tokens x 32 heads
 // share every key/value tile of a 128-row tile.
 //
@@ -584,7 +585,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 // that counts thread arrivals exists twice (by step parity).
 namespace pp {
 constexpr int BNK = 64;                                          // keys per step
-constexpr int NS = 8;                                            // stages of the key/value ring
+constexpr int NS = 8;                                            // stages of the key/value ring (head size 256: 4 of them, of twice the size)
 enum { PP_FULL = 0, PP_EMPTY = NS, PP_SF = 2 * NS, PP_PF = PP_SF + 4, PP_SC = PP_PF + 4, PP_OC = PP_SC + 4, PP_OF = PP_OC + 4,
        PP_LF = PP_OF + 4, PP_NBARS = PP_LF + 2 };                // SF, PF, SC, OC, OF: [tile][step parity]
 constexpr int PP_NTHREADS = 512;
@@ -611,10 +612,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
 }
 
-template <int D>
+// NT: query tiles per CTA.  Tensor memory holds 2 x 2 x 64 score columns and NT x D output columns: two tiles up to
+// head size 128, one tile (its scores at columns 0..127, its output at 256..511) at head size 256.
+template <int D, int NT>
 __global__ void __launch_bounds__(pp::PP_NTHREADS, 1)
 attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
     using namespace pp;
+    static_assert(256 + NT * D <= 512, "tensor memory: scores of two tiles, then the output tiles");
+    constexpr int NSD = D > 128 ? 4 : NS;                        // ring stages in use (a stage is D x 64 x 2 bytes)
     constexpr int CB = D / 64;
     constexpr uint32_t QBLK = BM * 128, KVBLK = BNK * 128;       // bytes of one 64-column block of a query / key tile
     constexpr uint32_t QT_BYTES = CB * QBLK, KV_BYTES = CB * KVBLK;
@@ -622,8 +627,8 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     constexpr uint32_t S_COL = 0, O_COL = 256;                   // scores of (tile t, buffer b) at t * 128 + b * 64; output of tile t at 256 + t * D
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-    unsigned char* Qs = smem;                                    // [2 tiles]
-    unsigned char* ring = Qs + 2 * QT_BYTES;                     // [NS stages]
+    unsigned char* Qs = smem;                                    // [NT tiles]
+    unsigned char* ring = Qs + NT * QT_BYTES;                    // [NSD stages]
     __shared__ __align__(8) unsigned long long bars[PP_NBARS];
     __shared__ uint32_t tmem_slot;
     __shared__ float alpha_s[2][2][BM];                          // [step parity][tile]: factor for a row of O before the step's product is added
@@ -636,10 +641,10 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     tile /= p.row_tiles;
     const int kvh = tile % p.Hkv, seq = tile / p.Hkv;
     const int q0 = p.qsl[seq], q_len = p.qsl[seq + 1] - q0, kv_len = p.seq_lens[seq];
-    const int nrows = q_len * G, row0 = rt * (2 * BM);
+    const int nrows = q_len * G, row0 = rt * (NT * BM);
     if (row0 >= nrows) return;                                   // uniform over the CTA, before anything is allocated
     const int ctx = kv_len - q_len;
-    const int rows_here = min(2 * BM, nrows - row0);
+    const int rows_here = min(NT * BM, nrows - row0);
     const int tok_lo = row0 / G, tok_hi = (row0 + rows_here - 1) / G;
     int key_hi = ctx + tok_hi + 1;                               // exclusive
     int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
@@ -879,9 +884,9 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             };
             int it = 0;                                         // tiles copied so far
             auto emit = [&](const CUtensorMap* map, int y_lane, int code) -> bool {
-                const int st = it % NS;
+                const int st = it % NSD;
                 int ok = 1;
-                if (lane == 0) ok = mbar_wait_relaxed(BAR(PP_EMPTY + st), ((it / NS) & 1) ^ 1, code);
+                if (lane == 0) ok = mbar_wait_relaxed(BAR(PP_EMPTY + st), ((it / NSD) & 1) ^ 1, code);
                 if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
                 if (lane == 0) mbar_expect_tx(BAR(PP_FULL + st), KV_BYTES);
                 for (int x = 0; x < nboxes; ++x) {
@@ -921,19 +926,19 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             auto k_index = [&](int j) { return j < 2 ? j : 2 * j - 1; };
             auto v_index = [&](int j) { return j == nsteps - 1 ? 2 * nsteps - 1 : 2 * j + 2; };
             if (warp == 15) {
-                uint32_t q_lo[2][CB];                           // lower descriptor words of the query blocks
+                uint32_t q_lo[NT][CB];                          // lower descriptor words of the query blocks
 #pragma unroll
-                for (int t = 0; t < 2; ++t)
+                for (int t = 0; t < NT; ++t)
 #pragma unroll
                     for (int cb = 0; cb < CB; ++cb) q_lo[t][cb] = desc_lo(smem_u32(Qs + t * QT_BYTES + cb * QBLK), 16);
                 const uint32_t ring_k_lo = desc_lo(smem_u32(ring), 16);
                 for (int j = 0; j < nsteps; ++j) {
-                    const int b = j & 1, idx = k_index(j), st = idx % NS;
-                    if (!mbar_wait(BAR(PP_FULL + st), (idx / NS) & 1, 3)) break;
+                    const int b = j & 1, idx = k_index(j), st = idx % NSD;
+                    if (!mbar_wait(BAR(PP_FULL + st), (idx / NSD) & 1, 3)) break;
                     const uint32_t k_lo = ring_k_lo + (uint32_t)st * (KV_BYTES >> 4);
                     bool ok = true;
 #pragma unroll
-                    for (int t = 0; t < 2; ++t) {
+                    for (int t = 0; t < NT; ++t) {
                         if (t < ntq) {
                             // the buffer holds P(j-2) until its product with V has finished
                             if (j >= 2 && !mbar_wait(BAR(PP_OF + 2 * t + b), ((j - 2) >> 1) & 1, 4)) { ok = false; break; }
@@ -957,9 +962,9 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 const uint32_t ring_v_lo = desc_lo(smem_u32(ring), KVBLK);
                 const uint32_t s_tmem = tmem_base + S_COL + (uint32_t)t * 128, o_tmem = tmem_base + O_COL + (uint32_t)t * D;
                 for (int j = 0; j < nsteps; ++j) {
-                    const int b = j & 1, idx = v_index(j), st = idx % NS;
+                    const int b = j & 1, idx = v_index(j), st = idx % NSD;
                     const uint32_t par = (j >> 1) & 1;
-                    if (!mbar_wait(BAR(PP_FULL + st), (idx / NS) & 1, 5)) break;
+                    if (!mbar_wait(BAR(PP_FULL + st), (idx / NSD) & 1, 5)) break;
                     if (!mbar_wait(BAR(PP_PF + 2 * t + b), par, 7)) break;
                     if (!mbar_wait(BAR(PP_OC + 2 * t + b), par, 6)) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1023,8 +1028,9 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, 
 }
 template <int D>
 int launch_pp(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, cudaStream_t s) {
-    const size_t smem = 2 * (size_t)(D / 64) * BM * 128 + pp::NS * (size_t)(D / 64) * pp::BNK * 128 + 1024;
-    auto k = attn_tc_pp_kernel<D>;
+    constexpr int NT = D > 128 ? 1 : 2, NSD = D > 128 ? 4 : pp::NS;
+    const size_t smem = NT * (size_t)(D / 64) * BM * 128 + NSD * (size_t)(D / 64) * pp::BNK * 128 + 1024;
+    auto k = attn_tc_pp_kernel<D, NT>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     k<<<dim3(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits), pp::PP_NTHREADS, smem, s>>>(mk, mv, p);
@@ -1047,13 +1053,14 @@ extern "C" int ttie_attn_tc_error() {
     return v;
 }
 
-// Head size 64 or 128; page size a multiple of 8 that divides 128 or is a multiple of 128.
+// Head size 64, 128 or 256 (256: the two-tile kernel's form only, with one tile); page size a multiple of 8 that
+// divides 128 or is a multiple of 128.
 extern "C" int ttie_attn_tc_supported(int D, int page_size) {
-    return (D == 64 || D == 128) && page_size >= 8 && page_size % 8 == 0 && (128 % page_size == 0 || page_size % 128 == 0) && page_size <= 256;
+    return (D == 64 || D == 128 || D == 256) && page_size >= 8 && page_size % 8 == 0 && (128 % page_size == 0 || page_size % 128 == 0) && page_size <= 256;
 }
 
-// two_tiles: 0 = a CTA owns one 128-row query tile (any number of rows; decode steps), 1 = a CTA owns 256 rows as two
-// tiles taken in turns (prompt portions).
+// two_tiles: 0 = a CTA owns one 128-row query tile (any number of rows; decode steps; head size 64 or 128), 1 = the
+// kernel for prompt portions: a CTA owns 256 rows as two tiles taken in turns (128 rows as one tile at head size 256).
 // num_splits > 1: the key range is cut into pieces of split_len keys (a multiple of 128) over grid y; the partial
 // results go to `scratch` (ttie_attn_scratch_floats) and a merge kernel writes `out`.
 extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
@@ -1066,6 +1073,7 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("attention_tc: %d heads are not a multiple of %d kv heads", Hq, Hkv);
     if (q_stride % 8 || ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out | (uintptr_t)scratch) & 15)
         TTIE_FAIL("attention_tc: pointers must be 16-byte aligned and the query stride a multiple of 8");
+    if (D > 128 && !two_tiles) TTIE_FAIL("attention_tc: head size %d runs in the prompt-portion form only", D);
     if (num_splits < 1) num_splits = 1;
     if (num_splits > 1 && (split_len <= 0 || split_len % BN || !scratch))
         TTIE_FAIL("attention_tc: splits need scratch and a split length that is a multiple of %d", BN);
@@ -1080,13 +1088,13 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.block_table = block_table; p.table_width = table_width;
     p.page_size = page_size; p.qsl = qsl; p.seq_lens = seq_lens; p.out = (__nv_bfloat16*)out;
     p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
-    p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), two_tiles ? 2 * BM : BM);
+    p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), two_tiles && D <= 128 ? 2 * BM : BM);
     p.num_splits = num_splits; p.split_len = split_len;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("attention_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
     const bool ahead = max_q_len * (Hq / Hkv) >= BM;             // full row tiles: a prompt portion
-    const int rc = two_tiles ? (D == 64 ? launch_pp<64>(mk, mv, p, s) : launch_pp<128>(mk, mv, p, s))
+    const int rc = two_tiles ? (D == 64 ? launch_pp<64>(mk, mv, p, s) : D == 128 ? launch_pp<128>(mk, mv, p, s) : launch_pp<256>(mk, mv, p, s))
                  : D == 64 ? (ahead ? launch<64, true>(mk, mv, p, s) : launch<64, false>(mk, mv, p, s))
                            : (ahead ? launch<128, true>(mk, mv, p, s) : launch<128, false>(mk, mv, p, s));
     if (rc) return rc;

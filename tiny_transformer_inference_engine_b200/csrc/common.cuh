@@ -58,6 +58,9 @@ int attn_merge_bf16(const float* ws_o, const float* ws_ml, void* out, int rows, 
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// multiprocessors of the current device (asked once per device)
+int num_sms();
+
 // Programmatic dependent launch: a kernel launched this way may be scheduled while its predecessor in
 // the stream drains; it must call pdl_wait() before it touches anything the predecessor wrote (the
 // kernels here call it first thing, so only launch latency and CTA scheduling overlap).  Works inside

@@ -28,6 +28,21 @@ bool pdl_enabled() {
 }
 }  // namespace ttie
 extern "C" void ttie_set_pdl(int on) { ttie::g_pdl = on ? 1 : 0; }
+
+namespace ttie {
+int num_sms() {
+    static int count[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!count[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        count[dev] = n;
+    }
+    return count[dev];
+}
+}  // namespace ttie
+extern "C" int ttie_num_sms() { return ttie::num_sms(); }
 extern "C" const char* ttie_last_error() { return ttie::g_error; }
 extern "C" int ttie_abi_version() { return 4; }
 
@@ -318,12 +333,12 @@ extern "C" int ttie_swiglu(const void* gate_up, void* out, int T, int F, int dty
     const int threads = 256;
     if (dtype == kBF16 && F % 8 == 0 && !(((uintptr_t)gate_up | (uintptr_t)out) & 15)) {
         const size_t total8 = total / 8;
-        const int blocks = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
+        const int blocks = (int)((total8 + threads - 1) / threads < num_sms() * 16 ? (total8 + threads - 1) / threads : num_sms() * 16);
         swiglu_vec8_kernel<<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, F / 8, total8);
         TTIE_CHECK_LAUNCH("swiglu");
         return 0;
     }
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const int blocks = (int)((total + threads - 1) / threads < num_sms() * 16 ? (total + threads - 1) / threads : num_sms() * 16);
     if (dtype == kF32) swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, F, total);
     else if (dtype == kBF16) swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, F, total);
     else TTIE_FAIL("swiglu: unknown dtype %d", dtype);

@@ -269,16 +269,6 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
     return 0;
 }
 
-int num_sms() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
-
 template <int BN, int STAGES, typename OutT>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const TcParams& p, cudaStream_t s) {
     const size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;

@@ -52,11 +52,8 @@ _SIGNATURES = {
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_int,
                                 _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
-    "ttie_probe_mma_issue": [_c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
 }
-
-NUM_SMS = 148
 
 
 class KernelError(RuntimeError):
@@ -86,7 +83,8 @@ class CudaOps:
             fn.argtypes, fn.restype = argtypes, _c_int
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
-        self.attn_target_ctas = 4 * NUM_SMS      # decode tiles are small: four CTAs share an SM
+        self.num_sms = int(torch.cuda.get_device_properties(self.device).multi_processor_count)   # the plans below are sized for it
+        self.attn_target_ctas = 4 * self.num_sms  # decode tiles are small: four CTAs share an SM
         self.attn_cluster_max_rows = 64         # query rows per request (tokens x heads per kv head) up to which the decode form runs
         self.attn_cluster_max_size = 8          # CTAs per cluster (16 is placed on fewer SMs at a time)
         self.attn_cluster_tiles_per_warp = 1    # ... and only while a warp walks at most this many 64-key tiles
@@ -164,7 +162,7 @@ class CudaOps:
         16-row tiles alone are too few to balance the SMs."""
         tiles = math.ceil(N / 16)
         full = math.ceil(K / 128) * 128
-        if not may_split or tiles >= 4 * NUM_SMS:
+        if not may_split or tiles >= 4 * self.num_sms:
             return full
         best, best_eff = full, 0.0
         for S in (1, 2, 3, 4, 6, 8):
@@ -172,7 +170,7 @@ class CudaOps:
             if ks < 256:
                 break
             ctas = tiles * math.ceil(K / ks)
-            eff = (ctas / NUM_SMS) / math.ceil(ctas / NUM_SMS)
+            eff = (ctas / self.num_sms) / math.ceil(ctas / self.num_sms)
             if eff > best_eff + 0.02:
                 best, best_eff = ks, eff
         return best
@@ -299,11 +297,14 @@ class CudaOps:
 
     def attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size=None):
         """Which attention kernel runs and how the key range is split: (kernel, num_splits,
-        split_len).  bfloat16 with a head size that is a multiple of 16 up to 128 runs on
-        tensor cores; everything else runs the general float32-arithmetic kernel.  The key
+        split_len).  bfloat16 with a head size that is a multiple of 16 up to 128, or 256, runs
+        on tensor cores; everything else runs the general float32-arithmetic kernel.  The key
         range is split only when the query rows alone cannot fill the GPU."""
         G = num_heads // num_kv_heads
         rows = max_q_len * G
+        if (dtype == torch.bfloat16 and page_size is not None and head_dim > 128
+                and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
+            return self._tc_wide_plan(num_seqs, num_kv_heads, rows, max_kv_len)
         if (dtype == torch.bfloat16 and page_size is not None and rows >= self.attn_tc_min_rows
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
             # prompt portions: the tcgen05 kernel with two query tiles per CTA.  Where its CTAs fill less than half of
@@ -311,9 +312,9 @@ class CudaOps:
             # without one goes to the one-tile kernel, which has twice the CTAs (measured at 512 tokens x 32 heads:
             # 16.4 against 21.6 us; the last 512 of 8,192 tokens: 105 us cut in two, 147 us uncut)
             base = num_seqs * num_kv_heads * math.ceil(rows / 256)
-            if base > NUM_SMS // 2:
+            if base > self.num_sms // 2:
                 return "tcpp", 1, 0
-            n = max(1, min(NUM_SMS // base, max_kv_len // self.attn_tcpp_min_split))
+            n = max(1, min(self.num_sms // base, max_kv_len // self.attn_tcpp_min_split))
             if n > 1:
                 split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
                 n = math.ceil(max_kv_len / split_len)
@@ -329,13 +330,27 @@ class CudaOps:
         else:
             kernel, tile_rows, unit, min_len = "simt", 32, 32, 128
         base = num_seqs * num_kv_heads * math.ceil(rows / tile_rows)
-        if base >= NUM_SMS or max_kv_len <= min_len:
+        if base >= self.num_sms or max_kv_len <= min_len:
             return kernel, 1, 0
         # as many splits as fit one wave of resident CTAs, none shorter than min_len keys
         want = max(1, min(self.attn_target_ctas // base, math.ceil(max_kv_len / min_len)))
         split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
         num_splits = math.ceil(max_kv_len / split_len)
         return (kernel, num_splits, split_len) if num_splits > 1 else (kernel, 1, 0)
+
+    def _tc_wide_plan(self, num_seqs, num_kv_heads, rows, max_kv_len):
+        """Head size 256: every step takes the prompt-portion tcgen05 kernel with one 128-row tile per CTA.  Where
+        the row tiles fill less than half of the GPU the key range is cut over CTAs as well: into pieces of at least
+        256 keys for steps of few rows (decoded tokens), of at least 1,024 keys for portions."""
+        base = num_seqs * num_kv_heads * math.ceil(rows / 128)
+        if base > self.num_sms // 2:
+            return "tcpp", 1, 0
+        shortest = self.attn_tc_min_split if rows <= 128 else self.attn_tcpp_min_split
+        n = max(1, min(self.num_sms // base, max_kv_len // shortest))
+        if n > 1:
+            split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
+            n = math.ceil(max_kv_len / split_len)
+        return ("tcpp", n, split_len) if n > 1 else ("tcpp", 1, 0)
 
     def _tc_split_plan(self, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size):
         """The tcgen05 kernel for steps with few query rows per request and contexts too long for the decode
@@ -345,9 +360,10 @@ class CudaOps:
         the requests alone fill the GPU."""
         rows = max_q_len * (num_heads // num_kv_heads)
         base = num_seqs * num_kv_heads
-        if page_size is None or rows > 128 or rows < 16 or base > NUM_SMS or not self.lib.ttie_attn_tc_supported(head_dim, page_size):
+        if (page_size is None or rows > 128 or rows < 16 or base > self.num_sms or head_dim > 128
+                or not self.lib.ttie_attn_tc_supported(head_dim, page_size)):
             return None
-        n = max(1, min(NUM_SMS // base, math.ceil(max_kv_len / self.attn_tc_min_split)))
+        n = max(1, min(self.num_sms // base, math.ceil(max_kv_len / self.attn_tc_min_split)))
         split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
         n = math.ceil(max_kv_len / split_len)
         return ("tc", n, split_len) if n > 1 else ("tc", 1, 0)
@@ -369,7 +385,7 @@ class CudaOps:
         tile_rows = self.lib.ttie_attn_cluster_tile_rows(max_q_len, num_heads, num_kv_heads)
         base = num_seqs * num_kv_heads * math.ceil(rows / tile_rows)
         groups = 4 if max_kv_len > 128 else 2
-        want = max(1, min(self.attn_cluster_max_size, (NUM_SMS + base // 2) // base, math.ceil(max_kv_len / (64 * groups))))
+        want = max(1, min(self.attn_cluster_max_size, (self.num_sms + base // 2) // base, math.ceil(max_kv_len / (64 * groups))))
         C = 1 << (want.bit_length() - 1)                       # a power of two
         while C > 1 and self._clusters_active(head_dim, max_q_len, num_heads, num_kv_heads, groups, C) < base:
             C //= 2                                            # all clusters of the step have to run at once

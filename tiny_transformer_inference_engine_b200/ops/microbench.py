@@ -1,6 +1,6 @@
 """Per-kernel timings against their rooflines, at the sizes of a model configuration.
 
-    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|prefill_attention|issue|all]
+    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|prefill_attention|all]
                                                                     [--batch 8] [--ctx 4096] [--tokens 2048]
 
 Every kernel is timed alone inside a captured CUDA graph of ``--iters`` launches (so the host's launch
@@ -240,33 +240,9 @@ def gemm_tc(ops, a):
         raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
 
 
-def issue(ops, a):
-    """What an issuing thread's instruction stream costs: clocks per tcgen05.mma by shape and operand source, and
-    what follows a batch of 8 products (a commit, a barrier wait, a fence, a flag poll) with one and with two
-    issuing threads.  "issued" is the clock count at which the thread is past its last instruction, "finished" when
-    the products are done; the second falls behind the first only by the pipeline's depth."""
-    print("== one thread's stream of tcgen05.mma [128 x N x 16], 64 batches of 8 products; clocks per batch (8 x N/2 is the tensor core's time)")
-    out = torch.zeros(2, dtype=torch.int64, device=DEV)
-    batches = 64
-    names = ["products only", "+ tcgen05.commit", "+ commit + wait for that commit", "+ commit + wait on a barrier that completed long ago",
-             "+ commit + tcgen05.fence::after_thread_sync", "+ commit + poll of a shared-memory flag that is set",
-             "+ commit + finished-barrier wait, two issuing threads (clocks per pair of batches)"]
-    stream = torch.cuda.current_stream().cuda_stream
-    def run(n, tm, after):
-        for _ in range(2):
-            ops._check(ops.lib.ttie_probe_mma_issue(n, tm, after, batches, out.data_ptr(), stream), "issue probe")
-            torch.cuda.synchronize()
-        return [v / batches for v in out.tolist()]
-
-    for n, tm in ((64, 0), (128, 0), (256, 0), (64, 1), (128, 1)):
-        for after in (range(7) if (n, tm) == (64, 0) else (0,)):
-            t = run(n, tm, after)
-            print(f"N={n:3d} A in {'tensor' if tm else 'shared'} memory, {names[after]:82s} issued {t[0]:7.1f}  finished {t[1]:7.1f}  (tensor core: {8 * n // 2})", flush=True)
-
-
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "prefill_attention", "issue", "all"))
+    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "prefill_attention", "all"))
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -289,8 +265,6 @@ def main(argv=None):
         attention(ops, a)
     if a.what in ("prefill_attention", "all"):
         prefill_attention(ops, a)
-    if a.what == "issue":
-        issue(ops, a)
     return 0
 
 
