@@ -77,7 +77,7 @@ def test_tables_slots_and_release():
 def test_groups_and_window():
     full, win = PagedKVNeed(1, 8), PagedKVNeed(1, 8, window=6)
     m = manager([full, win, full, None], page=4, pages=6)
-    assert len(m.groups) == 2 and m.groups[0].entries == [0, 2] and m.groups[1].entries == [1]
+    assert len(m.groups) == 2 and m.groups[0].entries == [(0, 0), (2, 0)] and m.groups[1].entries == [(1, 0)]
     m.admit("a")
     m.extend("a", 0, 10)
     assert m.table(0, "a") == [1, 2, 3] and m.table(1, "a") == [1, 2, 3]
@@ -96,25 +96,69 @@ def test_groups_and_window():
 
 def test_state_slots_are_zeroed():
     m = manager([PagedKVNeed(1, 8), FixedStateNeed((3,))], slots=2)
-    state = m.entry_state[1]
-    assert state.shape == (2, 3)
+    state = m.entry_state[(1, 0)]
+    assert state.shape == (3, 3)                                   # two slots and the scratch row that slot id -1 indexes
     a = m.admit("a")
     state[a] += 5
     m.release("a")
     b = m.admit("b")
     assert b == a and torch.equal(state[b], torch.zeros(3))
     views = m.views({0: torch.zeros((1, 1), dtype=torch.int32)})
-    assert views[0].k_pages.shape == (9, 1, 4, 8) and views[1].state is state
+    assert views[0][0].k_pages.shape == (9, 1, 4, 8) and views[1][0].state is state
 
 
 def test_shared_cache_views():
     need = PagedKVNeed(2, 8)
     order = [RunEntry(0), RunEntry(1, cache_from=0), RunEntry(0)]
     m = manager([need, None, need], order)
-    assert m.groups[0].entries == [0, 2]
-    v = m.views({0: torch.zeros((1, 1), dtype=torch.int32)})
+    assert m.groups[0].entries == [(0, 0), (2, 0)]
+    v = [x[0] for x in m.views({0: torch.zeros((1, 1), dtype=torch.int32)})]
     assert v[1].k_pages.data_ptr() == v[0].k_pages.data_ptr() and not v[1].writable and v[0].writable
     assert v[2].k_pages.data_ptr() != v[0].k_pages.data_ptr()
+
+
+def test_an_entry_with_several_needs_gets_as_many_views():
+    """A block whose mixer keeps pages and a state of fixed size, beside a plain one: the views come in the order
+    of the needs, the pages of both entries share a group, and a reader of the first entry sees both views."""
+    kv = PagedKVNeed(1, 8)
+    order = [RunEntry(0), RunEntry(1), RunEntry(2, cache_from=0)]
+    m = manager([[kv, FixedStateNeed((5,)), FixedStateNeed((2, 2), "bfloat16")], kv, []], order, slots=2)
+    assert m.groups[0].entries == [(0, 0), (1, 0)] and sorted(m.entry_state) == [(0, 1), (0, 2)]
+    v = m.views({0: torch.zeros((1, 1), dtype=torch.int32)})
+    assert [type(x).__name__ for x in v[0]] == ["PagedKVView", "FixedStateView", "FixedStateView"]
+    assert v[0][1].state.shape == (3, 5) and v[0][2].state.shape == (3, 2, 2) and v[0][2].state.dtype == torch.bfloat16
+    assert len(v[1]) == 1 and len(v[2]) == 3 and not any(x.writable for x in v[2])
+    assert v[2][1].state is v[0][1].state
+    a = m.admit("a")
+    v[0][1].state[a] += 1
+    m.release("a")
+    assert m.admit("b") == a and float(v[0][1].state[a].abs().sum()) == 0
+
+
+def test_each_group_has_its_own_page_size_and_page_count():
+    """An explicit page count gives every group room for the same number of tokens in pages of its own size; a byte
+    budget stops growing a windowed group where its requests can hold no more and spends the rest on the others."""
+    full, win, big = PagedKVNeed(1, 8), PagedKVNeed(1, 8, window=6), PagedKVNeed(2, 16, page_size=16)
+    m = manager([full, win, big], page=4, pages=9)                 # 8 usable pages of 4 tokens = 32 tokens
+    assert [g.page_size for g in m.groups] == [4, 4, 16] and [g.num_pages for g in m.groups] == [9, 9, 3]
+    assert m.groups[2].kv.shape == (1, 2, 3, 2, 16, 16) and m.page_size == 4
+    m.admit("a"); m.extend("a", 0, 17)
+    assert m.table(0, "a") == [1, 2, 3, 4, 5] and m.table(2, "a") == [1, 2]
+    with pytest.raises(OutOfPages):
+        m.extend("a", 17, 33)                                      # 33 tokens: 9 pages of 4, 3 of 16
+    assert m.table(0, "a") == [1, 2, 3, 4, 5] and m.table(2, "a") == [1, 2]
+    m.release("a"); m.check()
+    # a byte budget: float32, group "full": 2*1*4*1*8*4 = 256 B/page, "win" the same
+    order = [RunEntry(0), RunEntry(1)]
+    mb = CacheManager([full, win], order, 4, None, 2, "float32", "cpu", kv_budget_bytes=256 * 60, allocate=False,
+                      max_step_tokens=8)
+    # a windowed request holds at most pages_for(6 + 8 - 1, 4) + 1 = 5 pages; two slots: 10 pages (+ scratch)
+    assert mb.groups[1].num_pages == 11 and mb.groups[0].num_pages == 60 - 11
+    assert mb.request_fits_empty_pool(48 * 4) and not mb.request_fits_empty_pool(48 * 4 + 1)
+    assert mb.admission_headroom(40 * 4, 5) and not mb.admission_headroom(40 * 4, 6)    # the windowed group: 10 free - 5
+    # without a bound on the step the windowed group is sized like the other
+    mu = CacheManager([full, win], order, 4, None, 2, "float32", "cpu", kv_budget_bytes=256 * 60, allocate=False)
+    assert [g.num_pages for g in mu.groups] == [30, 30]
 
 
 @pytest.mark.parametrize("seed", range(8))

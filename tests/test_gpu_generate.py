@@ -88,7 +88,7 @@ def test_graph_replays_match_whole_prompts_bfloat16():
             del fed[r]
     graphs, _ = make_engine(cfg, 3, 64, 80, "bfloat16", max_seqs=4, budget=4096, graphs=True, weights=w, cudagraph_batch_sizes=[1, 2, 4])
     got = run_steps(graphs, steps)
-    assert graphs.stats()["step_graph_replays"] == 70
+    assert graphs.stats()["step_graph_replays"] == 70 - 4              # 70 decode steps; the four that met a new bucket ran eagerly
     assert {k[:2] for k in graphs.stepper._graphs} == {(4, 4096), (4, 2048), (2, 512), (1, 512)}
     assert {graphs.ops.attention_plan(torch.bfloat16, 4, 16, 1, 64, 1, n, 64)[0] for n in (300, 4096)} == {"mma_c4", "tc"}
     worst, where = worst_relative(got, expected)

@@ -106,7 +106,9 @@ def test_attention_part_with_position_encoding(ops, dtype, style):
 # ------------------------------------------------------------------------------------------ toy parts
 class ToyDecayMixer(Mixer):
     """A mixer with state of its own and no pages: s_t = a * s_{t-1} + W x_t per request, y_t = s_t.
-    Its state lives in the state slot of the request; a portion advances it token by token."""
+    Its state lives in the state slot of the request; a portion advances it token by token on the host,
+    a step of single tokens advances every request at once on the device (so a decode step can be
+    captured: the padding rows of a captured step carry slot -1, which indexes the scratch row)."""
 
     def __init__(self, prefix, dim, decay):
         super().__init__(prefix)
@@ -123,6 +125,11 @@ class ToyDecayMixer(Mixer):
 
     def forward(self, x, ctx, cache):
         u = self.ops.linear(x, self.w, None).float()
+        if ctx.max_q_len == 1 and self.capturable:
+            rows = torch.remainder(ctx.slot_ids.long(), cache.state.shape[0])
+            s = self.decay * cache.state[rows] + u
+            cache.state.index_copy_(0, rows, s)
+            return s.to(x.dtype)
         y = torch.empty_like(u)
         qsl, slots = ctx.host["query_start_loc"], ctx.slot_ids.tolist()
         for i in range(ctx.num_seqs):
@@ -134,6 +141,31 @@ class ToyDecayMixer(Mixer):
         return y.to(x.dtype)
 
 
+class ToyHostDecayMixer(ToyDecayMixer):
+    """The same, always on the host: a part that reads device values in its step says so, and the engine then
+    runs the model without captured graphs."""
+    capturable = False
+
+
+class ToyAttentionPlusDecay(Mixer):
+    """A mixer that keeps two things between steps - pages of keys and values, and a state of fixed size - as the
+    sum of an attention part and a decay part; it reports both needs and gets both views."""
+
+    def __init__(self, prefix, attention, decay):
+        super().__init__(prefix)
+        self.attn, self.toy = build_part("mixer", attention), build_part("mixer", decay)
+
+    def children(self):
+        return [self.attn, self.toy]
+
+    def cache_needs(self):
+        return self.attn.cache_needs() + self.toy.cache_needs()
+
+    def forward(self, x, ctx, caches):
+        pages, state = caches
+        return self.attn.forward(x, ctx, pages) + self.toy.forward(x, ctx, state)
+
+
 def toy_spec(config):
     d, D = config.d_model, config.head_dim
     norm = lambda p: PartSpec("rmsnorm", p, {"dim": d, "eps": config.rms_norm_eps})
@@ -143,13 +175,17 @@ def toy_spec(config):
     def attn(p, **kw):
         return PartSpec("attention", p, {"d_model": d, "num_heads": config.num_heads, "num_kv_heads": config.num_kv_heads,
                                          "head_dim": D, "position": rope, **kw})
-    mixers = [attn("layers.0.attn"), PartSpec("toy_decay", "layers.1.toy", {"dim": d, "decay": 0.5}),
-              attn("layers.2.attn", window=config.extra["window"]), attn("layers.3.attn", shares_kv=True)]
+    decay = config.extra.get("decay_kind", "toy_decay")
+    mixers = [attn("layers.0.attn"), PartSpec(decay, "layers.1.toy", {"dim": d, "decay": 0.5}),
+              attn("layers.2.attn", window=config.extra["window"]), attn("layers.3.attn", shares_kv=True),
+              PartSpec("toy_attention_plus_decay", "layers.4", {"attention": attn("layers.4.attn"),
+                                                                "decay": PartSpec(decay, "layers.4.toy", {"dim": d, "decay": 0.5})})]
     layers = [LayerSpec(PartSpec("pre_norm", f"layers.{i}", {"mixer_norm": norm(f"layers.{i}.n1"), "mixer": m,
                                                               "ffn_norm": norm(f"layers.{i}.n2"), "ffn": ffn(f"layers.{i}.mlp")}))
               for i, m in enumerate(mixers)]
     # layer 0 runs twice (each run with a cache of its own); layer 3 reads the cache of the first run of layer 0
-    order = (RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(0), RunEntry(3, cache_from=0))
+    # and layer 4's mixer keeps pages and a state
+    order = (RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(0), RunEntry(3, cache_from=0), RunEntry(4))
     return ModelSpec(d_model=d, vocab_size=config.vocab_size, max_seq_len=config.max_seq_len,
                      embedding=PartSpec("token", "emb", {"vocab_size": config.vocab_size, "dim": d}),
                      layers=tuple(layers), run_order=order, final_norm=norm("final_norm"),
@@ -192,27 +228,35 @@ def toy_plain_forward(cfg, w, tokens):
     x = block(x, 2, lambda h: attn(h, "layers.2.attn", window=cfg["window"]))
     x = block(x, 0, lambda h: attn(h, "layers.0.attn"))
     x = block(x, 3, lambda h: attn(h, "layers.3.attn", kv=kept["first"]))
+    x = block(x, 4, lambda h: attn(h, "layers.4.attn") + toy(h, "layers.4.toy"))
     return pm.plain_rmsnorm(x, w["final_norm.weight"], eps) @ w["lm_head.weight"].T
+
+
+TOY_CFG = dict(architecture="toy_mix", vocab_size=300, d_model=80, num_layers=5, num_heads=5, num_kv_heads=1,
+               hidden_size=112, max_seq_len=256, rope_theta=3000.0, rms_norm_eps=1e-5, window=21)
 
 
 @pytest.fixture
 def toy_registered():
     register_part("mixer", "toy_decay")(ToyDecayMixer)
+    register_part("mixer", "toy_host_decay")(ToyHostDecayMixer)
+    register_part("mixer", "toy_attention_plus_decay")(ToyAttentionPlusDecay)
     register_model("toy_mix")(toy_spec)
     yield
     unregister_model("toy_mix")
+    unregister_part("mixer", "toy_attention_plus_decay")
+    unregister_part("mixer", "toy_host_decay")
     unregister_part("mixer", "toy_decay")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "decode", "portions", "mixed"])
 def test_toy_architecture_is_built_and_stepped(toy_registered, dtype, mode):
-    cfg = dict(architecture="toy_mix", vocab_size=300, d_model=80, num_layers=4, num_heads=5, num_kv_heads=1,
-               hidden_size=112, max_seq_len=256, rope_theta=3000.0, rms_norm_eps=1e-5, window=21)
+    cfg = dict(TOY_CFG)
     mc = ModelConfig.from_dict(cfg)
     assert mc.extra == {"window": 21}
     w = random_tensors(mc, 3, perturb_norms=True)
-    assert "layers.1.toy.mix.weight" in w and "layers.3.attn.k_proj.weight" not in w
+    assert "layers.1.toy.mix.weight" in w and "layers.3.attn.k_proj.weight" not in w and "layers.4.toy.mix.weight" in w
     g = torch.Generator().manual_seed(8)
     reqs = {f"r{i}": torch.randint(0, 300, (n,), generator=g).tolist() for i, n in enumerate((70, 150, 33, 256, 90))}
     steps = {"whole": tu.whole, "decode": tu.prefill_then_decode, "portions": tu.portions, "mixed": tu.mixed}[mode](reqs)
@@ -221,12 +265,59 @@ def test_toy_architecture_is_built_and_stepped(toy_registered, dtype, mode):
                       cache=CacheConfig(block_size=page, num_gpu_blocks=tu.max_live_tokens(steps) // page + 1),
                       sched=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64))
     eng = Engine(mc, w, ec)
-    # three runs own pages: two full-attention runs share a group, the windowed run has its own
-    assert [len(g_.entries) for g_ in eng.manager.groups] == [2, 1] and list(eng.manager.entry_state) == [1]
+    # four runs own pages: three full-attention runs share a group, the windowed run has its own; two keep a state
+    assert [len(g_.entries) for g_ in eng.manager.groups] == [3, 1] and sorted(eng.manager.entry_state) == [(1, 0), (5, 1)]
     exp = {rid: toy_plain_forward(cfg, w, toks) for rid, toks in reqs.items()}
     got = tu.run_steps(eng, steps)
     bad = tu.first_wrong(got, exp, TOL[dtype])
     assert bad is None, f"first wrong place {bad}"
+
+
+def toy_greedy(cfg, w, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(toy_plain_forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("pipelined", [False, True])
+def test_toy_architecture_generates_from_captured_graphs(toy_registered, pipelined):
+    """The toy architecture - a windowed cache group, a state of fixed size, a mixer with two needs - through
+    Engine.generate with captured decode steps (and the next step launched ahead of the host): the step that
+    captures a graph must advance the per-request state once, and a windowed group must not stop the pipeline.
+    Greedy tokens equal the architecture written out plainly."""
+    cfg = dict(TOY_CFG)
+    mc = ModelConfig.from_dict(cfg)
+    w = random_tensors(mc, 3, std=0.3, perturb_norms=True)           # weights large enough for decided argmaxes
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 300, (n,), generator=g).tolist() for n in (30, 7, 55)]
+    from tiny_transformer_inference_engine_b200 import SamplingParams
+    ec = EngineConfig(dtype="float32", device=DEV, use_cuda_graphs=True, pipelined_decode=pipelined,
+                      cache=CacheConfig(block_size=8, num_gpu_blocks=64),
+                      sched=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=32, cudagraph_batch_sizes=[1, 2, 4]))
+    eng = Engine(mc, w, ec)
+    assert eng.model.capturable
+    new = [40, 26, 33]                                                # requests end at different steps: the batch bucket changes
+    out = eng.generate(prompts, [SamplingParams(max_new_tokens=n, greedy=True) for n in new])
+    assert eng.stepper.counters["graph_replays"] > 20 and len(eng.stepper._graphs) >= 2
+    for p, o, n in zip(prompts, out, new):
+        assert o == toy_greedy(cfg, w, p, n)
+    eng.manager.check()
+    assert all(g_.allocator.num_free == g_.allocator.num_usable for g_ in eng.manager.groups)
+
+
+def test_a_part_that_cannot_be_captured_keeps_the_model_off_graphs(toy_registered):
+    cfg = dict(TOY_CFG, decay_kind="toy_host_decay")
+    mc = ModelConfig.from_dict(cfg)
+    w = random_tensors(mc, 3, std=0.3, perturb_norms=True)
+    from tiny_transformer_inference_engine_b200 import SamplingParams
+    ec = EngineConfig(dtype="float32", device=DEV, use_cuda_graphs=True, cache=CacheConfig(block_size=8, num_gpu_blocks=40),
+                      sched=SchedulerConfig(max_num_seqs=2, max_num_batched_tokens=32, cudagraph_batch_sizes=[1, 2]))
+    eng = Engine(mc, w, ec)
+    assert not eng.model.capturable and eng.stepper.graph_batch_sizes == []
+    prompt = list(range(3, 20))
+    assert eng.generate([prompt], SamplingParams(max_new_tokens=12, greedy=True))[0] == toy_greedy(cfg, w, prompt, 12)
+    assert eng.stepper.counters["graph_replays"] == 0
 
 
 # ------------------------------------------------------------------------------------------ more toy parts

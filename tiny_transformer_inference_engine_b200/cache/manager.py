@@ -3,11 +3,20 @@ and slots for per-request state of fixed size.
 
 The reference keeps one pool ``kv[L, 2, pages, page, Hkv, D]`` with one allocator and a
 Python block table per ``Sequence`` (serving/kv_pool.py:12-21, serving/sequence.py:14-30).
-Here the run entries of a model that need a cache are sorted into **groups** by what
-they need (kv heads, head size, window): a group has its own pages, its own allocator
-and its own block table per request, so a windowed layer can give pages back while a
-full-attention layer keeps all of its.  A page id addresses the same slab in every
-cache layer of its group and in K and V, as in the reference.
+Here the cache needs of a model's run entries (an entry may have several: a block
+reports one per cache-using sub-part) are sorted into **groups** by what they ask for
+(kv heads, head size, window, page size): a group has its own page size, its own number
+of pages, its own allocator and its own block table per request, so a windowed layer
+can give pages back - and needs far fewer pages to begin with - while a full-attention
+layer keeps all of its.  A page id addresses the same slab in every cache layer of its
+group and in K and V, as in the reference.
+
+Sizing.  With an explicit ``num_pages`` every group gets room for the same number of
+tokens (``(num_pages - 1) * page_size``; a group with another page size gets as many
+pages of its own size as that takes).  With a byte budget the manager looks for the
+largest number of tokens T such that all groups together fit the budget, where a
+windowed group never needs more than ``max_slots`` requests x (window + longest
+step) tokens: its share stops growing there and the rest goes to the other groups.
 
 Pages go back to the allocator when the request is released (finished or preempted)
 and, for a windowed group, as soon as every position of the page lies before the
@@ -16,8 +25,9 @@ never read because the kernels start at the window's first key.  Freed pages are
 again at once (LIFO) and are not cleared: reads are bounded by the request's length.
 
 State slots: ``max_slots`` ids; a request takes one at admission and gives it back at
-release.  A run entry that asks for ``FixedStateNeed`` gets a tensor
-``[max_slots, *shape]`` whose row ``slot`` is zeroed when the slot is handed out.
+release.  A need of ``FixedStateNeed`` gets a tensor ``[max_slots + 1, *shape]`` whose
+row ``slot`` is zeroed when the slot is handed out; the last row is scratch (slot id -1,
+the padding rows of a captured decode step, indexes it).
 """
 from __future__ import annotations
 
@@ -36,12 +46,18 @@ def pages_for(num_tokens: int, page_size: int) -> int:
     return -(-num_tokens // page_size)            # serving/sequence.py:32-33
 
 
+def _as_list(need) -> list:
+    if need is None:
+        return []
+    return list(need) if isinstance(need, (list, tuple)) else [need]
+
+
 @dataclass
 class CacheGroup:
     need: PagedKVNeed
     page_size: int
     num_pages: int
-    entries: List[int] = field(default_factory=list)          # run entries, in cache-layer order
+    entries: List[Tuple[int, int]] = field(default_factory=list)   # (run entry, index of the need in it), in cache-layer order
     allocator: PageAllocator = None
     kv: Optional[torch.Tensor] = None                         # [layers, 2, pages, Hkv, page, D]
     tables: Dict[Hashable, List[int]] = field(default_factory=dict)
@@ -61,51 +77,87 @@ class CacheGroup:
         # models/model_config.py:84-88, per group
         return 2 * len(self.entries) * self.page_size * self.need.num_kv_heads * self.need.head_dim * elem_size
 
+    def pages_of_request(self, num_tokens: int, max_step_tokens: Optional[int]) -> int:
+        """The most pages a request of ``num_tokens`` holds at one time: all of them, or - with a window - those
+        of the window plus the longest step (pages the window has passed are given back before new ones are taken)."""
+        whole = pages_for(num_tokens, self.page_size)
+        if self.window is None or max_step_tokens is None:
+            return whole
+        return min(whole, pages_for(self.window + max_step_tokens - 1, self.page_size) + 1)
+
 
 class CacheManager:
-    def __init__(self, needs: List[Optional[object]], run_order: List[RunEntry], page_size: int,
+    def __init__(self, needs: List[object], run_order: List[RunEntry], page_size: int,
                  num_pages: Optional[int], max_slots: int, dtype: str, device,
-                 kv_budget_bytes: Optional[int] = None, allocate: bool = True):
-        self.page_size, self.max_slots = int(page_size), int(max_slots)
+                 kv_budget_bytes: Optional[int] = None, allocate: bool = True, max_step_tokens: Optional[int] = None):
+        """``needs[e]``: what run entry ``e`` asks for - None, one need, or a list of needs.  ``page_size`` is the
+        page size of every need that names none.  ``max_step_tokens``: the most tokens a request brings in one
+        step (the scheduler's budget); it bounds what a windowed group has to hold."""
+        self.default_page_size, self.max_slots = int(page_size), int(max_slots)
+        self.max_step_tokens = max_step_tokens
         self.dtype = _TORCH_DTYPES[dtype]
         self.device = torch.device(device)
         self.run_order = list(run_order)
         self.groups: List[CacheGroup] = []
-        self.entry_group: Dict[int, Tuple[int, int]] = {}      # run entry -> (group, cache layer)
-        self.entry_state: Dict[int, torch.Tensor] = {}
-        self._state_needs: Dict[int, FixedStateNeed] = {}
+        self.entry_needs: List[list] = [_as_list(n) for n in needs]
+        self.entry_group: Dict[Tuple[int, int], Tuple[int, int]] = {}    # (run entry, need index) -> (group, cache layer)
+        self.entry_state: Dict[Tuple[int, int], torch.Tensor] = {}
+        self._state_needs: Dict[Tuple[int, int], FixedStateNeed] = {}
         by_need: Dict[PagedKVNeed, int] = {}
-        for e, need in enumerate(needs):
-            if need is None:
-                continue
-            if isinstance(need, PagedKVNeed):
-                if need not in by_need:
-                    by_need[need] = len(self.groups)
-                    self.groups.append(CacheGroup(need, self.page_size, 0))
-                g = by_need[need]
-                self.entry_group[e] = (g, len(self.groups[g].entries))
-                self.groups[g].entries.append(e)
-            elif isinstance(need, FixedStateNeed):
-                self._state_needs[e] = need
-            else:
-                raise TypeError(f"run entry {e}: unknown cache need {need!r}")
+        for e, entry_needs in enumerate(self.entry_needs):
+            for k, need in enumerate(entry_needs):
+                if isinstance(need, PagedKVNeed):
+                    if need not in by_need:
+                        by_need[need] = len(self.groups)
+                        ps = int(need.page_size or self.default_page_size)
+                        if ps < 1:
+                            raise ValueError(f"run entry {e}: page size {ps}")
+                        self.groups.append(CacheGroup(need, ps, 0))
+                    g = by_need[need]
+                    self.entry_group[(e, k)] = (g, len(self.groups[g].entries))
+                    self.groups[g].entries.append((e, k))
+                elif isinstance(need, FixedStateNeed):
+                    self._state_needs[(e, k)] = need
+                else:
+                    raise TypeError(f"run entry {e}: unknown cache need {need!r}")
         elem = torch.empty((), dtype=self.dtype).element_size()
-        if num_pages is None:
-            per_page = sum(g.bytes_per_page(elem) for g in self.groups) or 1
-            num_pages = max(2, int(kv_budget_bytes or 0) // per_page)
-        for g in self.groups:
-            g.num_pages = int(num_pages)
+        if num_pages is not None:
+            tokens = (int(num_pages) - 1) * self.default_page_size
+            counts = [pages_for(tokens, g.page_size) + 1 for g in self.groups]
+        else:
+            counts = self._size_from_budget(int(kv_budget_bytes or 0), elem)
+        for g, n in zip(self.groups, counts):
+            g.num_pages = max(2, int(n))
             g.allocator = PageAllocator(g.num_pages)
             if allocate:
                 # zero-initialised like the reference's pool (serving/kv_pool.py:12-16)
-                g.kv = torch.zeros((len(g.entries), 2, g.num_pages, g.need.num_kv_heads, self.page_size,
+                g.kv = torch.zeros((len(g.entries), 2, g.num_pages, g.need.num_kv_heads, g.page_size,
                                     g.need.head_dim), dtype=self.dtype, device=self.device)
         self.slots = PageAllocator(self.max_slots, reserve_zero=False)
         self.slot_of: Dict[Hashable, int] = {}
         if allocate:
-            for e, need in self._state_needs.items():
-                self.entry_state[e] = torch.zeros((self.max_slots, *need.shape), dtype=_TORCH_DTYPES[need.dtype],
-                                                  device=self.device)
+            for key, need in self._state_needs.items():
+                self.entry_state[key] = torch.zeros((self.max_slots + 1, *need.shape), dtype=_TORCH_DTYPES[need.dtype],
+                                                    device=self.device)
+
+    def _size_from_budget(self, budget: int, elem: int) -> List[int]:
+        """Pages per group (scratch page included) for the largest token capacity that fits ``budget`` bytes."""
+        def pages(g: CacheGroup, tokens: int) -> int:
+            n = pages_for(tokens, g.page_size)
+            if g.window is not None and self.max_step_tokens is not None:
+                n = min(n, self.max_slots * g.pages_of_request(tokens, self.max_step_tokens))
+            return n + 1
+
+        def cost(tokens: int) -> int:
+            return sum(pages(g, tokens) * g.bytes_per_page(elem) for g in self.groups)
+
+        lo, hi = 0, 1
+        while cost(hi) <= budget and hi < (1 << 40):
+            lo, hi = hi, hi * 2
+        while hi - lo > 1:                                     # cost is monotone in tokens
+            mid = (lo + hi) // 2
+            lo, hi = (mid, hi) if cost(mid) <= budget else (lo, mid)
+        return [pages(g, lo) for g in self.groups]
 
     # ---------------------------------------------------------------- requests
     def has_request(self, rid) -> bool:
@@ -125,7 +177,6 @@ class CacheManager:
         for state in self.entry_state.values():
             state[slot].zero_()
         return slot
-
     def _plan(self, rid, start: int, new_len: int):
         """Per group: (pages to free now, logical pages to fill)."""
         plan = []
@@ -191,8 +242,19 @@ class CacheManager:
     def num_usable_pages(self) -> int:
         return min((g.allocator.num_usable for g in self.groups), default=0)
 
-    def max_tokens_in_empty_pool(self) -> int:
-        return self.num_usable_pages * self.page_size
+    @property
+    def page_size(self) -> int:
+        """The smallest page size in use: a portion cut at a multiple of it ends on a page edge in that group."""
+        return min((g.page_size for g in self.groups), default=self.default_page_size)
+
+    def request_fits_empty_pool(self, num_tokens: int) -> bool:
+        """Whether a lone request of ``num_tokens`` could be held with every other page free."""
+        return all(g.pages_of_request(num_tokens, self.max_step_tokens) <= g.allocator.num_usable for g in self.groups)
+
+    def admission_headroom(self, num_tokens: int, reserve: int) -> bool:
+        """The reference's admission rule, group by group (serving/scheduler.py:33-37): after the pages of a request
+        of ``num_tokens`` are taken, ``reserve`` pages must be left."""
+        return all(g.allocator.num_free - g.pages_of_request(num_tokens, self.max_step_tokens) >= reserve for g in self.groups)
 
     def table(self, group: int, rid) -> List[int]:
         return self.groups[group].tables[rid]
@@ -218,19 +280,21 @@ class CacheManager:
             raise AssertionError("a state slot is lost")
 
     # ---------------------------------------------------------------- views for a step
-    def views(self, block_tables: Dict[int, torch.Tensor]) -> List[object]:
-        """One cache view per run entry for a step whose per-group block tables (device,
-        int32 [N, max_pages]) are given."""
-        views: List[object] = []
+    def views(self, block_tables: Dict[int, torch.Tensor]) -> List[List[object]]:
+        """For every run entry the list of its cache views, one per need in the order the block reported them, for
+        a step whose per-group block tables (device, int32 [N, max_pages]) are given.  An entry that reads another
+        entry's cache gets that entry's views, not writable."""
+        views: List[List[object]] = []
         for e, entry in enumerate(self.run_order):
             src = e if entry.cache_from is None else entry.cache_from
             writable = entry.cache_from is None
-            if src in self.entry_group:
-                gi, layer = self.entry_group[src]
-                g = self.groups[gi]
-                views.append(PagedKVView(g.kv[layer, 0], g.kv[layer, 1], block_tables[gi], g.page_size, writable))
-            elif src in self.entry_state:
-                views.append(FixedStateView(self.entry_state[src], writable))
-            else:
-                views.append(None)
+            mine = []
+            for k in range(len(self.entry_needs[src])):
+                if (src, k) in self.entry_group:
+                    gi, layer = self.entry_group[(src, k)]
+                    g = self.groups[gi]
+                    mine.append(PagedKVView(g.kv[layer, 0], g.kv[layer, 1], block_tables[gi], g.page_size, writable))
+                else:
+                    mine.append(FixedStateView(self.entry_state[(src, k)], writable))
+            views.append(mine)
         return views

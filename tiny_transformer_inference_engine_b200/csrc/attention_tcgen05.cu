@@ -49,9 +49,10 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+// limit: clocks after which the wait gives up (about a second by default)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code, long long limit = WAIT_CYCLES) {
     if (mbar_try(bar, parity)) return true;
-    const long long deadline = clock64() + WAIT_CYCLES;
+    const long long deadline = clock64() + limit;
     while (!mbar_try(bar, parity)) {
         if (clock64() > deadline) {
             atomicCAS(&g_attn_tc_error, 0, code);
@@ -1001,8 +1002,25 @@ EncodeTiledFn encode_fn() {
     }
     return fn;
 }
-// pages [num_pages][Hkv][page][D] seen as a matrix [num_pages*Hkv*page][D]; box = 64 columns x box_rows keys
+// pages [num_pages][Hkv][page][D] seen as a matrix [num_pages*Hkv*page][D]; box = 64 columns x box_rows keys.
+// A pool keeps its address for the life of an engine and every layer of every step asks for the same few maps, so the
+// last ones made are kept (per host thread) and an encode is paid once per pool, layer and kernel form.
+int encode_page_map(CUtensorMap* map, const void* base, long long rows, int D, int box_rows);
 int make_page_map(CUtensorMap* map, const void* base, long long rows, int D, int box_rows) {
+    struct Kept { const void* base; long long rows; int D, box_rows; CUtensorMap map; };
+    constexpr int KEEP = 256;
+    thread_local Kept kept[KEEP];
+    thread_local int used = 0, next = 0;
+    for (int i = 0; i < used; ++i)
+        if (kept[i].base == base && kept[i].rows == rows && kept[i].D == D && kept[i].box_rows == box_rows) { *map = kept[i].map; return 0; }
+    if (encode_page_map(map, base, rows, D, box_rows)) return -1;
+    Kept& k = kept[next];
+    k.base = base; k.rows = rows; k.D = D; k.box_rows = box_rows; k.map = *map;
+    next = (next + 1) % KEEP;
+    if (used < KEEP) ++used;
+    return 0;
+}
+int encode_page_map(CUtensorMap* map, const void* base, long long rows, int D, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) TTIE_FAIL("attention_tc: cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
@@ -1020,8 +1038,14 @@ template <int D, bool AHEAD>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, cudaStream_t s) {
     const size_t smem = (size_t)(D / 64) * BM * 128 + 4 * (size_t)(D / 64) * BN * 128 + 1024;
     auto k = attn_tc_kernel<D, AHEAD>;
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    static bool allowed[64] = {false};                           // the attribute is set once per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!allowed[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        allowed[dev] = true;
+    }
     k<<<dim3(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits), NTHREADS, smem, s>>>(mk, mv, p);
     TTIE_CHECK_LAUNCH("attention_tc");
     return 0;
@@ -1031,13 +1055,39 @@ int launch_pp(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& 
     constexpr int NT = D > 128 ? 1 : 2, NSD = D > 128 ? 4 : pp::NS;
     const size_t smem = NT * (size_t)(D / 64) * BM * 128 + NSD * (size_t)(D / 64) * pp::BNK * 128 + 1024;
     auto k = attn_tc_pp_kernel<D, NT>;
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    static bool allowed[64] = {false};                           // the attribute is set once per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!allowed[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        allowed[dev] = true;
+    }
     k<<<dim3(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits), pp::PP_NTHREADS, smem, s>>>(mk, mv, p);
     TTIE_CHECK_LAUNCH("attention_tc (two query tiles)");
     return 0;
 }
 }  // namespace
+
+// The path a kernel takes when a barrier never completes, run on purpose and briefly: one thread waits with the
+// kernels' own bounded wait, and a limit of the caller's choosing, on a barrier at which nobody arrives.  The wait runs
+// out, records `code` in the error word and its host mirror as it would in an attention kernel, and the kernel returns.
+__global__ void wait_selftest_kernel(long long limit_cycles, int code, int* gave_up) {
+    __shared__ __align__(8) unsigned long long bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *gave_up = mbar_wait(smem_u32(&bar), 0, code, limit_cycles) ? 0 : 1;
+}
+extern "C" int ttie_attn_tc_wait_selftest(long long limit_cycles, int code, int* gave_up, void* stream) {
+    if (limit_cycles <= 0 || limit_cycles > 200000000LL) TTIE_FAIL("wait self-test: limit of %lld clocks (1 .. 200,000,000)", limit_cycles);
+    if (!gave_up) TTIE_FAIL("wait self-test: no result word");
+    wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_cycles, code, gave_up);
+    TTIE_CHECK_LAUNCH("wait self-test");
+    return 0;
+}
 
 // A word of pinned host memory (device-accessible) that also receives the failure code, so the host can look at it
 // after every step without a call into the runtime.  nullptr: none.

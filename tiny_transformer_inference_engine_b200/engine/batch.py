@@ -137,11 +137,12 @@ class BatchPacker:
         scratch page with length 1, and the tables get ``pages_per_seq[group]`` columns.
         ``copy_only``: fill and copy the buffer but build no context (a graph replay needs none)."""
         key = None
-        if (copy_only and buffers is not None
-                and all(len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e in entries)
-                and all(g.window is None for g in self.manager.groups)):
+        if buffers is not None and all(len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e in entries):
+            # a decode step in a fixed layout: its layout is remembered (tokens may be fed into it on the device), and
+            # where no group has a window - a window moves table entries that the short path does not look at - the
+            # next step of the same requests rewrites only what changed
             key = (tuple(e.rid for e in entries), pad_seqs, tuple(sorted(pages_per_seq.items())), buffers[0].data_ptr())
-            if self._repack_decode(entries, key):
+            if copy_only and all(g.window is None for g in self.manager.groups) and self._repack_decode(entries, key):
                 return None
         self._last = None
         self.validate(entries)

@@ -51,6 +51,10 @@ class Engine:
         self.ops = ops
         self.spec = model_spec(config)
         self.model = Model(self.spec)
+        # sizes the kernels do not take are refused here, before weights are read or a pool is made
+        if hasattr(ops, "check_dtype"):
+            ops.check_dtype(self.dtype)
+        self.model.validate(ops, self.dtype, ec.cache.block_size)
         specs = self.model.param_specs()
         # weights are checked against the configuration before anything large is allocated
         if isinstance(tensors_or_folder, (str, os.PathLike)):
@@ -63,11 +67,16 @@ class Engine:
         needs = self.model.cache_needs()
         self.manager = CacheManager(needs, self.model.run_order, ec.cache.block_size, ec.cache.num_gpu_blocks,
                                     ec.sched.max_num_seqs, ec.kv_dtype, self.device,
-                                    kv_budget_bytes=ec.cache.kv_budget_bytes)
-        # models/model_config.py:101-102: the pool must hold one full-length sequence plus the scratch page
-        if self.manager.groups and self.manager.num_usable_pages * ec.cache.block_size < 1:
-            raise ValueError("the cache pool holds no page")
-        graphs = ec.sched.cudagraph_batch_sizes if (ec.use_cuda_graphs and self.device.type == "cuda") else []
+                                    kv_budget_bytes=ec.cache.kv_budget_bytes,
+                                    max_step_tokens=ec.sched.max_num_batched_tokens)
+        # The reference insists that the pool hold one sequence of max_seq_len plus the scratch page
+        # (models/model_config.py:101-102).  Here a smaller pool is allowed on purpose - a replay or a test sizes its
+        # pool for the tokens it will hold - and add_request refuses a request that could never fit; what cannot work
+        # at all is a group without a usable page.
+        if any(g.allocator.num_usable < 1 for g in self.manager.groups):
+            raise ValueError("a cache group holds no usable page")
+        # a part that reads device values on the host keeps the whole model off the captured path
+        graphs = ec.sched.cudagraph_batch_sizes if (ec.use_cuda_graphs and self.device.type == "cuda" and self.model.capturable) else []
         self.stepper = Stepper(self.model, self.manager, ops, self.dtype, self.device, graphs)
         self.sampler = Sampler(ops, ec.sched.max_num_seqs, config.vocab_size, self.device)
         self._slot_ids = None

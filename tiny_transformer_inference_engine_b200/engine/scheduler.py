@@ -92,8 +92,8 @@ class Scheduler:
         if params.max_new_tokens == 0:
             raise ValueError("max_new_tokens must be > 0 for a scheduled request")
         most = len(prompt) + params.max_new_tokens - 1      # the last sampled token is never cached
-        if pages_for(most, self.manager.page_size) > self.manager.num_usable_pages:
-            raise ValueError(f"request needs {pages_for(most, self.manager.page_size)} pages; "
+        if not self.manager.request_fits_empty_pool(most):
+            raise ValueError(f"request needs {pages_for(most, self.manager.page_size)} pages of {self.manager.page_size} tokens; "
                              f"an empty pool has {self.manager.num_usable_pages}")
         req = Request(self.next_rid, prompt, params)
         self.next_rid += 1
@@ -144,9 +144,8 @@ class Scheduler:
     def _admit_ok(self, req: Request) -> bool:
         if not self.manager.can_admit() or len(self.running) >= self.config.max_num_seqs:
             return False
-        need = pages_for(req.num_tokens, self.manager.page_size)
-        # serving/scheduler.py:33-37: keep one growth page for every running request and this one
-        return self.manager.num_free_pages - need >= len(self.running) + 1 or not self.running
+        # serving/scheduler.py:33-37: keep one growth page for every running request and this one (in every cache group)
+        return self.manager.admission_headroom(req.num_tokens, len(self.running) + 1) or not self.running
 
     def plan(self) -> List[StepEntry]:
         """Chooses the step's entries and takes their pages.  ``want`` is ``[last]`` for an

@@ -87,23 +87,32 @@ class Stepper:
         g = self._graphs.get(key)
         pages = self._fixed_pages()
         if g is None:
+            # The step that meets a new (batch, context) bucket runs eagerly - that is the warm-up - and its results
+            # are the step's results; the capture that follows runs nothing, so per-request state that a part advances
+            # (fixed-size state, sampler draw counters) moves once.
             words = 8 * (bucket + 4) + sum(bucket * w + 4 for w in pages.values()) + 64
             host = torch.empty(words, dtype=torch.int32, pin_memory=True)
             dev = torch.zeros(words, dtype=torch.int32, device=self.device)
             ctx = self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(host, dev))
+            if feed is not None:
+                self.packer.feed_tokens(feed)
             # the captured kernels must cover every context length of the bucket: size them for the longest
             ctx.max_kv_len = keys                                # (a decode step is one class: nothing else carries a length)
             views = self.manager.views(ctx.block_tables)
-            self.model.forward(ctx, views)                       # warm-up outside the capture
+            logits = self.model.forward(ctx, views)
+            tokens = sampler.sample(logits, ctx.slot_ids) if sampler is not None else None
             torch.cuda.synchronize(self.device)
             ctx.step_cache.clear()                              # what parts computed once per step is computed again inside the graph
             graph = torch.cuda.CUDAGraph()
             before = getattr(self.ops, "launches", 0)
-            with torch.cuda.graph(graph):                       # (capturing runs nothing: no draw is counted here)
-                logits = self.model.forward(ctx, views)
-                tokens = sampler.sample(logits, ctx.slot_ids) if sampler is not None else None
-            g = _DecodeGraph(bucket, host, dev, graph, logits, tokens, ctx, getattr(self.ops, "launches", 0) - before)
-            self._graphs[key] = g
+            with torch.cuda.graph(graph):
+                g_logits = self.model.forward(ctx, views)
+                g_tokens = sampler.sample(g_logits, ctx.slot_ids) if sampler is not None else None
+            self._graphs[key] = _DecodeGraph(bucket, host, dev, graph, g_logits, g_tokens, ctx,
+                                             getattr(self.ops, "launches", 0) - before)
+            if tokens is not None:
+                self.last_tokens = tokens[:n]
+            return logits[:n]
         self.packer.pack(entries, pad_seqs=bucket, pages_per_seq=pages, buffers=(g.host, g.dev), copy_only=True)
         if feed is not None:
             self.packer.feed_tokens(feed)

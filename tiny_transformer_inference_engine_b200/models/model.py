@@ -68,17 +68,24 @@ class Model:
             owners[pid].load(params)
 
     # ---------------------------------------------------------------- cache
-    def cache_needs(self) -> List[Optional[object]]:
-        """What each run entry needs of the cache manager (None for an entry that reads
-        another entry's cache or needs nothing)."""
-        needs = []
-        for entry in self.run_order:
-            need = self.blocks[entry.layer].mixer_part().cache_need()
-            needs.append(None if entry.cache_from is not None else need)
-        return needs
+    def cache_needs(self) -> List[List[object]]:
+        """What each run entry needs of the cache manager: the list its block reports (empty for an entry that
+        reads another entry's cache or keeps nothing)."""
+        return [[] if entry.cache_from is not None else list(self.blocks[entry.layer].cache_needs())
+                for entry in self.run_order]
+
+    @property
+    def capturable(self) -> bool:
+        """False if any part says its step cannot run inside a captured CUDA graph."""
+        return all(p.capturable for p in self.parts())
+
+    def validate(self, ops, dtype: torch.dtype, page_size: int) -> None:
+        """Asks every part whether its kernels take its sizes (raises with the part's message if not)."""
+        for p in self.parts():
+            p.validate(ops, dtype, page_size)
 
     # ---------------------------------------------------------------- step
-    def forward(self, ctx: StepContext, cache_views: List[object]) -> torch.Tensor:
+    def forward(self, ctx: StepContext, cache_views: List[List[object]]) -> torch.Tensor:
         """Runs the step's tokens; returns float32 logits [ctx.num_logit_rows, vocab]."""
         stream = ResidualStream(self.embedding.forward(ctx))
         for e, entry in enumerate(self.run_order):

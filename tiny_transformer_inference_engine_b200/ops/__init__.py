@@ -84,6 +84,9 @@ class CudaOps:
         self.lib.ttie_last_error.restype = ctypes.c_char_p
         self.launches = 0                     # kernels of this library launched so far
         self.num_sms = int(torch.cuda.get_device_properties(self.device).multi_processor_count)   # the plans below are sized for it
+        self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None) or \
+            (lambda index: torch.cuda.current_stream(index).cuda_stream)
         self.attn_target_ctas = 4 * self.num_sms  # decode tiles are small: four CTAs share an SM
         self.attn_cluster_max_rows = 64         # query rows per request (tokens x heads per kv head) up to which the decode form runs
         self.attn_cluster_max_size = 8          # CTAs per cluster (16 is placed on fewer SMs at a time)
@@ -109,9 +112,11 @@ class CudaOps:
         if rc != 0:
             raise KernelError(f"{what}: {self.lib.ttie_last_error().decode()}")
 
-    @staticmethod
-    def _stream(t: torch.Tensor):
-        return torch.cuda.current_stream(t.device).cuda_stream
+    def _stream(self, t: torch.Tensor = None):
+        """torch's current stream of the device as a raw handle (asked at every call: a graph capture changes it).
+        The direct query is an order of magnitude cheaper than building a ``torch.cuda.Stream`` object, which
+        counts on steps that are not replayed from a graph."""
+        return self._raw_stream(self._device_index)
 
     @staticmethod
     def _dt(t: torch.Tensor) -> int:
@@ -119,6 +124,27 @@ class CudaOps:
             return _DT[t.dtype]
         except KeyError:
             raise KernelError(f"dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+    # ------------------------------------------------------------------ what the kernels take
+    def check_dtype(self, dtype):
+        if dtype not in _DT:
+            raise KernelError(f"dtype {dtype} is not supported (float32 or bfloat16)")
+
+    def check_attention(self, dtype, num_heads, num_kv_heads, head_dim, page_size):
+        """Raises unless some attention kernel here takes the sizes: the general kernel takes every head size that is
+        a multiple of 4 up to 256, any head counts and any page size (the tensor-core kernels cover subsets of that)."""
+        self.check_dtype(dtype)
+        if head_dim <= 0 or head_dim % 4 or head_dim > 256:
+            raise KernelError(f"attention: head size {head_dim} not supported (multiples of 4 up to 256)")
+        if num_kv_heads <= 0 or num_heads % num_kv_heads:
+            raise KernelError(f"attention: {num_heads} heads are not a multiple of {num_kv_heads} kv heads")
+        if page_size < 1:
+            raise KernelError(f"attention: page size {page_size}")
+
+    def check_norm(self, dtype, dim):
+        self.check_dtype(dtype)
+        if dim * 4 > 200 * 1024:
+            raise KernelError(f"rmsnorm: width {dim} needs {dim * 4} bytes of shared memory (limit 204800)")
 
     # ------------------------------------------------------------------ ops
     def embed(self, token_ids, table, out):

@@ -253,8 +253,11 @@ def main(argv=None):
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--attn-batches", default="1,8,64", help="batch sizes of --what attention")
     ap.add_argument("--attn-contexts", default="", help="context lengths of --what attention (default 512, 2048, ctx, 4 ctx)")
+    ap.add_argument("--skinny-max-rows", type=int, default=None, help="rows up to which the weight-streaming product is used (default: the engine's)")
     a = ap.parse_args(argv)
     ops = get_ops(DEV)
+    if a.skinny_max_rows is not None:
+        ops.skinny_max_rows = a.skinny_max_rows
     if a.what in ("decode", "all"):
         decode(ops, a)
     if a.what in ("prefill", "all"):

@@ -70,6 +70,11 @@ class PagedAttention(Mixer):
             self.b_in = torch.cat([params[f"{n[k]}.bias"] for k in keys], dim=0).contiguous()
             self.b_out = params[f"{n['o']}.bias"].contiguous()
 
+    def validate(self, ops, dtype, page_size):
+        check = getattr(ops, "check_attention", None)
+        if check is not None:
+            check(dtype, self.num_heads, self.num_kv_heads, self.head_dim, page_size)
+
     # ---------------------------------------------------------------- cache
     def cache_need(self):
         return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
@@ -102,9 +107,19 @@ class PagedAttention(Mixer):
                        q_out=q if qkv.dim() == 3 else None, cs_table=cs_table)
         out = torch.empty((T, Hq * D), dtype=x.dtype, device=x.device)
         # one launch per class of requests (decoded tokens; prompt portions), each planned as if it were alone
-        for c in ctx.classes():
-            ops.paged_attention(q[c.tok_lo:c.tok_hi], Hq, Hkv, D, cache.k_pages, cache.v_pages,
-                                cache.block_table[c.seq_lo:c.seq_hi], cache.page_size, c.query_start_loc,
-                                ctx.seq_lens[c.seq_lo:c.seq_hi], c.seq_hi - c.seq_lo, c.max_q_len, c.max_kv_len,
-                                self.scale, self.window or 0, out[c.tok_lo:c.tok_hi])
+        classes = ctx.classes()
+        if len(classes) == 1:
+            c = classes[0]
+            ops.paged_attention(q, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
+                                c.query_start_loc, ctx.seq_lens, ctx.num_seqs, c.max_q_len, c.max_kv_len,
+                                self.scale, self.window or 0, out)
+        else:
+            for ci, c in enumerate(classes):
+                key = ("attention class views", id(cache.block_table), ci)    # the same for every layer of a cache group
+                views = ctx.step_cache.get(key)
+                if views is None:
+                    views = ctx.step_cache[key] = (cache.block_table[c.seq_lo:c.seq_hi], ctx.seq_lens[c.seq_lo:c.seq_hi])
+                ops.paged_attention(q[c.tok_lo:c.tok_hi], Hq, Hkv, D, cache.k_pages, cache.v_pages, views[0],
+                                    cache.page_size, c.query_start_loc, views[1], c.seq_hi - c.seq_lo, c.max_q_len,
+                                    c.max_kv_len, self.scale, self.window or 0, out[c.tok_lo:c.tok_hi])
         return ops.linear(out, self.w_out, self.b_out, partial_ok=True)

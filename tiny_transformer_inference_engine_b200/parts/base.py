@@ -11,11 +11,16 @@ Categories and the methods each must have:
 
 ``norm``      ``add_norm(resid, delta) -> x``; ``norm_rows(resid, delta, rows) -> x``
 ``position``  ``rotary_table() -> (inv_freq, style) | None``; ``apply(q, k, positions)``
-``mixer``     ``cache_need()``; ``forward(x, ctx, cache) -> y``
+``mixer``     ``cache_need()`` (or ``cache_needs()`` for several); ``forward(x, ctx, cache) -> y``
 ``ffn``       ``forward(x, ctx) -> y``
 ``embedding`` ``forward(ctx) -> resid``
 ``head``      ``forward(x) -> logits``
-``block``     ``forward(stream, ctx, cache)`` (arrangement of the four above)
+``block``     ``cache_needs()``; ``forward(stream, ctx, caches)`` (arrangement of the four above)
+
+Every part may also say ``capturable = False`` (its step reads device values on the host, so it
+cannot run inside a captured CUDA graph: a model with such a part steps without graphs) and
+override ``validate(ops, dtype, page_size)`` to refuse, when the engine is built, sizes that
+its kernels do not take.
 """
 from __future__ import annotations
 
@@ -45,7 +50,8 @@ class ParamSpec:
     """
     shape: Tuple[int, ...]
     storage: str = "matrix"            # "matrix" | "vector" | "table"
-    init: str = "normal"               # random-weights mode: "normal" | "ones" | "zeros"
+    init: str = "normal"               # random-weights mode: "normal" | "ones" | "zeros"; tables: "randint" | "arange" | "zeros"
+    high: Optional[int] = None         # "randint": values are uniform in [0, high)
 
 
 @dataclass(frozen=True)
@@ -81,6 +87,7 @@ class PagedKVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None       # None: all keys
+    page_size: Optional[int] = None    # None: the engine's page size
 
 
 @dataclass(frozen=True)
@@ -101,7 +108,7 @@ class PagedKVView:
 
 @dataclass
 class FixedStateView:
-    state: torch.Tensor                # [state_slots, *shape]; row = ctx.slot_ids[seq]
+    state: torch.Tensor                # [state_slots + 1, *shape]; row = ctx.slot_ids[seq]; the last row is scratch (slot id -1)
     writable: bool = True
 
 
@@ -177,6 +184,7 @@ class ResidualStream:
 class Part:
     """Base of every part: constants in, tensor specs out, tensors loaded by relative name."""
     category = "part"
+    capturable = True                  # False: the part's step cannot be captured in a CUDA graph
 
     def __init__(self, prefix: str = ""):
         self.prefix = prefix
@@ -198,6 +206,10 @@ class Part:
         self.ops, self.dtype, self.device = ops, dtype, device
         for c in self.children():
             c.bind(ops, dtype, device)
+
+    def validate(self, ops, dtype: torch.dtype, page_size: int) -> None:
+        """Raises if the part's sizes, the compute dtype or the page size are something its kernels do not take.
+        Called when the engine is built, before weights are read or a pool is allocated."""
 
 
 class Norm(Part):
@@ -233,7 +245,15 @@ class Mixer(Part):
     category = "mixer"
 
     def cache_need(self):
+        """The one thing this mixer keeps between steps (``PagedKVNeed``, ``FixedStateNeed``) or None; ``forward``
+        then receives the one view made for it (or None)."""
         return None
+
+    def cache_needs(self) -> List[object]:
+        """For a mixer that keeps several things (say pages and a state of fixed size): the list of its needs;
+        ``forward`` then receives the list of views in the same order.  The default wraps ``cache_need()``."""
+        need = self.cache_need()
+        return [] if need is None else [need]
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
         raise NotImplementedError
@@ -263,8 +283,18 @@ class Head(Part):
 class Block(Part):
     category = "block"
 
-    def mixer_part(self) -> Mixer:
+    def cache_needs(self) -> List[object]:
+        """Everything the block's sub-parts keep between steps, as one list; ``forward`` receives as many views, in
+        this order, and hands each sub-part its own."""
+        return []
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches: List[object]) -> None:
         raise NotImplementedError
 
-    def forward(self, stream: ResidualStream, ctx: StepContext, cache) -> None:
-        raise NotImplementedError
+
+def mixer_cache_argument(mixer: Mixer, views: List[object]):
+    """What a mixer's ``forward`` gets as ``cache`` out of the views made for its needs: the list itself if the
+    mixer declares ``cache_needs()`` of its own, else the single view (None if it keeps nothing)."""
+    if type(mixer).cache_needs is not Mixer.cache_needs:
+        return list(views)
+    return views[0] if views else None

@@ -7,7 +7,7 @@
 """
 from __future__ import annotations
 
-from .base import Block, PartSpec, ResidualStream, StepContext
+from .base import Block, PartSpec, ResidualStream, StepContext, mixer_cache_argument
 from ..registry import register_part, build_part
 
 
@@ -23,11 +23,11 @@ class PreNormBlock(Block):
     def children(self):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
 
-    def mixer_part(self):
-        return self.mixer
+    def cache_needs(self):
+        return self.mixer.cache_needs()                            # the feed-forward parts here keep nothing between steps
 
-    def forward(self, stream: ResidualStream, ctx: StepContext, cache) -> None:
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches) -> None:
         h = self.mixer_norm.add_norm(stream.resid, stream.delta)
-        a = self.mixer.forward(h, ctx, cache)
+        a = self.mixer.forward(h, ctx, mixer_cache_argument(self.mixer, caches))
         h = self.ffn_norm.add_norm(stream.resid, a)
         stream.delta = self.ffn.forward(h, ctx)

@@ -30,6 +30,11 @@ class RMSNorm(Norm):
     def load(self, params):
         self.weight = params["weight"]
 
+    def validate(self, ops, dtype, page_size):
+        check = getattr(ops, "check_norm", None)
+        if check is not None:
+            check(dtype, self.dim)
+
     def add_norm(self, resid: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         out = torch.empty(resid.shape, dtype=self.dtype, device=resid.device)
         self.ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)

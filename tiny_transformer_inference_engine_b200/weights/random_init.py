@@ -2,7 +2,7 @@
 
 Every matrix, embedding and bias is N(0, std) from a CPU ``torch.Generator`` seeded
 with ``seed``, drawn in the sorted order of the tensor names so that the same
-(config, seed) always gives the same bits; norm weights are ``1 + N(0, std)`` when
+(config, seed) always gives the same bits; integer tables follow the rule their ``ParamSpec`` names; norm weights are ``1 + N(0, std)`` when
 ``perturb_norms`` is set (so a test sees the norm weight act) and 1 otherwise, which
 is the reference's initialisation (models/rmsnorm.py:9).
 """
@@ -34,7 +34,17 @@ def random_tensors(config: ModelConfig, seed: int, std: float = 0.02, perturb_no
     for name in sorted(specs):
         ps = specs[name][2]
         if ps.storage == "table":
-            raise ValueError(f"no random rule for integer table {name}")
+            # integer tables: uniform in [0, high), or 0, 1, 2, ... along the last dimension, or zeros
+            if ps.init == "randint" and ps.high:
+                t = torch.randint(0, int(ps.high), ps.shape, generator=gen, device=device)
+            elif ps.init == "arange":
+                t = torch.arange(ps.shape[-1], device=device).expand(ps.shape)
+            elif ps.init == "zeros":
+                t = torch.zeros(ps.shape, dtype=torch.int64, device=device)
+            else:
+                raise ValueError(f"integer table {name}: its ParamSpec must say init='randint' (with high=), 'arange' or 'zeros'")
+            out[name] = t.to(torch.int32).contiguous()
+            continue
         if ps.init == "normal":
             t = torch.randn(ps.shape, generator=gen, dtype=torch.float32, device=device) * std
         elif ps.init == "ones":
