@@ -8,7 +8,9 @@ install it.  Each of its kernels has a ``setup.py`` of its own (kernels/pagedatt
 kernels/rmsnorm_kernel/setup.py, kernels/rope_kernel/setup.py, kernels/flashattn/setup.py,
 kernels/softmax_kernel/setup.py, kernels/cuda-kSAMPLING/setup.py); this script runs each of them
 with ``build_ext --inplace`` in the copy, with ``TORCH_CUDA_ARCH_LIST=10.0`` in the environment so
-that torch's extension builder adds an sm_100 target beside whatever the file itself asks for.
+that torch's extension builder targets sm_100.  ``kernels/pagedattn/setup.py`` names its own targets
+(sm_80 and sm_90 machine code, no PTX), and torch adds none when a file does that, so for that one the
+sm_100 target is handed to nvcc through its ``NVCC_APPEND_FLAGS`` environment variable.
 No file of the reference is edited.  nvcc cross-compiles, so no GPU is needed.
 
 ``bench.py --impl reference`` imports the copy from ``baseline/_ref`` and reports ``unavailable``
@@ -24,6 +26,7 @@ import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
+OWN_TARGETS = {"pagedattn"}      # folders whose setup.py fixes the nvcc targets itself
 KERNELS = {                      # folder under kernels/ -> module it builds
     "rmsnorm_kernel": "rmsnorm_cuda",
     "rope_kernel": "rope_cuda",
@@ -62,8 +65,9 @@ def main() -> int:
         print(f"{module}: building in kernels/{folder} ...", flush=True)
         log = os.path.join(DEST, "kernels", folder, "build_sm100.log")
         with open(log, "w") as f:
+            kenv = dict(env, NVCC_APPEND_FLAGS="-gencode=arch=compute_100,code=sm_100") if folder in OWN_TARGETS else env
             rc = subprocess.call([sys.executable, "setup.py", "build_ext", "--inplace"], cwd=os.path.join(DEST, "kernels", folder),
-                                 env=env, stdout=f, stderr=subprocess.STDOUT)
+                                 env=kenv, stdout=f, stderr=subprocess.STDOUT)
         ok = rc == 0 and built(module, folder)
         print(f"{module}: {'ok' if ok else 'FAILED (see ' + log + ')'} after {time.time() - t0:.0f} s", flush=True)
         if not ok:

@@ -263,9 +263,25 @@ def main():
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "pip cannot install the reference: neither setup.py nor pyproject.toml; its CUDA extensions "
-                          "are prebuilt for cpython-310/sm_86 and its paged path needs them"}))
+        # The unmodified reference from baseline/_ref, in a process of its own (none of this package is imported there):
+        # baseline/reference_arm.py builds its PagedTransformer at the same sizes and times its generate_batched loop.
+        if args.gpus != 1:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference runs on one GPU"}))
+            return 0
+        cmd = [sys.executable, os.path.join(ROOT, "baseline", "reference_arm.py"), "--steps", str(args.steps),
+               "--warmup", str(max(args.warmup, 3)), "--batch", str(args.batch)]
+        if args.layers:
+            cmd += ["--layers", str(args.layers)]
+        try:
+            run = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+            lines = [l for l in run.stdout.strip().split("\n") if l.startswith("{")]
+            if run.returncode == 0 and lines:
+                print(lines[-1])
+            else:
+                tail = " ".join((run.stderr or run.stdout).split())[-300:]
+                print(json.dumps({"impl": "reference", "unavailable": f"the reference's process ended with code {run.returncode}: {tail}"}))
+        except subprocess.TimeoutExpired:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's process did not finish in 1500 s"}))
         return 0
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")

@@ -371,6 +371,10 @@ paged_attn_cluster_kernel(const MmaParams p) {
     const int nrows = q_len * G;
     const int row0 = rt * BM;
     if (row0 >= nrows) return;                                                     // the same for every CTA of the cluster
+    // "I have started": a CTA may write into another's shared memory only once that CTA is known to run, and a CTA
+    // with no keys of its own reaches the exchange at once.  The matching wait stands before the first remote
+    // store; the key loop lies between them, so it costs nothing.
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     const int ctx = kv_len - q_len;
 
     const int tok_lo = row0 / G, tok_hi = (min(nrows, row0 + BM) - 1) / G;
@@ -563,6 +567,7 @@ paged_attn_cluster_kernel(const MmaParams p) {
         if ((lane & 3) == 0) { MLp[(kg * BM + r) * 2] = m_run[h]; MLp[(kg * BM + r) * 2 + 1] = l; }
     }
     __syncthreads();
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");                    // every CTA of the cluster has started
     // the groups of this CTA, in group order (maxima are in log2 units)
     const int rows_per_owner = (BM + (int)C - 1) / (int)C;
     for (int e = tid; e < BM * (D / 4); e += NT) {

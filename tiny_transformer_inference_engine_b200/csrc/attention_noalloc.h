@@ -23,6 +23,9 @@ extern "C" {
 //
 // * The first call on a device looks up the array's device address (cudaGetSymbolAddress with
 //   that device current).  Make that first call before any stream capture begins.
+// * T must be the number of query tokens the requests bring, qsl[num_seqs] (no padding tokens behind
+//   them): the pass that adds the splits up reads T * Hq rows of partial results, and only the rows of
+//   the requests' own tokens have been written.
 // * All calls on a device share the array.  Nothing in it has to start at zero - every entry a
 //   call reads, the same call has written - so the last call's contents do no harm; but two calls
 //   that overlap on the GPU (different streams, no ordering) race on it.  Order them.
