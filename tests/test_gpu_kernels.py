@@ -326,8 +326,11 @@ def sampler_state(rows):
     return st
 
 
-@pytest.mark.parametrize("V", [256, 515, 1000, 32000, 65024])
-def test_sampling_distribution_and_draw(ops, V):
+@pytest.mark.parametrize("V,ctas", [(256, 0), (515, 1), (515, 2), (1000, 4), (1000, 8), (32000, 0), (32000, 1), (65024, 0), (65024, 2),
+                                    (50001, 8), (256000, 0), (50000, 1), (337001, 8)])
+def test_sampling_distribution_and_draw(ops, V, ctas):
+    """``ctas`` CTAs share a row (0: the kernel's own choice); vocabularies that are no multiple of anything, slices
+    that fit shared memory and slices that do not (50,000 tokens with one CTA, 337,001 with eight)."""
     g = torch.Generator().manual_seed(V)
     rows = [(1, 0, 0, 1.0, 1.0, 0), (2, 5, 32, 0.8, 1.0, 0), (3, 1, 0, 0.7, 0.9, 0), (4, 9, 50, 1.3, 0.5, 0),
             (5, 2, 1, 1.0, 1.0, 0), (6, 0, 0, 1.0, 1.0, 1), (7, 3, V + 5, 2.0, 0.999, 0), (8, 4, 3, 0.1, 0.3, 0)]
@@ -339,7 +342,11 @@ def test_sampling_distribution_and_draw(ops, V):
     out = torch.empty(R, dtype=torch.int32, device=DEV)
     probs = torch.zeros(R, V, device=DEV)
     st_gpu = state.clone().to(DEV)
-    ops.sample(logits.to(DEV), slot_ids.to(DEV), st_gpu, out, probs_out=probs)
+    ops.sample(logits.to(DEV), slot_ids.to(DEV), st_gpu, out, probs_out=probs, ctas_per_row=ctas)
+    # the same draws without asking for the probabilities, and whatever the number of CTAs: the same tokens
+    again = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), slot_ids.to(DEV), state.clone().to(DEV), again, ctas_per_row=1 if ctas != 1 else 4)
+    assert torch.equal(again, out)
     out, probs, st_after = out.cpu(), probs.cpu(), st_gpu.cpu()
     assert torch.equal(st_after[:, 2], state[:, 2] + 1)           # every draw counter advanced
     for r, (seed, draws, top_k, temp, top_p, greedy) in enumerate(rows):

@@ -1,4 +1,4 @@
-// Sampling on the device: one block per row of logits, per-request state in a table.
+// Sampling on the device: a row of logits is shared by up to 8 CTAs (a thread-block cluster), per-request state in a table.
 //
 // Order and meaning as the reference's sample() (sampling.py:110-135): logits / temperature,
 // top-k as a threshold (everything >= the k-th largest value stays, sampling.py:85-92), top-p
@@ -61,38 +61,133 @@ __device__ u64 block_sum_u64(u64 v, u64* scratch) {
     return r;
 }
 
-// staged: the row (divided by the temperature) lives in shared memory after the first pass, so the later passes
-// do not go back to global memory; a row too long for that is read from global memory every time.
+// ---- histograms in shared memory.  The keys of a row crowd into a few bins of the leading digit, so one atomic per
+// element would serialise; a warp first adds up the contributions of its lanes that fall into the same bin and one
+// lane per bin adds the sum.  All 32 lanes call these together; a lane without an element passes bin = -1.
+__device__ __forceinline__ void hist_add_count(u64* hist, int bin) {
+    if (!__ballot_sync(0xffffffffu, bin >= 0)) return;               // (after the leading digit few lanes still take part)
+    const unsigned peers = __match_any_sync(0xffffffffu, bin);
+    if (bin >= 0 && (int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (u64)__popc(peers));
+}
+__device__ __forceinline__ void hist_add_mass(u64* hist, int bin, u64 mass) {
+    unsigned todo = __ballot_sync(0xffffffffu, bin >= 0);
+    while (todo) {                                                    // one round per distinct bin among the lanes
+        const int leader = __ffs(todo) - 1;
+        const int b = __shfl_sync(0xffffffffu, bin, leader);
+        const bool mine = bin == b;
+        u64 v = mine ? mass : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((int)(threadIdx.x & 31) == leader) atomicAdd(&hist[b], v);
+        todo &= ~__ballot_sync(0xffffffffu, mine);
+    }
+}
+
+// Walks the 256 bins from the highest down with a running sum that starts at `base`, and returns the first bin at
+// which the sum, this bin included, reaches `limit` (strict: exceeds it); bin 0 if none does.  *above = base + the bins
+// above the one returned.  One warp calls it: a lane owns 8 bins, the lanes' sums are scanned by shuffles.
+__device__ __forceinline__ int pick_digit(const u64* hist, u64 base, u64 limit, bool strict, u64* above) {
+    const int lane = threadIdx.x & 31;
+    u64 h[8], t = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { h[j] = hist[255 - 8 * lane - j]; t += h[j]; }
+    u64 incl = t;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const u64 up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    u64 cum = base + incl - t, at = 0;
+    int hit = -1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const u64 next = cum + h[j];
+        if (hit < 0 && (strict ? next > limit : next >= limit)) { hit = 255 - 8 * lane - j; at = cum; }
+        cum = next;
+    }
+    const unsigned found = __ballot_sync(0xffffffffu, hit >= 0);
+    const u64 total = __shfl_sync(0xffffffffu, incl, 31);
+    if (!found) { *above = base + total - hist[0]; return 0; }
+    const int src = __ffs(found) - 1;
+    *above = __shfl_sync(0xffffffffu, at, src);
+    return __shfl_sync(0xffffffffu, hit, src);
+}
+
+// ---- exchange between the CTAs that share a row (a thread-block cluster of C CTAs; C = 1: one CTA, no cluster)
+__device__ __forceinline__ unsigned cluster_ctarank() { unsigned r; asm("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+template <typename T>
+__device__ __forceinline__ void put_remote(T* local, unsigned rank, T v) {     // *local of CTA `rank` of the cluster = v
+    unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    if (sizeof(T) == 8) asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote), "l"(*reinterpret_cast<u64*>(&v)) : "memory");
+    else asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(*reinterpret_cast<unsigned*>(&v)) : "memory");
+}
+// Every CTA of the cluster hands in `n` values (thread t < n hands in v); afterwards buf[k * n + t] holds CTA k's
+// value t in every CTA.  The caller alternates between two buffers from one exchange to the next: a CTA can be at
+// most one exchange ahead of another, so a buffer is not written again while a slower CTA still reads it.
+template <int C, typename T>
+__device__ __forceinline__ void all_gather(T* buf, int n, T v, unsigned rank) {
+    if (C == 1) {
+        if ((int)threadIdx.x < n) buf[threadIdx.x] = v;
+        __syncthreads();
+    } else {
+        if ((int)threadIdx.x < n) {
+#pragma unroll
+            for (int k = 0; k < C; ++k) put_remote(buf + (int)rank * n + threadIdx.x, (unsigned)k, v);
+        }
+        cluster_sync_all();
+    }
+}
+
+// One row of logits is shared by C CTAs: CTA `rank` owns tokens [v0, v1) and keeps them (divided by the temperature)
+// in its shared memory after the first pass, so the later passes do not go back to global memory; a slice too long
+// for that (staged == 0) is read from global memory every time.  Maxima, histograms and sums of the slices are
+// exchanged through distributed shared memory; every CTA then takes the same decisions from the same integers.
+template <int C>
 __global__ void __launch_bounds__(THREADS)
-sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ slot_ids, int* __restrict__ state,
+sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __restrict__ slot_ids, int* __restrict__ state,
               int* __restrict__ out, float* __restrict__ probs_out, int staged) {
     extern __shared__ __align__(16) float s_row[];
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ u64 s_u64[32];
     __shared__ u64 s_hist[256];
+    __shared__ u64 x_hist[2][C * 256];                               // exchange buffers, by exchange parity
+    __shared__ u64 x_u64[2][C];
+    __shared__ float x_val[C];
+    __shared__ int x_idx[C];
     __shared__ unsigned s_prefix;
     __shared__ u64 s_acc;
     __shared__ int s_found;
     __shared__ u64 s_warp[THREADS / 32];
 
     TTIE_PDL_ENTRY();
-    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float* row = logits + (size_t)r * V;
-    if (slot_ids[r] < 0) {                                            // a padding row of a fixed-size batch: no request, no draw
-        if (tid == 0) out[r] = 0;
-        return;
+    const unsigned rank = C == 1 ? 0u : cluster_ctarank();
+    const int r = blockIdx.x / C, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int v0 = min(V, (int)rank * slice), n = min(V, v0 + slice) - v0;     // this CTA's tokens: v0 .. v0 + n - 1
+    const float* row = logits + (size_t)r * V + v0;
+    const int slot = slot_ids[r];
+    if (slot < 0) {                                                   // a padding row of a fixed-size batch: no request, no draw
+        if (tid == 0 && rank == 0) out[r] = 0;
+        return;                                                       // (the same for every CTA of the cluster)
     }
-    int* st = state + (size_t)slot_ids[r] * 8;
+    // "I have started": nobody writes into a peer's shared memory before that peer is known to run (the wait stands
+    // before the first exchange, with the first pass over the slice in between)
+    if (C > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    int* st = state + (size_t)slot * 8;
     const unsigned seed_lo = (unsigned)st[0], seed_hi = (unsigned)st[1], draws = (unsigned)st[2];
     const int top_k = st[3];
     const float temperature = __int_as_float(st[4]), top_p = __int_as_float(st[5]);
     const int greedy = st[6];
+    int xq = 0;                                                       // exchanges so far (their parity picks the buffer)
 
-    // 1. maximum and the lowest index that holds it (and the row into shared memory)
+    // 1. maximum and the lowest index that holds it (and the slice into shared memory)
     float best = -INFINITY; int best_i = 0x7fffffff;
-    if (staged && (V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
-        for (int i = tid * 4; i < V; i += THREADS * 4) {
+    if (staged && (n & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        for (int i = tid * 4; i < n; i += THREADS * 4) {
             const float4 x = *reinterpret_cast<const float4*>(row + i);
             *reinterpret_cast<float4*>(s_row + i) = x;
             const float xs[4] = {x.x, x.y, x.z, x.w};
@@ -101,7 +196,7 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
                 if (xs[k] > best || (xs[k] == best && i + k < best_i)) { best = xs[k]; best_i = i + k; }
         }
     } else {
-        for (int i = tid; i < V; i += THREADS) {
+        for (int i = tid; i < n; i += THREADS) {
             const float x = row[i];
             if (staged) s_row[i] = x;
             if (x > best || (x == best && i < best_i)) { best = x; best_i = i; }
@@ -123,22 +218,55 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
             const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
             if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
         }
-        if (lane == 0) { s_val[0] = best; s_idx[0] = best_i; }
+        if (lane == 0) { s_val[0] = best; s_idx[0] = best_i == 0x7fffffff ? 0x7fffffff : best_i + v0; }
     }
     __syncthreads();
-    best = s_val[0]; best_i = s_idx[0];
+    if (C > 1) {                                                      // the slices' maxima, in rank order: lower tokens win ties
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+        all_gather<C, float>(x_val, 1, s_val[0], rank);
+        all_gather<C, int>(x_idx, 1, s_idx[0], rank);
+        best = -INFINITY; best_i = 0x7fffffff;
+#pragma unroll
+        for (int k = 0; k < C; ++k)
+            if (x_val[k] > best || (x_val[k] == best && x_idx[k] < best_i)) { best = x_val[k]; best_i = x_idx[k]; }
+    } else {
+        best = s_val[0]; best_i = s_idx[0];
+    }
     if (best_i == 0x7fffffff) best_i = 0;                            // a row of NaNs: report token 0
     if (greedy) {
-        if (tid == 0) { out[r] = best_i; st[2] = (int)(draws + 1); }
-        if (probs_out) for (int i = tid; i < V; i += THREADS) probs_out[(size_t)r * V + i] = (i == best_i) ? 1.f : 0.f;
+        if (tid == 0 && rank == 0) { out[r] = best_i; st[2] = (int)(draws + 1); }
+        if (probs_out) for (int i = tid; i < n; i += THREADS) probs_out[(size_t)r * V + v0 + i] = (v0 + i == best_i) ? 1.f : 0.f;
         return;
     }
     const float ymax = best / temperature;
     if (staged) {
-        for (int i = tid; i < V; i += THREADS) s_row[i] = s_row[i] / temperature;
+        for (int i = tid; i < n; i += THREADS) s_row[i] = s_row[i] / temperature;
         __syncthreads();
     }
     auto Y = [&](int i) -> float { return staged ? s_row[i] : row[i] / temperature; };
+    // the cluster's sum of a histogram of 256 bins that every CTA has filled in s_hist for its slice: into s_hist
+    auto sum_hist = [&]() {
+        if (C > 1) {
+            u64* buf = x_hist[xq & 1]; ++xq;
+            all_gather<C, u64>(buf, 256, tid < 256 ? s_hist[tid] : 0, rank);
+            if (tid < 256) {
+                u64 t = 0;
+#pragma unroll
+                for (int k = 0; k < C; ++k) t += buf[k * 256 + tid];
+                s_hist[tid] = t;
+            }
+        }
+        __syncthreads();
+    };
+    u64 xs_parity = 0;                                                // exchanges of single values so far
+    auto sum_u64 = [&](u64 v, u64* parts) -> u64 {                    // the cluster's sum of a per-CTA value; parts[k]: CTA k's
+        u64* buf = x_u64[xs_parity & 1]; ++xs_parity;
+        all_gather<C, u64>(buf, 1, v, rank);
+        u64 t = 0;
+#pragma unroll
+        for (int k = 0; k < C; ++k) { if (parts) parts[k] = buf[k]; t += buf[k]; }
+        return t;
+    };
 
     // 2. top-k threshold: the k-th largest key, by radix select over 4 digits of 8 bits
     unsigned cut_key = 0;
@@ -147,19 +275,21 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
         for (int shift = 24; shift >= 0; shift -= 8) {
             for (int b = tid; b < 256; b += THREADS) s_hist[b] = 0;
             __syncthreads();
-            for (int i = tid; i < V; i += THREADS) {
-                const unsigned key = ordered_key(Y(i));
-                if (shift == 24 || (key >> (shift + 8)) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], (u64)1);
+            for (int i0 = 0; i0 < n; i0 += THREADS) {                 // (whole warps go round together)
+                const int i = i0 + tid;
+                int bin = -1;
+                if (i < n) {
+                    const unsigned key = ordered_key(Y(i));
+                    if (shift == 24 || (key >> (shift + 8)) == prefix) bin = (int)((key >> shift) & 255u);
+                }
+                hist_add_count(s_hist, bin);
             }
             __syncthreads();
-            if (tid == 0) {
-                u64 cum = 0; int digit = 0;
-                for (int b = 255; b >= 0; --b) {
-                    if (cum + s_hist[b] >= remaining) { digit = b; break; }
-                    cum += s_hist[b];
-                }
-                s_prefix = (prefix << 8) | (unsigned)digit;
-                s_acc = remaining - cum;
+            sum_hist();
+            if (warp == 0) {
+                u64 above;
+                const int digit = pick_digit(s_hist, 0, remaining, false, &above);
+                if (lane == 0) { s_prefix = (prefix << 8) | (unsigned)digit; s_acc = remaining - above; }
             }
             __syncthreads();
             prefix = s_prefix; remaining = s_acc;
@@ -171,31 +301,34 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     // 3. top-p threshold: the smallest key whose strictly-larger keys hold mass <= top_p * total
     if (top_p < 1.0f) {
         u64 z = 0;
-        for (int i = tid; i < V; i += THREADS) {
+        for (int i = tid; i < n; i += THREADS) {
             const float y = Y(i);
             if (ordered_key(y) >= cut_key) z += mass_of(y, ymax);
         }
         z = block_sum_u64(z, s_u64);
+        if (C > 1) z = sum_u64(z, nullptr);
         const u64 limit = (u64)((double)top_p * (double)z);
         unsigned prefix = 0; u64 acc = 0;
         for (int shift = 24; shift >= 0; shift -= 8) {
             for (int b = tid; b < 256; b += THREADS) s_hist[b] = 0;
             __syncthreads();
-            for (int i = tid; i < V; i += THREADS) {
-                const float y = Y(i);
-                const unsigned key = ordered_key(y);
-                if (key >= cut_key && (shift == 24 || (key >> (shift + 8)) == prefix))
-                    atomicAdd(&s_hist[(key >> shift) & 255u], mass_of(y, ymax));
+            for (int i0 = 0; i0 < n; i0 += THREADS) {
+                const int i = i0 + tid;
+                int bin = -1;
+                u64 m = 0;
+                if (i < n) {
+                    const float y = Y(i);
+                    const unsigned key = ordered_key(y);
+                    if (key >= cut_key && (shift == 24 || (key >> (shift + 8)) == prefix)) { bin = (int)((key >> shift) & 255u); m = mass_of(y, ymax); }
+                }
+                hist_add_mass(s_hist, bin, m);
             }
             __syncthreads();
-            if (tid == 0) {
-                int digit = 0; u64 a = acc;
-                for (int b = 255; b >= 0; --b) {
-                    if (a + s_hist[b] > limit || b == 0) { digit = b; break; }   // the cut lies inside this digit
-                    a += s_hist[b];                                              // (digit 0 if nothing is cut)
-                }
-                s_prefix = (prefix << 8) | (unsigned)digit;
-                s_acc = a;
+            sum_hist();
+            if (warp == 0) {                                                   // the cut lies inside the digit picked
+                u64 a;                                                         // (digit 0 if nothing is cut)
+                const int digit = pick_digit(s_hist, acc, limit, true, &a);
+                if (lane == 0) { s_prefix = (prefix << 8) | (unsigned)digit; s_acc = a; }
             }
             __syncthreads();
             prefix = s_prefix; acc = s_acc;
@@ -204,21 +337,34 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
         if (prefix > cut_key) cut_key = prefix;
     }
 
-    // 4. draw: inverse CDF in index order over the kept tokens.  A thread owns a run of consecutive tokens (an odd
-    // number of them, so the threads of a warp read different banks of the staged row).
-    const int chunk = ((V + THREADS - 1) / THREADS) | 1;
-    const int i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
+    // 4. draw: inverse CDF in index order over the kept tokens.  A thread owns a run of consecutive tokens of the
+    // slice (an odd number of them, so the threads of a warp read different banks of the staged row); a slice that
+    // is not staged is walked by warps instead, 32 consecutive tokens at a time, so its loads coalesce.
+    const bool by_thread = staged != 0;
+    const int chunk = by_thread ? (((n + THREADS - 1) / THREADS) | 1) : ((((n + THREADS / 32 - 1) / (THREADS / 32)) + 31) & ~31);
+    const int i0 = min(n, (by_thread ? tid : warp) * chunk), i1 = min(n, i0 + chunk);
     u64 local = 0;
-    for (int i = i0; i < i1; ++i) {
-        const float y = Y(i);
-        if (ordered_key(y) >= cut_key) local += mass_of(y, ymax);
-    }
-    // inclusive scan of the threads' sums: inside each warp by shuffles, then over the warps' totals (integers: exact)
-    u64 incl = local;
+    if (by_thread) {
+        for (int i = i0; i < i1; ++i) {
+            const float y = Y(i);
+            if (ordered_key(y) >= cut_key) local += mass_of(y, ymax);
+        }
+    } else {
+        for (int i = i0 + lane; i < i1; i += 32) {
+            const float y = Y(i);
+            if (ordered_key(y) >= cut_key) local += mass_of(y, ymax);
+        }
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const u64 up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);     // the warp's run: every lane holds its sum
+    }
+    // inclusive scan of the runs' sums: inside each warp by shuffles, then over the warps' totals (integers: exact)
+    u64 incl = local;
+    if (by_thread) {
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const u64 up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
     }
     if (lane == 31) s_warp[warp] = incl;
     __syncthreads();
@@ -233,48 +379,105 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
     }
     __syncthreads();
     incl += warp ? s_warp[warp - 1] : 0;
-    const u64 total = s_warp[THREADS / 32 - 1];
+    const u64 mine = s_warp[THREADS / 32 - 1];                        // kept mass of this CTA's slice
+    u64 parts[C];
+    const u64 total = C > 1 ? sum_u64(mine, parts) : mine;
+    u64 below = 0;                                                    // kept mass of the slices before this one
+#pragma unroll
+    for (int k = 0; k < C; ++k) if (C > 1 && k < (int)rank) below += parts[k];
     unsigned rnd[4];
     philox4x32_10(draws, 0u, 0u, 0u, seed_lo, seed_hi, rnd);
     const double u = (double)(rnd[0] >> 8) * (1.0 / 16777216.0);
     u64 target = (u64)(u * (double)total);
-    if (target >= total) target = total ? total - 1 : 0;
-    if (tid == 0) s_found = best_i;                                   // total == 0 cannot happen (the maximum has mass 2^40)
+    if (target >= total) target = total ? total - 1 : 0;             // total == 0 cannot happen (the maximum has mass 2^40)
+    const bool here = target >= below && target < below + mine;       // exactly one CTA holds the target
+    if (tid == 0) s_found = -1;
     __syncthreads();
-    const u64 before = incl - local;
-    if (local > 0 && target >= before && target < before + local) {
-        u64 c = before;
-        for (int i = i0; i < i1; ++i) {
-            const float y = Y(i);
-            if (ordered_key(y) >= cut_key) {
-                c += mass_of(y, ymax);
-                if (target < c) { s_found = i; break; }
+    const u64 before = below + incl - local;
+    if (here && local > 0 && target >= before && target < before + local) {
+        if (by_thread) {
+            u64 c = before;
+            for (int i = i0; i < i1; ++i) {
+                const float y = Y(i);
+                if (ordered_key(y) >= cut_key) {
+                    c += mass_of(y, ymax);
+                    if (target < c) { s_found = v0 + i; break; }
+                }
+            }
+        } else {
+            // the warp walks its run again, 32 tokens at a time, with a scan over the lanes
+            u64 c = before;
+            for (int i = i0; i < i1; i += 32) {
+                const int j = i + lane;
+                u64 m = 0;
+                if (j < i1) { const float y = Y(j); if (ordered_key(y) >= cut_key) m = mass_of(y, ymax); }
+                u64 sc = m;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const u64 up = __shfl_up_sync(0xffffffffu, sc, o);
+                    if (lane >= o) sc += up;
+                }
+                const bool hit = m > 0 && target >= c + sc - m && target < c + sc;
+                const unsigned where = __ballot_sync(0xffffffffu, hit);
+                if (where) { if (hit) s_found = v0 + j; break; }
+                c += __shfl_sync(0xffffffffu, sc, 31);
             }
         }
     }
     __syncthreads();
-    if (tid == 0) { out[r] = s_found; st[2] = (int)(draws + 1); }
+    if (tid == 0) {
+        if (here) out[r] = s_found >= 0 ? s_found : best_i;
+        if (rank == 0) st[2] = (int)(draws + 1);
+    }
     if (probs_out) {
         const double inv = total ? 1.0 / (double)total : 0.0;
-        for (int i = tid; i < V; i += THREADS) {
+        for (int i = tid; i < n; i += THREADS) {
             const float y = Y(i);
-            probs_out[(size_t)r * V + i] = ordered_key(y) >= cut_key ? (float)((double)mass_of(y, ymax) * inv) : 0.f;
+            probs_out[(size_t)r * V + v0 + i] = ordered_key(y) >= cut_key ? (float)((double)mass_of(y, ymax) * inv) : 0.f;
         }
     }
 }
+
+constexpr int STAGE_FLOATS = 40 * 1024;                              // 160 KB of a slice in shared memory, beside the exchange buffers
+
+template <int C>
+int launch(const float* logits, int R, int V, const int* slot_ids, int* state, int* out, float* probs_out, cudaStream_t s) {
+    int slice = (V + C - 1) / C;
+    slice = (slice + 3) & ~3;                                         // slices start on 16-byte boundaries of a row that does
+    const int staged = slice <= STAGE_FLOATS;
+    const size_t smem = staged ? (size_t)slice * sizeof(float) : 0;
+    auto k = sample_kernel<C>;
+    static bool allowed = false;
+    if (!allowed) {
+        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, STAGE_FLOATS * 4) != cudaSuccess)
+            TTIE_FAIL("sample: %d bytes of shared memory refused", STAGE_FLOATS * 4);
+        allowed = true;
+    }
+    if (C == 1) TTIE_LAUNCH(k, R, THREADS, smem, s, logits, V, slice, slot_ids, state, out, probs_out, staged);
+    else TTIE_LAUNCH_CLUSTER(k, R * C, THREADS, smem, s, dim3(C, 1, 1), logits, V, slice, slot_ids, state, out, probs_out, staged);
+    TTIE_CHECK_LAUNCH("sample");
+    return 0;
+}
 }  // namespace
+
+// ctas_per_row: 0 = chosen from the vocabulary (slices of about 8,192 tokens, at most 8 CTAs: a cluster), else 1, 2, 4 or 8.
+extern "C" int ttie_sample_tuned(const float* logits, int R, int V, const int* slot_ids, int* state, int* out,
+                                 float* probs_out, int ctas_per_row, void* stream) {
+    if (R <= 0) return 0;
+    if (V <= 0) TTIE_FAIL("sample: empty vocabulary");
+    int C = ctas_per_row;
+    if (C == 0) C = V <= 8192 ? 1 : V <= 16384 ? 2 : V <= 32768 ? 4 : 8;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (C) {
+        case 1: return launch<1>(logits, R, V, slot_ids, state, out, probs_out, s);
+        case 2: return launch<2>(logits, R, V, slot_ids, state, out, probs_out, s);
+        case 4: return launch<4>(logits, R, V, slot_ids, state, out, probs_out, s);
+        case 8: return launch<8>(logits, R, V, slot_ids, state, out, probs_out, s);
+    }
+    TTIE_FAIL("sample: %d CTAs per row (1, 2, 4 or 8)", C);
+}
 
 extern "C" int ttie_sample(const float* logits, int R, int V, const int* slot_ids, int* state, int* out,
                            float* probs_out, void* stream) {
-    if (R <= 0) return 0;
-    if (V <= 0) TTIE_FAIL("sample: empty vocabulary");
-    // the row in shared memory when it fits beside the kernel's own (200 KB: 51,200 tokens)
-    const size_t smem = (size_t)V * sizeof(float);
-    const int staged = smem <= 200 * 1024;
-    if (staged && smem > 40 * 1024 &&
-        cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
-        TTIE_FAIL("sample: 200 KB of shared memory refused");
-    TTIE_LAUNCH(sample_kernel, R, THREADS, staged ? smem : 0, (cudaStream_t)stream, logits, V, slot_ids, state, out, probs_out, staged);
-    TTIE_CHECK_LAUNCH("sample");
-    return 0;
+    return ttie_sample_tuned(logits, R, V, slot_ids, state, out, probs_out, 0, stream);
 }

@@ -53,6 +53,7 @@ _SIGNATURES = {
                                 _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_sample": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void],
+    "ttie_sample_tuned": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void],
 }
 
 
@@ -461,10 +462,11 @@ class CudaOps:
                 self._dt(qkv), self._stream(qkv)), "paged_attention")
         self.launches += 2 if num_splits > 1 else 1
 
-    def sample(self, logits, slot_ids, state, out, probs_out=None):
+    def sample(self, logits, slot_ids, state, out, probs_out=None, ctas_per_row=0):
+        """``ctas_per_row``: 0 = chosen from the vocabulary's size; 1, 2, 4 or 8 CTAs (a cluster) share a row."""
         R, V = logits.shape
-        self._check(self.lib.ttie_sample(_ptr(logits), R, V, _ptr(slot_ids), _ptr(state), _ptr(out), _ptr(probs_out),
-                                         self._stream(logits)), "sample")
+        self._check(self.lib.ttie_sample_tuned(_ptr(logits), R, V, _ptr(slot_ids), _ptr(state), _ptr(out), _ptr(probs_out),
+                                               int(ctas_per_row), self._stream(logits)), "sample")
         self.launches += 1
 
 

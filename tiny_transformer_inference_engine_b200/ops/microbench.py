@@ -122,6 +122,9 @@ def decode(ops, a):
     st[:, 5] = 0x3f800000
     tok = torch.empty(B, dtype=torch.int32, device=DEV)
     line("sampling (temperature)", timeit(lambda i: ops.sample(logits, tseq, st, tok)), bytes_=B * V * 4)
+    st[:, 3] = 32
+    st[:, 5] = 0x3f666666                                     # top-k 32, top-p 0.9
+    line("sampling (temperature, top-k 32, top-p 0.9)", timeit(lambda i: ops.sample(logits, tseq, st, tok)), bytes_=B * V * 4)
 
 
 def prefill(ops, a):
