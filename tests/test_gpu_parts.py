@@ -110,6 +110,8 @@ class ToyDecayMixer(Mixer):
     a step of single tokens advances every request at once on the device (so a decode step can be
     captured: the padding rows of a captured step carry slot -1, which indexes the scratch row)."""
 
+    capturable = "decode"              # a portion is advanced on the host: only steps of single tokens can be captured
+
     def __init__(self, prefix, dim, decay):
         super().__init__(prefix)
         self.dim, self.decay = dim, decay
@@ -296,7 +298,7 @@ def test_toy_architecture_generates_from_captured_graphs(toy_registered, pipelin
                       cache=CacheConfig(block_size=8, num_gpu_blocks=64),
                       sched=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=32, cudagraph_batch_sizes=[1, 2, 4]))
     eng = Engine(mc, w, ec)
-    assert eng.model.capturable
+    assert eng.model.capturable == "decode" and not eng.stepper.capture_repeated
     new = [40, 26, 33]                                                # requests end at different steps: the batch bucket changes
     out = eng.generate(prompts, [SamplingParams(max_new_tokens=n, greedy=True) for n in new])
     assert eng.stepper.counters["graph_replays"] > 20 and len(eng.stepper._graphs) >= 2

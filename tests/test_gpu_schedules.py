@@ -237,3 +237,35 @@ def test_sizes_the_kernels_do_not_take_are_refused_at_construction():
     finally:
         weights.loader.place = inner
     assert not calls                                                   # refused before any weight was looked at
+
+
+# ------------------------------------------------------------------------------------------ repeated step layouts
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_step_layouts_are_replayed_from_graphs(dtype):
+    """A long prompt fed in equal portions beside two decoding requests: from its second occurrence on, the step's
+    layout is captured and replayed.  Logits at every wanted place against the plain model; the requests' lengths,
+    pages and tokens differ from replay to replay, a page edge and a context bucket are crossed on the way."""
+    cfg = dict(architecture="mqa_gpt", vocab_size=211, d_model=256, num_layers=2, num_heads=2, num_kv_heads=1,
+               hidden_size=320, max_seq_len=2600, rope_theta=10000.0, rms_norm_eps=1e-5, bias=False, dtype="float32")
+    eng, w = make_engine(cfg, 13, 16, 260, dtype, max_seqs=4, budget=64, graphs=True, cudagraph_batch_sizes=[1, 2, 4])
+    assert eng.stepper.capture_repeated
+    g = torch.Generator().manual_seed(6)
+    a = torch.randint(0, 211, (2400,), generator=g).tolist()
+    b = torch.randint(0, 211, (60,), generator=g).tolist()
+    c = torch.randint(0, 211, (45,), generator=g).tolist()
+    steps = [{"entries": [{"id": "b", "tokens": b[:20], "want": [19]}, {"id": "c", "tokens": c[:5], "want": [4]}], "end": []}]
+    for i in range(40):                                              # portions of 48 tokens of a: contexts 48 .. 1920, beside one token of b and of c
+        steps.append({"entries": [{"id": "a", "tokens": a[48 * i:48 * (i + 1)], "want": [0, 47]},
+                                  {"id": "b", "tokens": b[20 + i:21 + i], "want": [0]},
+                                  {"id": "c", "tokens": c[5 + i:6 + i], "want": [0]}],
+                      "end": (["b", "c"] if i == 39 else [])})
+    for i in range(10):                                              # then a alone in the same portions, across the 2,048-key bucket
+        steps.append({"entries": [{"id": "a", "tokens": a[1920 + 48 * i:1920 + 48 * (i + 1)], "want": [47]}], "end": ["a"] if i == 9 else []})
+    got = tu.run_steps(eng, steps)
+    st = eng.stepper.counters
+    assert st["step_graphs_captured"] == 3 and st["step_graph_replays"] == 38 + 0 + 6, st     # (a's portions alone: two context buckets, met 2 and 8 times)
+    exp = {"a": plain_forward(cfg, w, a), "b": plain_forward(cfg, w, b), "c": plain_forward(cfg, w, c)}
+    bad = tu.first_wrong(got, exp, TOL[dtype])
+    assert bad is None, f"first wrong place {bad}"
+    # no more graphs are kept than allowed, and a layout that never comes again is never captured
+    assert len(eng.stepper._step_graphs) <= eng.stepper.max_step_graphs

@@ -77,7 +77,9 @@ class Engine:
             raise ValueError("a cache group holds no usable page")
         # a part that reads device values on the host keeps the whole model off the captured path
         graphs = ec.sched.cudagraph_batch_sizes if (ec.use_cuda_graphs and self.device.type == "cuda" and self.model.capturable) else []
-        self.stepper = Stepper(self.model, self.manager, ops, self.dtype, self.device, graphs)
+        self.stepper = Stepper(self.model, self.manager, ops, self.dtype, self.device, graphs,
+                               capture_repeated=bool(graphs) and ec.capture_repeated_steps and self.model.capturable is True,
+                               step_graph_max_tokens=ec.step_graph_max_tokens, max_step_graphs=ec.max_step_graphs)
         self.sampler = Sampler(ops, ec.sched.max_num_seqs, config.vocab_size, self.device)
         self._slot_ids = None
         self._inflight: Optional[_Pending] = None

@@ -12,9 +12,17 @@ CUDA graph per batch-size bucket and context-length bucket: the metadata buffer 
 address and layout, so a replay needs only the one host-to-device copy.  The kernels of a
 graph are planned for the longest context of its bucket (512, 2048, 8192, ... keys, at most
 the model's ``max_seq_len``), so short contexts do not run kernels cut for long ones.
+
+Any other step whose layout comes again - the same numbers of tokens per request in the
+same order, the same wanted places, the same context buckets, as in a prompt that is fed in
+equal portions beside a steady set of decoding requests - is captured the second time it is
+seen and replayed from then on: a step of a few hundred tokens on a small model is otherwise
+bound by the host's launches, not by the GPU.  A few such graphs are kept (least recently
+used goes); long steps are left alone.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Dict, List, Optional
 
 import torch
@@ -33,13 +41,19 @@ class _DecodeGraph:
 
 class Stepper:
     def __init__(self, model: Model, manager: CacheManager, ops, dtype: torch.dtype, device,
-                 graph_batch_sizes: Optional[List[int]] = None):
+                 graph_batch_sizes: Optional[List[int]] = None, capture_repeated: bool = False,
+                 step_graph_max_tokens: int = 1024, max_step_graphs: int = 64):
         self.model, self.manager, self.ops, self.dtype = model, manager, ops, dtype
         self.device = torch.device(device)
         self.packer = BatchPacker(manager, ops, dtype, device, model.spec.vocab_size, model.spec.max_seq_len)
         self.graph_batch_sizes = sorted(graph_batch_sizes or [])
         self._graphs: Dict[tuple, _DecodeGraph] = {}
-        self.counters = {"steps": 0, "tokens": 0, "graph_replays": 0}
+        self.capture_repeated = bool(capture_repeated)
+        self.step_graph_max_tokens, self.max_step_graphs = int(step_graph_max_tokens), int(max_step_graphs)
+        self._step_graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()      # repeated layouts, least recently used first
+        self._seen: Dict[tuple, int] = {}                                          # layouts met once and not captured yet
+        self._step_pool = None                                                     # memory pool the graphs of repeated layouts share
+        self.counters = {"steps": 0, "tokens": 0, "graph_replays": 0, "step_graph_replays": 0, "step_graphs_captured": 0}
         self.last_tokens: Optional[torch.Tensor] = None      # tokens sampled inside the last step's graph, or None
 
     # ---------------------------------------------------------------- plain step
@@ -61,9 +75,74 @@ class Stepper:
                 return self._step_graph(entries, bucket, sampler, feed)
         if feed is not None:
             raise ValueError("tokens can be fed on the device only into a captured decode step")
+        if self.capture_repeated and sum(len(e.tokens) for e in entries) <= self.step_graph_max_tokens:
+            logits = self._step_repeated(entries)
+            if logits is not None:
+                return logits
         ctx = self.packer.pack(entries)
         views = self.manager.views(ctx.block_tables)
         return self.model.forward(ctx, views)
+
+    # ---------------------------------------------------------------- repeated layouts
+    def _bucket(self, keys: int) -> int:
+        limit, b = self.model.spec.max_seq_len, 2048                 # coarse: every bucket is a layout of its own
+        while b < keys and b < limit:
+            b *= 4
+        return min(b, limit)
+
+    def _step_repeated(self, entries) -> Optional[torch.Tensor]:
+        """Replays the graph of this step's layout if there is one, captures one if the layout was seen before
+        (running the step eagerly for its results first), else notes the layout and returns None."""
+        single = [e for e in entries if len(e.tokens) == 1]
+        others = [e for e in entries if len(e.tokens) != 1]
+        buckets = tuple(self._bucket(max(e.start + len(e.tokens) for e in cls)) if cls else 0 for cls in (single, others))
+        key = (tuple((len(e.tokens), tuple(e.want)) for e in entries), buckets)
+        pages = self._fixed_pages()
+        g = self._step_graphs.get(key)
+        if g is not None:
+            self._step_graphs.move_to_end(key)
+            self.packer.pack(entries, pages_per_seq=pages, buffers=(g.host, g.dev), copy_only=True)
+            g.graph.replay()
+            if hasattr(self.ops, "launches"):
+                self.ops.launches += g.launches
+            self.counters["step_graph_replays"] += 1
+            return g.logits
+        if key not in self._seen:
+            if len(self._seen) > 4096:
+                self._seen.clear()
+            self._seen[key] = 1
+            return None
+        del self._seen[key]
+        n, T = len(entries), sum(len(e.tokens) for e in entries)
+        words = 4 * (T + 4) + 5 * (n + 5) + sum(len(e.want) for e in entries) + sum(n * w + 4 for w in pages.values()) + 64
+        host = torch.empty(words, dtype=torch.int32, pin_memory=True)
+        dev = torch.zeros(words, dtype=torch.int32, device=self.device)
+        ctx = self.packer.pack(entries, pages_per_seq=pages, buffers=(host, dev))
+        # the captured kernels must cover every context length of the buckets: size them for the longest
+        classes = ctx.seq_classes or []
+        if classes:
+            for c, b in zip(classes, buckets):
+                c.max_kv_len = b
+        ctx.max_kv_len = max(buckets)
+        views = self.manager.views(ctx.block_tables)
+        # this step runs eagerly, planned as the graph will be: its results are the step's, and every kernel the
+        # graph holds has run once before the capture (a kernel's first launch may load code, which a capture forbids)
+        logits = self.model.forward(ctx, views)
+        torch.cuda.synchronize(self.device)
+        ctx.step_cache.clear()
+        graph = torch.cuda.CUDAGraph()
+        before = getattr(self.ops, "launches", 0)
+        # the graphs of repeated layouts share one memory pool: one of them runs at a time, and a step's logits are
+        # read (by the sampler, or copied out) before the next step starts, as with two replays of one graph
+        if self._step_pool is None:
+            self._step_pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(graph, pool=self._step_pool):
+            g_logits = self.model.forward(ctx, views)
+        while len(self._step_graphs) >= self.max_step_graphs:
+            self._step_graphs.popitem(last=False)
+        self._step_graphs[key] = _DecodeGraph(0, host, dev, graph, g_logits, None, ctx, getattr(self.ops, "launches", 0) - before)
+        self.counters["step_graphs_captured"] += 1
+        return logits
 
     @staticmethod
     def _is_decode(entries) -> bool:

@@ -66,6 +66,9 @@ class Model:
             owners[id(part)] = part
         for pid, params in per_part.items():
             owners[pid].load(params)
+        tune = getattr(getattr(self, "ops", None), "tune_products", None)
+        if tune is not None:                                       # the kernel library may measure which product suits each shape
+            tune([w for p in self.parts() for w in p.product_weights() if w is not None])
 
     # ---------------------------------------------------------------- cache
     def cache_needs(self) -> List[List[object]]:
@@ -75,9 +78,13 @@ class Model:
                 for entry in self.run_order]
 
     @property
-    def capturable(self) -> bool:
-        """False if any part says its step cannot run inside a captured CUDA graph."""
-        return all(p.capturable for p in self.parts())
+    def capturable(self):
+        """What of this model's steps can run inside a captured CUDA graph: True (any step), "decode" (steps of
+        single tokens only) or False - the least that any part allows."""
+        kinds = [p.capturable for p in self.parts()]
+        if not all(kinds):
+            return False
+        return True if all(k is True for k in kinds) else "decode"
 
     def validate(self, ops, dtype: torch.dtype, page_size: int) -> None:
         """Asks every part whether its kernels take its sizes (raises with the part's message if not)."""

@@ -61,6 +61,10 @@ class KernelError(RuntimeError):
     pass
 
 
+def _row_bucket(M: int) -> int:
+    return 16 if M <= 16 else 32 if M <= 32 else 64
+
+
 def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
@@ -96,7 +100,9 @@ class CudaOps:
         self.attn_tc_min_split = 256            # keys per CTA from which the tcgen05 kernel splits a decode step's key range
         self.attn_tcpp_min_split = 1024         # keys per CTA below which a prompt portion's key range is not cut
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
-        self.skinny_max_rows = 8                # rows up to which the weight-streaming product replaces the library's
+        self.skinny_max_rows = 8                # rows up to which the weight-streaming product always replaces the library's
+        self._product_choice = {}               # (N, K, row bucket) -> "skinny" | "library" for 9..64 rows (tune_products)
+        self.product_timings = {}               # what tune_products measured: (N, K, rows) -> {"library": ms, "skinny": ms}
         self.lib.ttie_attn_tc_supported.restype = _c_int
         self._tc_pinned = torch.zeros(2, dtype=torch.int32).pin_memory()       # failure codes of the tcgen05 kernels, written by the device
         self._tc_words = self._tc_pinned.numpy()
@@ -181,8 +187,56 @@ class CudaOps:
 
     # ---- matrix products
     def _skinny_ok(self, x, w):
-        return (x.dtype == torch.bfloat16 and x.shape[0] <= self.skinny_max_rows and x.shape[1] % 8 == 0
+        M = x.shape[0]
+        if M > self.skinny_max_rows and not (M <= 64 and self._product_choice.get((w.shape[0], w.shape[1], _row_bucket(M))) == "skinny"):
+            return False
+        return (x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
                 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+    def tune_products(self, weights, iters=8):
+        """For 9 to 64 rows neither this package's weight-streaming product nor the library's wins at every shape
+        (measured at the Llama-2-7B widths the library is ahead by 10-20 %; on a narrow, deep matrix such as
+        [2048, 16384] it leaves half of the memory bandwidth unused).  So each distinct bfloat16 matrix shape of a
+        model is timed once per row bucket (16, 32, 64) with both, as a replayed graph of ``iters`` launches
+        that rotate over the model's matrices of that shape, and the faster one is remembered.  Small matrices
+        (under 4 Mi elements) are left to the library."""
+        groups, launches = {}, self.launches
+        for w in weights:
+            if w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1 and w.shape[0] * w.shape[1] >= (4 << 20):
+                groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
+        for (N, K), ws in groups.items():
+            for M in (16, 32, 64):
+                if (N, K, M) in self._product_choice:
+                    continue
+                x = torch.randn(M, K, device=self.device).to(torch.bfloat16)
+                if not self._skinny_shape_ok(x, ws[0]):
+                    continue
+                took = {}
+                for kind in ("library", "skinny"):
+                    self._product_choice[(N, K, M)] = kind
+                    fn = lambda i: self.linear(x, ws[i % len(ws)], None, partial_ok=True)
+                    for i in range(2):
+                        fn(i)
+                    torch.cuda.synchronize(self.device)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        for i in range(iters):
+                            fn(i)
+                    g.replay()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    g.replay()
+                    b.record()
+                    torch.cuda.synchronize(self.device)
+                    took[kind] = a.elapsed_time(b)
+                    del g
+                self._product_choice[(N, K, M)] = "skinny" if took["skinny"] < 0.97 * took["library"] else "library"
+                self.product_timings[(N, K, M)] = took
+        self.launches = launches
+
+    @staticmethod
+    def _skinny_shape_ok(x, w):
+        return x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
 
     def _kslice(self, N, K, may_split):
         """K range per CTA of the weight-streaming kernel.  K is split over CTAs (partial sums) when the

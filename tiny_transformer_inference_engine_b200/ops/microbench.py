@@ -155,6 +155,8 @@ def prefill(ops, a):
     for plan in dict.fromkeys([planned, ("tcpp", 1, 0), ("tc", 1, 0), ("mma", 1, 0)]):
         if plan[0].startswith("tc") and not ops.lib.ttie_attn_tc_supported(D, page):
             continue
+        if (plan[0] == "tc" and D > 128) or (plan[0] == "mma" and not ops.lib.ttie_attn_mma_supported(D)):
+            continue
         line(f"causal paged attention {plan}", timeit(lambda i: ops.paged_attention(qkv, Hq, Hkv, D, kp, vp, table, page, qsl, sl, 1, T, T, 1 / math.sqrt(D), 0, o, plan=plan), iters=4),
              flops=4 * Hq * D * T * (T + 1) // 2)
     err = ops.tc_error()
@@ -163,11 +165,11 @@ def prefill(ops, a):
 
 
 def prefill_attention(ops, a):
-    """Causal attention over prompt lengths and two head layouts (32 heads of 128, 71 heads of 64, one kv head each;
-    pages of 64 and of 16 keys): the two-tile tcgen05 kernel beside the one-tile one, and a 512-token portion behind a
-    long context with the planned split of the key range."""
+    """Causal attention over prompt lengths and three head layouts (32 heads of 128, 71 heads of 64, 8 heads of 256,
+    one kv head each; pages of 64 and of 16 keys): the two-tile tcgen05 kernel (one tile at head size 256) beside the
+    one-tile one, and a 512-token portion behind a long context with the planned split of the key range."""
     print("== causal attention of one prompt: two-tile tcgen05 kernel | one-tile tcgen05 kernel")
-    for Hq, D, page in ((32, 128, 64), (71, 64, 64), (32, 128, 16)):
+    for Hq, D, page in ((32, 128, 64), (71, 64, 64), (32, 128, 16), (8, 256, 64), (8, 256, 16)):
         for T in (512, 2048, 8192):
             nb = T // page + 2
             kp = torch.randn(nb, 1, page, D, device=DEV).bfloat16()
@@ -177,7 +179,9 @@ def prefill_attention(ops, a):
             qsl = torch.tensor([0, T], dtype=torch.int32, device=DEV)
             sl = torch.tensor([T], dtype=torch.int32, device=DEV)
             o = torch.empty(T, Hq * D, device=DEV, dtype=torch.bfloat16)
-            for plan in (("tcpp", 1, 0), ("tc", 1, 0)):
+            for plan in dict.fromkeys([ops.attention_plan(torch.bfloat16, 1, Hq, 1, D, T, T, page), ("tcpp", 1, 0), ("tc", 1, 0)]):
+                if plan[0] == "tc" and D > 128:
+                    continue                                     # head size 256 has the one form
                 us = timeit(lambda i: ops.paged_attention(qkv, Hq, 1, D, kp, vp, table, page, qsl, sl, 1, T, T, 1 / math.sqrt(D), 0, o, plan=plan), iters=4)
                 line(f"{Hq} heads of {D}, pages of {page}, {T:5d} tokens {plan}", us, flops=4 * Hq * D * T * (T + 1) // 2)
     Hq, D, page, T, ctx = 32, 128, 64, 512, 8192

@@ -70,6 +70,9 @@ class PagedAttention(Mixer):
             self.b_in = torch.cat([params[f"{n[k]}.bias"] for k in keys], dim=0).contiguous()
             self.b_out = params[f"{n['o']}.bias"].contiguous()
 
+    def product_weights(self):
+        return [self.w_in, self.w_out]
+
     def validate(self, ops, dtype, page_size):
         check = getattr(ops, "check_attention", None)
         if check is not None:

@@ -18,7 +18,8 @@ Categories and the methods each must have:
 ``block``     ``cache_needs()``; ``forward(stream, ctx, caches)`` (arrangement of the four above)
 
 Every part may also say ``capturable = False`` (its step reads device values on the host, so it
-cannot run inside a captured CUDA graph: a model with such a part steps without graphs) and
+cannot run inside a captured CUDA graph: a model with such a part steps without graphs) or
+``capturable = "decode"`` (only its steps of single tokens can be captured) and
 override ``validate(ops, dtype, page_size)`` to refuse, when the engine is built, sizes that
 its kernels do not take.
 """
@@ -184,7 +185,7 @@ class ResidualStream:
 class Part:
     """Base of every part: constants in, tensor specs out, tensors loaded by relative name."""
     category = "part"
-    capturable = True                  # False: the part's step cannot be captured in a CUDA graph
+    capturable = True                  # True: any step; "decode": only steps of single tokens; False: none can be captured in a CUDA graph
 
     def __init__(self, prefix: str = ""):
         self.prefix = prefix
@@ -206,6 +207,11 @@ class Part:
         self.ops, self.dtype, self.device = ops, dtype, device
         for c in self.children():
             c.bind(ops, dtype, device)
+
+    def product_weights(self) -> List[torch.Tensor]:
+        """The matrices this part multiplies activations by (after ``load``), for kernel libraries that choose an
+        implementation per matrix shape by measuring."""
+        return []
 
     def validate(self, ops, dtype: torch.dtype, page_size: int) -> None:
         """Raises if the part's sizes, the compute dtype or the page size are something its kernels do not take.

@@ -44,5 +44,8 @@ class LinearHead(Head):
     def load(self, params):
         self.weight = params["weight"].contiguous()
 
+    def product_weights(self):
+        return [self.weight]
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.ops.linear(x, self.weight, None, out_dtype=torch.float32)

@@ -37,6 +37,9 @@ class SwiGLU(FeedForward):
             self.b_gu = torch.cat([params["gate_proj.bias"], params["up_proj.bias"]], dim=0).contiguous()
             self.b_down = params["down_proj.bias"].contiguous()
 
+    def product_weights(self):
+        return [self.w_down]                     # (gate/up beyond 8 rows is the library's product plus the activation kernel)
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = self.ops.linear_swiglu(x, self.w_gu, self.b_gu, self.hidden)        # [T, F]
         return self.ops.linear(act, self.w_down, self.b_down, partial_ok=True)
