@@ -566,6 +566,42 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n):
     assert ops.tc_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (2048, 4352, 4096), (300, 520, 200), (1, 1000, 64), (129, 72, 4544),
+                                   (700, 515 * 8, 176 * 8), (260, 33000, 64), (513, 4096, 11008)])
+def test_gemm_tcgen05_on_cta_pairs(ops, M, N, K):
+    """The product on pairs of CTAs (tcgen05.mma.cta_group::2, 256 x 256 tiles) against float64: tiles that hang over
+    every edge, many tiles per pair (the persistent loop and both accumulator buffers), bias, float32 output, a
+    strided activation."""
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    b = torch.randn(N, generator=g).bfloat16().to(DEV)
+    ref = x.double() @ w.double().T
+    tol32 = 1e-5 * max(1.0, (K / 4096) ** 0.5)                    # 32-bit accumulation over K products
+    assert rel(ops.linear_tc_pair(x, w, None).double(), ref) < 8e-3
+    assert rel(ops.linear_tc_pair(x, w, b, torch.float32).double(), ref + b.double()) < tol32
+    wide = torch.randn(M, K + 64, generator=g).bfloat16().to(DEV)
+    xs = wide[:, 8:8 + K]
+    assert rel(ops.linear_tc_pair(xs, w, None, torch.float32).double(), xs.double() @ w.double().T) < tol32
+    assert ops.tc_error() == 0
+
+
+@pytest.mark.parametrize("M,F,K,bias", [(256, 128, 64, False), (2048, 11008, 4096, False), (300, 176, 200, True), (1, 1000, 64, True),
+                                        (515, 18176, 512, False), (130, 200, 4544, True)])
+def test_gemm_tcgen05_pair_with_swiglu(ops, M, F, K, bias):
+    """The gate/up product with silu(g) * u in its epilogue: the leader's half of the tile holds gate columns, its
+    peer's the matching up columns; widths that are no multiple of the tile, with and without biases."""
+    g = torch.Generator().manual_seed(M + F)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(2 * F, K, generator=g) * 0.05).bfloat16().to(DEV)
+    b = torch.randn(2 * F, generator=g).bfloat16().to(DEV) if bias else None
+    y = x.double() @ w.double().T + (b.double() if bias else 0)
+    ref = torch.nn.functional.silu(y[:, :F]) * y[:, F:]
+    out = ops.linear_swiglu_tc_pair(x, w, b, F)
+    assert out.shape == (M, F) and rel(out.double(), ref) < 8e-3
+    assert ops.tc_error() == 0
+
+
 # ------------------------------------------------------------------------------------------ tcgen05 attention
 TC_SHAPES = [(32, 1, 128, 64), (32, 1, 128, 16), (8, 2, 64, 8), (3, 1, 64, 128), (71, 1, 64, 64), (4, 2, 128, 32), (5, 5, 64, 256)]
 

@@ -286,9 +286,28 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const TcParams& p, cudaSt
 // wait ran out).  Synchronises the device.
 // A word of pinned host memory (device-accessible) that also receives the failure code, so the host can look at it
 // after every step without a call into the runtime.  nullptr: none.
+static int* h_tc_error_mirror = nullptr;                       // host copy of the pointer the device holds
 extern "C" int ttie_gemm_tc_set_mirror(int* host_word) {
+    h_tc_error_mirror = host_word;
     return cudaMemcpyToSymbol(g_tc_error_mirror, &host_word, sizeof(int*)) == cudaSuccess ? 0 : 1;
 }
+
+namespace ttie {
+// For the other product kernels of this library (other files): the device address of the error word, the host mirror's
+// address (or nullptr), and the tensor-map builder.
+int gemm_tc_error_words(int** word, int** mirror) {
+    static int* addr[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!addr[dev] && cudaGetSymbolAddress((void**)&addr[dev], g_tc_error) != cudaSuccess) return -1;
+    *word = addr[dev];
+    *mirror = h_tc_error_mirror;
+    return 0;
+}
+int gemm_tc_make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+    return make_map(map, base, rows, K, ld, box_rows);
+}
+}  // namespace ttie
 
 extern "C" int ttie_tc_error() {
     int v = 0, zero = 0;

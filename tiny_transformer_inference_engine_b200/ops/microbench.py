@@ -45,8 +45,21 @@ def peaks():
     return hbm, tf, src
 
 
+EAGER = False        # --eager: plain launches between two events (what a profiler sees as single kernels), few of them
+
+
 def timeit(fn, iters=24, warm=3):
     """Microseconds per call of ``fn(i)``, measured as one replay of a graph of ``iters`` calls."""
+    if EAGER:
+        fn(0)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(2):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / 2 * 1e3
     for i in range(warm):
         fn(i)
     torch.cuda.synchronize()
@@ -242,6 +255,11 @@ def gemm_tc(ops, a):
         flops = 2 * M * N * K
         line(f"{name} [{M}x{K}]x[{K}x{N}] library (cuBLAS)", timeit(lambda i: torch.mm(x, w.t()), iters=8), flops=flops)
         line(f"{name} [{M}x{K}]x[{K}x{N}] tcgen05 128x256", timeit(lambda i: ops.linear_tc(x, w, None, None, 256), iters=8), flops=flops)
+        line(f"{name} [{M}x{K}]x[{K}x{N}] tcgen05 CTA pairs 256x256", timeit(lambda i: ops.linear_tc_pair(x, w, None), iters=8), flops=flops)
+        if name == "gate_up":
+            act = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+            line(f"{name} library + SwiGLU kernel", timeit(lambda i: ops.swiglu(torch.mm(x, w.t()), act), iters=8), flops=flops)
+            line(f"{name} tcgen05 CTA pairs with SwiGLU epilogue", timeit(lambda i: ops.linear_swiglu_tc_pair(x, w, None, F), iters=8), flops=flops)
     err = ops.tc_error()
     if err:
         raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
@@ -260,8 +278,11 @@ def main(argv=None):
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--attn-batches", default="1,8,64", help="batch sizes of --what attention")
     ap.add_argument("--attn-contexts", default="", help="context lengths of --what attention (default 512, 2048, ctx, 4 ctx)")
+    ap.add_argument("--eager", action="store_true", help="three plain launches per line instead of a replayed graph (for a profiler)")
     ap.add_argument("--skinny-max-rows", type=int, default=None, help="rows up to which the weight-streaming product is used (default: the engine's)")
     a = ap.parse_args(argv)
+    global EAGER
+    EAGER = a.eager
     ops = get_ops(DEV)
     if a.skinny_max_rows is not None:
         ops.skinny_max_rows = a.skinny_max_rows
