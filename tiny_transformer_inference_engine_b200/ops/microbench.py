@@ -1,6 +1,6 @@
 """Per-kernel timings against their rooflines, at the sizes of a model configuration.
 
-    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|prefill_attention|all]
+    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|prefill_attention|tune|all]
                                                                     [--batch 8] [--ctx 4096] [--tokens 2048]
 
 Every kernel is timed alone inside a captured CUDA graph of ``--iters`` launches (so the host's launch
@@ -265,9 +265,26 @@ def gemm_tc(ops, a):
         raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
 
 
+def tune(ops, a):
+    """What ``CudaOps.tune_products`` measures at 16, 32 and 64 rows for the model's matrix shapes: the library's
+    product against this package's weight-streaming kernel (both rotate over several matrices of a shape)."""
+    d, F, V, Hq, Hkv, D = a.d_model, a.hidden, a.vocab, a.heads, a.kv_heads, a.d_model // a.heads
+    print("== products of 16 / 32 / 64 rows, us per launch: library | weight-streaming kernel -> choice")
+    weights = []
+    for N, K in (((Hq + 2 * Hkv) * D, d), (d, Hq * D), (d, F), (V, d)):
+        n = max(2, min(8, int(400e6 // (N * K * 2))))
+        weights += [torch.randn(N, K, device=DEV).bfloat16() * 0.02 for _ in range(n)]
+    ops._product_choice.clear()
+    ops.tune_products(weights)
+    for (N, K, M), took in sorted(ops.product_timings.items(), key=lambda kv: str(kv[0])):
+        if N == "swiglu":
+            continue
+        print(f"[{N}, {K}] {M:3d} rows   {took['library'] * 1000 / 8:7.1f} | {took['skinny'] * 1000 / 8:7.1f}   -> {ops._product_choice[(N, K, M)]}", flush=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "prefill_attention", "all"))
+    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "prefill_attention", "tune", "all"))
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -296,6 +313,8 @@ def main(argv=None):
         attention(ops, a)
     if a.what in ("prefill_attention", "all"):
         prefill_attention(ops, a)
+    if a.what == "tune":
+        tune(ops, a)
     return 0
 
 
