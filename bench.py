@@ -185,7 +185,7 @@ WORKLOADS = {
 }
 
 
-def run_workload(name, pk, layers=None):
+def run_workload(name, pk, layers=None, split_classes=True):
     """One of BASELINE.json's serving workloads through ``Engine.generate`` (host token lists in and out): requests are
     admitted, their prompts cut into portions under the token budget and run beside the decoded tokens of the others.
     Timed by the host's clock around the whole call, after one untimed run of the same workload.  ``frac`` is the sum
@@ -203,7 +203,7 @@ def run_workload(name, pk, layers=None):
     lens = torch.randint(w["prompt_lo"], w["prompt_hi"] + 1, (n_req,), generator=g).tolist()
     prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
     pages = sum(-(-(n + w["new_tokens"]) // page) for n in lens) + 2 * n_req + 2
-    ec = EngineConfig(dtype="bfloat16", device="cuda:0", use_cuda_graphs=True,
+    ec = EngineConfig(dtype="bfloat16", device="cuda:0", use_cuda_graphs=True, split_step_classes=split_classes,
                       cache=CacheConfig(block_size=page, num_gpu_blocks=pages),
                       sched=SchedulerConfig(max_num_seqs=n_req, max_num_batched_tokens=w["token_budget"],
                                             cudagraph_batch_sizes=[1, 2, 4, 8, 16, 32]))
@@ -260,6 +260,7 @@ def main():
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-workloads", action="store_true", help="skip the Falcon-width and Gemma-size serving workloads")
     ap.add_argument("--only-workload", default=None, choices=sorted(WORKLOADS), help="run one serving workload and print its record")
+    ap.add_argument("--no-class-split", action="store_true", help="with --only-workload: mixed steps as one attention launch (the comparison)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -291,7 +292,7 @@ def main():
 
     import torch
     if args.only_workload:
-        print(json.dumps({args.only_workload: run_workload(args.only_workload, peaks(), args.layers)}))
+        print(json.dumps({args.only_workload: run_workload(args.only_workload, peaks(), args.layers, not args.no_class_split)}))
         return 0
     cfg = dict(architecture="mqa_gpt", vocab_size=32000, d_model=4096, num_layers=32, num_heads=32, num_kv_heads=1,
                hidden_size=11008, max_seq_len=4096, rope_theta=10000.0, rms_norm_eps=1e-5, bias=False, dtype="bfloat16")

@@ -57,6 +57,7 @@ class EngineConfig:
     sched: SchedulerConfig = field(default_factory=SchedulerConfig)
     use_cuda_graphs: bool = True
     pipelined_decode: bool = True              # launch the next captured decode step before the host has read this one's tokens
+    split_step_classes: bool = True            # a mixed step's one-token requests and its portions run as two attention launches
     capture_repeated_steps: bool = True        # a step whose layout (tokens per request, wanted places) comes again is captured and replayed
     step_graph_max_tokens: int = 1024          # ... up to this many tokens (longer steps keep the GPU busy without it)
     max_step_graphs: int = 64                  # ... and at most this many such graphs are kept (least recently used goes; they share one memory pool)

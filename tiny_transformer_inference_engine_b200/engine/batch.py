@@ -32,8 +32,9 @@ def _round4(n: int) -> int:
 
 
 class BatchPacker:
-    def __init__(self, manager, ops, dtype: torch.dtype, device, vocab_size: int, max_seq_len: int):
+    def __init__(self, manager, ops, dtype: torch.dtype, device, vocab_size: int, max_seq_len: int, split_classes: bool = True):
         self.manager, self.ops, self.dtype = manager, ops, dtype
+        self.split_classes = bool(split_classes)       # False: a mixed step is one class (every request in the portions' launch)
         self.device = torch.device(device)
         self.vocab_size, self.max_seq_len = vocab_size, max_seq_len
         self._host = None
@@ -172,7 +173,7 @@ class BatchPacker:
         q_lens = [qsl[i + 1] - qsl[i] for i in range(N)]
         T = qsl[-1]
         # a mixed step: the second class's query_start_loc counted from its own first token
-        mixed = 0 < num_single < N_real
+        mixed = self.split_classes and 0 < num_single < N_real
         qsl_tail = [q - num_single for q in qsl[num_single:]] if mixed else []
         R = len(rows)
         tables, widths = [], []

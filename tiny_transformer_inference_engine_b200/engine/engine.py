@@ -79,7 +79,8 @@ class Engine:
         graphs = ec.sched.cudagraph_batch_sizes if (ec.use_cuda_graphs and self.device.type == "cuda" and self.model.capturable) else []
         self.stepper = Stepper(self.model, self.manager, ops, self.dtype, self.device, graphs,
                                capture_repeated=bool(graphs) and ec.capture_repeated_steps and self.model.capturable is True,
-                               step_graph_max_tokens=ec.step_graph_max_tokens, max_step_graphs=ec.max_step_graphs)
+                               step_graph_max_tokens=ec.step_graph_max_tokens, max_step_graphs=ec.max_step_graphs,
+                               split_classes=ec.split_step_classes)
         self.sampler = Sampler(ops, ec.sched.max_num_seqs, config.vocab_size, self.device)
         self._slot_ids = None
         self._inflight: Optional[_Pending] = None

@@ -42,10 +42,10 @@ class _DecodeGraph:
 class Stepper:
     def __init__(self, model: Model, manager: CacheManager, ops, dtype: torch.dtype, device,
                  graph_batch_sizes: Optional[List[int]] = None, capture_repeated: bool = False,
-                 step_graph_max_tokens: int = 1024, max_step_graphs: int = 64):
+                 step_graph_max_tokens: int = 1024, max_step_graphs: int = 64, split_classes: bool = True):
         self.model, self.manager, self.ops, self.dtype = model, manager, ops, dtype
         self.device = torch.device(device)
-        self.packer = BatchPacker(manager, ops, dtype, device, model.spec.vocab_size, model.spec.max_seq_len)
+        self.packer = BatchPacker(manager, ops, dtype, device, model.spec.vocab_size, model.spec.max_seq_len, split_classes)
         self.graph_batch_sizes = sorted(graph_batch_sizes or [])
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self.capture_repeated = bool(capture_repeated)

@@ -1,6 +1,6 @@
 """Per-kernel timings against their rooflines, at the sizes of a model configuration.
 
-    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|prefill_attention|tune|all]
+    python -m tiny_transformer_inference_engine_b200.ops.microbench [--what decode|prefill|gemm_tc|attention|prefill_attention|mixed|tune|all]
                                                                     [--batch 8] [--ctx 4096] [--tokens 2048]
 
 Every kernel is timed alone inside a captured CUDA graph of ``--iters`` launches (so the host's launch
@@ -265,6 +265,42 @@ def gemm_tc(ops, a):
         raise RuntimeError(f"a tensor-core kernel reported wait failure code {err}")
 
 
+def mixed(ops, a):
+    """The attention of a mixed step - ``--batch`` one-token requests with contexts of ``--ctx`` keys beside one 512-token
+    portion behind 2,048 cached tokens - as one launch planned for the whole step, as the two launches the engine makes
+    (one per class), and each class alone."""
+    Hq, Hkv, D, page = a.heads, a.kv_heads, a.d_model // a.heads, 64
+    B, ctx, Tp, behind = a.batch, a.ctx, 512, 2048
+    print(f"== attention of a mixed step: {B} one-token requests at {ctx} keys beside a {Tp}-token portion behind {behind}")
+    lens = [ctx] * B + [behind + Tp]
+    q_lens = [1] * B + [Tp]
+    pages_of = [-(-n // page) for n in lens]
+    nb = sum(pages_of) + 1
+    kp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
+    vp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
+    table = torch.zeros(B + 1, max(pages_of), dtype=torch.int32)
+    nxt = 1
+    for i, n in enumerate(pages_of):
+        table[i, :n] = torch.arange(nxt, nxt + n)
+        nxt += n
+    table = table.to(DEV)
+    T = B + Tp
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    qsl = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    qsl_tail = torch.tensor([0, Tp], dtype=torch.int32, device=DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    o = torch.empty(T, Hq * D, device=DEV, dtype=torch.bfloat16)
+    sc = 1 / math.sqrt(D)
+    nbytes = sum(lens) * Hkv * D * 2 * 2
+    whole = lambda i: ops.paged_attention(qkv, Hq, Hkv, D, kp, vp, table, page, qsl, sl, B + 1, Tp, max(lens), sc, 0, o)
+    first = lambda i: ops.paged_attention(qkv[:B], Hq, Hkv, D, kp, vp, table[:B], page, qsl[:B + 1], sl[:B], B, 1, ctx, sc, 0, o[:B])
+    second = lambda i: ops.paged_attention(qkv[B:], Hq, Hkv, D, kp, vp, table[B:], page, qsl_tail, sl[B:], 1, Tp, behind + Tp, sc, 0, o[B:])
+    line(f"one launch for the step {ops.attention_plan(torch.bfloat16, B + 1, Hq, Hkv, D, Tp, max(lens), page)}", timeit(whole, iters=8), bytes_=nbytes)
+    line("two launches, one per class", timeit(lambda i: (first(i), second(i)), iters=8), bytes_=nbytes)
+    line(f"the one-token requests alone {ops.attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx, page)}", timeit(first, iters=8))
+    line(f"the portion alone {ops.attention_plan(torch.bfloat16, 1, Hq, Hkv, D, Tp, behind + Tp, page)}", timeit(second, iters=8))
+
+
 def tune(ops, a):
     """What ``CudaOps.tune_products`` measures at 16, 32 and 64 rows for the model's matrix shapes: the library's
     product against this package's weight-streaming kernel (both rotate over several matrices of a shape)."""
@@ -284,7 +320,7 @@ def tune(ops, a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "prefill_attention", "tune", "all"))
+    ap.add_argument("--what", default="all", choices=("decode", "prefill", "gemm_tc", "attention", "prefill_attention", "mixed", "tune", "all"))
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -313,6 +349,8 @@ def main(argv=None):
         attention(ops, a)
     if a.what in ("prefill_attention", "all"):
         prefill_attention(ops, a)
+    if a.what == "mixed":
+        mixed(ops, a)
     if a.what == "tune":
         tune(ops, a)
     return 0
