@@ -567,7 +567,8 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n):
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (2048, 4352, 4096), (300, 520, 200), (1, 1000, 64), (129, 72, 4544),
-                                   (700, 515 * 8, 176 * 8), (260, 33000, 64), (513, 4096, 11008)])
+                                   (700, 515 * 8, 176 * 8), (260, 33000, 64), (513, 4096, 11008), (2048, 4096, 4096),
+                                   (1030, 19200, 72), (2048, 5000, 8 * 19), (4100, 4544, 1000)])
 def test_gemm_tcgen05_on_cta_pairs(ops, M, N, K):
     """The product on pairs of CTAs (tcgen05.mma.cta_group::2, 256 x 256 tiles) against float64: tiles that hang over
     every edge, many tiles per pair (the persistent loop and both accumulator buffers), bias, float32 output, a
@@ -587,7 +588,7 @@ def test_gemm_tcgen05_on_cta_pairs(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M,F,K,bias", [(256, 128, 64, False), (2048, 11008, 4096, False), (300, 176, 200, True), (1, 1000, 64, True),
-                                        (515, 18176, 512, False), (130, 200, 4544, True)])
+                                        (515, 18176, 512, False), (130, 200, 4544, True), (2048, 9700, 192, True)])
 def test_gemm_tcgen05_pair_with_swiglu(ops, M, F, K, bias):
     """The gate/up product with silu(g) * u in its epilogue: the leader's half of the tile holds gate columns, its
     peer's the matching up columns; widths that are no multiple of the tile, with and without biases."""
