@@ -268,6 +268,35 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
         return t;
     };
 
+    // The passes below visit every token of the slice several times.  A slice of up to 8 tokens per thread is kept in
+    // registers as (key, probability mass) - the mass is computed once, not once per pass - ; a longer one is read from
+    // shared (or global) memory and its masses recomputed on each visit.
+    constexpr int EPT = 8;
+    const int iters = (n + THREADS - 1) / THREADS;                 // visits per thread (the same for all: whole warps go round together)
+    const bool cached = iters <= EPT && (top_k > 0 || top_p < 1.0f);
+    unsigned ck[EPT];
+    u64 cm[EPT];
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+        ck[e] = 0; cm[e] = 0;
+        const int i = e * THREADS + tid;
+        if (cached && i < n) { const float y = Y(i); ck[e] = ordered_key(y); cm[e] = mass_of(y, ymax); }
+    }
+    auto for_all = [&](bool need_mass, auto&& body) {               // body(token present, key, mass)
+        if (cached) {
+#pragma unroll
+            for (int e = 0; e < EPT; ++e)
+                if (e < iters) body(e * THREADS + tid < n, ck[e], cm[e]);
+        } else {
+            for (int i0 = 0; i0 < n; i0 += THREADS) {
+                const int i = i0 + tid;
+                unsigned key = 0; u64 mass = 0;
+                if (i < n) { const float y = Y(i); key = ordered_key(y); if (need_mass) mass = mass_of(y, ymax); }
+                body(i < n, key, mass);
+            }
+        }
+    };
+
     // 2. top-k threshold: the k-th largest key, by radix select over 4 digits of 8 bits
     unsigned cut_key = 0;
     if (top_k > 0 && top_k < V) {
@@ -275,15 +304,10 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
         for (int shift = 24; shift >= 0; shift -= 8) {
             for (int b = tid; b < 256; b += THREADS) s_hist[b] = 0;
             __syncthreads();
-            for (int i0 = 0; i0 < n; i0 += THREADS) {                 // (whole warps go round together)
-                const int i = i0 + tid;
-                int bin = -1;
-                if (i < n) {
-                    const unsigned key = ordered_key(Y(i));
-                    if (shift == 24 || (key >> (shift + 8)) == prefix) bin = (int)((key >> shift) & 255u);
-                }
+            for_all(false, [&](bool there, unsigned key, u64) {
+                const int bin = there && (shift == 24 || (key >> (shift + 8)) == prefix) ? (int)((key >> shift) & 255u) : -1;
                 hist_add_count(s_hist, bin);
-            }
+            });
             __syncthreads();
             sum_hist();
             if (warp == 0) {
@@ -301,10 +325,7 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
     // 3. top-p threshold: the smallest key whose strictly-larger keys hold mass <= top_p * total
     if (top_p < 1.0f) {
         u64 z = 0;
-        for (int i = tid; i < n; i += THREADS) {
-            const float y = Y(i);
-            if (ordered_key(y) >= cut_key) z += mass_of(y, ymax);
-        }
+        for_all(true, [&](bool there, unsigned key, u64 mass) { if (there && key >= cut_key) z += mass; });
         z = block_sum_u64(z, s_u64);
         if (C > 1) z = sum_u64(z, nullptr);
         const u64 limit = (u64)((double)top_p * (double)z);
@@ -312,17 +333,10 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
         for (int shift = 24; shift >= 0; shift -= 8) {
             for (int b = tid; b < 256; b += THREADS) s_hist[b] = 0;
             __syncthreads();
-            for (int i0 = 0; i0 < n; i0 += THREADS) {
-                const int i = i0 + tid;
-                int bin = -1;
-                u64 m = 0;
-                if (i < n) {
-                    const float y = Y(i);
-                    const unsigned key = ordered_key(y);
-                    if (key >= cut_key && (shift == 24 || (key >> (shift + 8)) == prefix)) { bin = (int)((key >> shift) & 255u); m = mass_of(y, ymax); }
-                }
-                hist_add_mass(s_hist, bin, m);
-            }
+            for_all(true, [&](bool there, unsigned key, u64 mass) {
+                const bool in = there && key >= cut_key && (shift == 24 || (key >> (shift + 8)) == prefix);
+                hist_add_mass(s_hist, in ? (int)((key >> shift) & 255u) : -1, in ? mass : 0);
+            });
             __syncthreads();
             sum_hist();
             if (warp == 0) {                                                   // the cut lies inside the digit picked
@@ -460,13 +474,22 @@ int launch(const float* logits, int R, int V, const int* slot_ids, int* state, i
 }
 }  // namespace
 
-// ctas_per_row: 0 = chosen from the vocabulary (slices of about 8,192 tokens, at most 8 CTAs: a cluster), else 1, 2, 4 or 8.
+// ctas_per_row: 0 = chosen from the vocabulary and the rows (measured: more CTAs per row are faster as long as all rows'
+// clusters fit the GPU at once - 8 at batch 8, 2 at batch 64 - and a slice should fit the shared-memory staging), else
+// 1, 2, 4 or 8.
 extern "C" int ttie_sample_tuned(const float* logits, int R, int V, const int* slot_ids, int* state, int* out,
                                  float* probs_out, int ctas_per_row, void* stream) {
     if (R <= 0) return 0;
     if (V <= 0) TTIE_FAIL("sample: empty vocabulary");
     int C = ctas_per_row;
-    if (C == 0) C = V <= 8192 ? 1 : V <= 16384 ? 2 : V <= 32768 ? 4 : 8;
+    if (C == 0) {
+        int need = 1;                                                 // fewest CTAs whose slices can be staged
+        while (need < 8 && (V + need - 1) / need > STAGE_FLOATS) need *= 2;
+        int fit = 8;                                                  // most CTAs per row with every cluster resident at once
+        while (fit > 1 && (long long)R * fit > num_sms()) fit /= 2;
+        C = fit > need ? fit : need;
+        while (C > 1 && (V + C - 1) / C < 1024) C /= 2;               // (a tiny vocabulary needs no cluster)
+    }
     cudaStream_t s = (cudaStream_t)stream;
     switch (C) {
         case 1: return launch<1>(logits, R, V, slot_ids, state, out, probs_out, s);
