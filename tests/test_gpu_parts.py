@@ -179,7 +179,7 @@ def toy_spec(config):
                                          "head_dim": D, "position": rope, **kw})
     decay = config.extra.get("decay_kind", "toy_decay")
     mixers = [attn("layers.0.attn"), PartSpec(decay, "layers.1.toy", {"dim": d, "decay": 0.5}),
-              attn("layers.2.attn", window=config.extra["window"]), attn("layers.3.attn", shares_kv=True),
+              attn("layers.2.attn", window=config.extra["window"], page_size=16), attn("layers.3.attn", shares_kv=True),
               PartSpec("toy_attention_plus_decay", "layers.4", {"attention": attn("layers.4.attn"),
                                                                 "decay": PartSpec(decay, "layers.4.toy", {"dim": d, "decay": 0.5})})]
     layers = [LayerSpec(PartSpec("pre_norm", f"layers.{i}", {"mixer_norm": norm(f"layers.{i}.n1"), "mixer": m,
@@ -267,8 +267,11 @@ def test_toy_architecture_is_built_and_stepped(toy_registered, dtype, mode):
                       cache=CacheConfig(block_size=page, num_gpu_blocks=tu.max_live_tokens(steps) // page + 1),
                       sched=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64))
     eng = Engine(mc, w, ec)
-    # four runs own pages: three full-attention runs share a group, the windowed run has its own; two keep a state
+    # four runs own pages: three full-attention runs share a group, the windowed run has its own - with pages of its
+    # own size and as many of them as hold the same tokens; two runs keep a state
     assert [len(g_.entries) for g_ in eng.manager.groups] == [3, 1] and sorted(eng.manager.entry_state) == [(1, 0), (5, 1)]
+    assert [g_.page_size for g_ in eng.manager.groups] == [8, 16]
+    assert eng.manager.groups[1].num_pages == -(-(eng.manager.groups[0].num_pages - 1) * 8 // 16) + 1
     exp = {rid: toy_plain_forward(cfg, w, toks) for rid, toks in reqs.items()}
     got = tu.run_steps(eng, steps)
     bad = tu.first_wrong(got, exp, TOL[dtype])

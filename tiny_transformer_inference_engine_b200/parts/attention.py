@@ -10,7 +10,8 @@ project the concatenated heads with ``out``.  Query head ``h`` uses kv head
 
 The three projections are fused at load into one matrix ``[(Hq+2*Hkv)*D, d]`` so one
 product feeds the rotate-and-store kernel.  ``window`` (keys ``pos-window+1..pos``)
-is a parameter of the part; the reference's model has none.  A run entry that reads
+and ``page_size`` (a page size of this layer's own cache group) are parameters of the part; the reference's
+model has neither.  A run entry that reads
 another entry's cache (``shares_kv``) has no k/v projection and stores nothing.
 """
 from __future__ import annotations
@@ -29,7 +30,7 @@ class PagedAttention(Mixer):
     def __init__(self, prefix: str, d_model: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, bias: bool = False, window: Optional[int] = None,
                  scale: Optional[float] = None, shares_kv: bool = False,
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, page_size: Optional[int] = None):
         super().__init__(prefix)
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
@@ -37,6 +38,7 @@ class PagedAttention(Mixer):
             raise ValueError(f"window must be >= 1 or None, got {window}")
         self.d_model, self.num_heads, self.num_kv_heads, self.head_dim = d_model, num_heads, num_kv_heads, head_dim
         self.bias, self.window, self.shares_kv = bool(bias), window, bool(shares_kv)
+        self.page_size = None if page_size is None else int(page_size)     # None: the engine's page size
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.position = build_part("position", position)
         self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "out"}
@@ -76,11 +78,11 @@ class PagedAttention(Mixer):
     def validate(self, ops, dtype, page_size):
         check = getattr(ops, "check_attention", None)
         if check is not None:
-            check(dtype, self.num_heads, self.num_kv_heads, self.head_dim, page_size)
+            check(dtype, self.num_heads, self.num_kv_heads, self.head_dim, self.page_size or page_size)
 
     # ---------------------------------------------------------------- cache
     def cache_need(self):
-        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window, self.page_size)
 
     # ---------------------------------------------------------------- step
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
