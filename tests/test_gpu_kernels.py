@@ -365,6 +365,45 @@ def test_sampling_distribution_and_draw(ops, V, ctas):
     assert out[4] == int(torch.argmax(logits[4]))                 # top_k = 1 is argmax (tests/test_sampling.py:6-12)
 
 
+@pytest.mark.parametrize("V,ctas", [(32000, 1), (32000, 2), (32000, 8), (65024, 0), (256000, 0)])
+def test_sampling_after_a_top_k_cut(ops, V, ctas):
+    """With a small top-k the kernel leaves the row for a short list of candidates: top-k just below, at and above the
+    largest value for which it does (256), a much larger one, and cuts that fall into thousands of equal values (the
+    list overflows in some CTAs or in all, depending on how many share the row, and the whole row is walked): kept
+    sets, probabilities and draws as the plain sampler's, and the same token whatever the number of CTAs."""
+    g = torch.Generator().manual_seed(V + 1)
+    R = 8
+    logits = torch.randn(R, V, generator=g)
+    logits[4, ::5] = 2.5                                           # a fifth of the row is equal; about 0.6 % of the rest lies above
+    logits[5, 1::3] = 2.5
+    logits[7, 100] = logits[7, V - 1] = logits[7].max() + 0.5       # two equal maxima with top_k = 2
+    k4, k5 = int((logits[4] > 2.5).sum()) + 40, int((logits[5] > 2.5).sum()) + 7      # cuts inside the equal values
+    rows = [(11, 0, 250, 0.9, 0.9, 0), (12, 3, 256, 1.1, 1.0, 0), (13, 1, 257, 0.7, 0.8, 0), (14, 7, 1500, 1.0, 0.95, 0),
+            (15, 2, k4, 1.0, 0.9, 0), (16, 4, k5, 1.0, 1.0, 0), (17, 5, 32, 1.0, 0.9, 0), (18, 6, 2, 0.5, 0.6, 0)]
+    state = sampler_state(rows)
+    slot_ids = torch.arange(R, dtype=torch.int32)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    probs = torch.zeros(R, V, device=DEV)
+    st_gpu = state.clone().to(DEV)
+    ops.sample(logits.to(DEV), slot_ids.to(DEV), st_gpu, out, probs_out=probs, ctas_per_row=ctas)
+    for other in (1, 4):
+        again = torch.empty(R, dtype=torch.int32, device=DEV)
+        ops.sample(logits.to(DEV), slot_ids.to(DEV), state.clone().to(DEV), again, ctas_per_row=other)
+        assert torch.equal(again, out)
+    out, probs = out.cpu(), probs.cpu()
+    for r, (seed, draws, top_k, temp, top_p, greedy) in enumerate(rows):
+        exp = PLAIN.filtered_probs(logits[r], temp, top_k, top_p).float()
+        assert torch.equal(probs[r] > 0, exp > 0), f"row {r}: kept sets differ"
+        assert torch.allclose(probs[r], exp, atol=2e-6, rtol=1e-4)
+        u = uniform_from_state(seed & 0x7fffffff, seed >> 31, draws)
+        cdf = torch.cumsum(probs[r].double(), 0)
+        tok = int(out[r])
+        assert probs[r, tok] > 0
+        lo = cdf[tok - 1].item() if tok else 0.0
+        assert lo - 1e-5 <= u <= cdf[tok].item() + 1e-5, (r, u, lo, cdf[tok].item())
+    assert int((probs[4] > 0).sum()) > V // 5 and int((probs[5] > 0).sum()) > V // 3 - 1     # the equal values stayed together
+
+
 def test_sampling_skips_padding_rows(ops):
     """A row whose slot id is -1 (padding of a fixed-size batch) yields token 0 and touches no state."""
     V = 300

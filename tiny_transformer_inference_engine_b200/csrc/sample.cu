@@ -15,10 +15,13 @@
 // State row (int32 x 8): seed_lo, seed_hi, draws, top_k, temperature bits, top_p bits, greedy, -.
 #include "common.cuh"
 #include <math.h>
+#include <algorithm>
 using namespace ttie;
 
 namespace {
 constexpr int THREADS = 1024;
+constexpr int LIST_TOP_K = 256;                                      // largest top-k for which the short list is tried
+constexpr int KEEP_CAP = 1024;                                       // tokens one CTA may hand in to the short list
 typedef unsigned long long u64;
 
 __device__ __forceinline__ unsigned ordered_key(float x) {
@@ -146,10 +149,17 @@ __device__ __forceinline__ void all_gather(T* buf, int n, T v, unsigned rank) {
 // in its shared memory after the first pass, so the later passes do not go back to global memory; a slice too long
 // for that (staged == 0) is read from global memory every time.  Maxima, histograms and sums of the slices are
 // exchanged through distributed shared memory; every CTA then takes the same decisions from the same integers.
+//
+// With a top-k of a few hundred at most the row is left after two walks.  Every thread knows the largest value among its
+// own tokens from the first walk; the k-th largest of a CTA's 1,024 such values is a bound that at least k tokens of the
+// slice reach, so nothing below it can be among the row's k largest.  The tokens at or above the bound (a few more than k
+// per CTA) are gathered in token order, handed to the first CTA of the cluster, and that CTA alone does the exact top-k
+// cut, top-p and the draw on the list (`list_cap` entries fit the shared memory that held its slice).  If the list would
+// overflow (thousands of equal values at the bound), every CTA goes on with its whole slice instead.
 template <int C>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __restrict__ slot_ids, int* __restrict__ state,
-              int* __restrict__ out, float* __restrict__ probs_out, int staged) {
+              int* __restrict__ out, float* __restrict__ probs_out, int staged, int list_cap) {
     extern __shared__ __align__(16) float s_row[];
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
@@ -159,6 +169,10 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
     __shared__ u64 x_u64[2][C];
     __shared__ float x_val[C];
     __shared__ int x_idx[C];
+    __shared__ int x_cnt[C];
+    __shared__ float c_y[KEEP_CAP];                                   // this slice's tokens for the short list: value ...
+    __shared__ int c_i[KEEP_CAP];                                     // ... and place in the slice
+    __shared__ int s_scan[THREADS / 32];
     __shared__ unsigned s_prefix;
     __shared__ u64 s_acc;
     __shared__ int s_found;
@@ -202,6 +216,7 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
             if (x > best || (x == best && i < best_i)) { best = x; best_i = i; }
         }
     }
+    const float my_best = best;                                       // the largest among this thread's tokens (-inf: it has none)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -243,10 +258,17 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
         for (int i = tid; i < n; i += THREADS) s_row[i] = s_row[i] / temperature;
         __syncthreads();
     }
-    auto Y = [&](int i) -> float { return staged ? s_row[i] : row[i] / temperature; };
+    bool listed = false;                                              // the short list has replaced the row ...
+    bool solo = C == 1;                                               // ... and this CTA goes on alone
+    int n_cur = n;                                                    // tokens to walk: the slice, or the list
+    float* u_y = s_row;                                               // the list (it takes the slice's place): values ...
+    int* u_tok = reinterpret_cast<int*>(s_row + list_cap);            // ... and token ids, in token order
+    auto Y0 = [&](int i) -> float { return staged ? s_row[i] : row[i] / temperature; };
+    auto Y = [&](int i) -> float { return listed ? u_y[i] : Y0(i); };
+    auto TOK = [&](int i) -> int { return listed ? u_tok[i] : v0 + i; };
     // the cluster's sum of a histogram of 256 bins that every CTA has filled in s_hist for its slice: into s_hist
     auto sum_hist = [&]() {
-        if (C > 1) {
+        if (C > 1 && !solo) {
             u64* buf = x_hist[xq & 1]; ++xq;
             all_gather<C, u64>(buf, 256, tid < 256 ? s_hist[tid] : 0, rank);
             if (tid < 256) {
@@ -260,6 +282,7 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
     };
     u64 xs_parity = 0;                                                // exchanges of single values so far
     auto sum_u64 = [&](u64 v, u64* parts) -> u64 {                    // the cluster's sum of a per-CTA value; parts[k]: CTA k's
+        if (solo) { if (parts) parts[0] = v; return v; }
         u64* buf = x_u64[xs_parity & 1]; ++xs_parity;
         all_gather<C, u64>(buf, 1, v, rank);
         u64 t = 0;
@@ -268,11 +291,94 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
         return t;
     };
 
+    if (staged && list_cap > 0 && top_k > 0 && top_k < V && top_k <= LIST_TOP_K) {
+        // (a) the bound: the top_k-th largest of the threads' own maxima (a radix select over one key per thread)
+        const unsigned tkey = ordered_key(my_best / temperature);
+        unsigned prefix = 0; u64 remaining = (u64)top_k;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += THREADS) s_hist[b] = 0;
+            __syncthreads();
+            hist_add_count(s_hist, (shift == 24 || (tkey >> (shift + 8)) == prefix) ? (int)((tkey >> shift) & 255u) : -1);
+            __syncthreads();
+            if (warp == 0) {
+                u64 above;
+                const int digit = pick_digit(s_hist, 0, remaining, false, &above);
+                if (lane == 0) { s_prefix = (prefix << 8) | (unsigned)digit; s_acc = remaining - above; }
+            }
+            __syncthreads();
+            prefix = s_prefix; remaining = s_acc;
+            __syncthreads();
+        }
+        const unsigned low_key = prefix;
+        // (b) the tokens at or above it, in token order: a thread counts them in its run of consecutive tokens (an odd
+        // run length: different banks), a scan over the block gives each run its place
+        const int run = ((n + THREADS - 1) / THREADS) | 1;
+        const int a = min(n, tid * run), b = min(n, a + run);
+        int cnt = 0;
+        for (int i = a; i < b; ++i) cnt += ordered_key(s_row[i]) >= low_key ? 1 : 0;
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) s_scan[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = s_scan[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, w, o);
+                if (lane >= o) w += up;
+            }
+            s_scan[lane] = w;
+        }
+        __syncthreads();
+        int at = incl - cnt + (warp ? s_scan[warp - 1] : 0);
+        const int kept = s_scan[THREADS / 32 - 1];
+        if (kept <= KEEP_CAP) {
+            for (int i = a; i < b; ++i) {
+                const float y = s_row[i];
+                if (ordered_key(y) >= low_key) { c_y[at] = y; c_i[at] = i; ++at; }
+            }
+        }
+        // (c) how many each CTA brings (this exchange also tells that every CTA is done reading its slice)
+        int before = 0, total = 0;
+        bool fits = true;
+        if (C > 1) {
+            all_gather<C, int>(x_cnt, 1, kept, rank);
+#pragma unroll
+            for (int k = 0; k < C; ++k) {
+                fits = fits && x_cnt[k] <= KEEP_CAP;
+                if (k < (int)rank) before += x_cnt[k];
+                total += x_cnt[k];
+            }
+        } else {
+            __syncthreads();
+            fits = kept <= KEEP_CAP; total = kept;
+        }
+        fits = fits && total <= list_cap;
+        if (fits) {
+            // (d) into the first CTA's list, slice after slice; the others are done
+            for (int j = tid; j < kept; j += THREADS) {
+                if (C > 1) { put_remote(u_y + before + j, 0u, c_y[j]); put_remote(u_tok + before + j, 0u, v0 + c_i[j]); }
+                else { u_y[j] = c_y[j]; u_tok[j] = v0 + c_i[j]; }
+            }
+            if (C > 1) {
+                cluster_sync_all();
+                if (rank != 0) return;
+            } else {
+                __syncthreads();
+            }
+            listed = true; solo = true; n_cur = total;
+        }
+    }
+
     // The passes below visit every token of the slice several times.  A slice of up to 8 tokens per thread is kept in
     // registers as (key, probability mass) - the mass is computed once, not once per pass - ; a longer one is read from
     // shared (or global) memory and its masses recomputed on each visit.
     constexpr int EPT = 8;
-    const int iters = (n + THREADS - 1) / THREADS;                 // visits per thread (the same for all: whole warps go round together)
+    const int iters = (n_cur + THREADS - 1) / THREADS;             // visits per thread (the same for all: whole warps go round together)
     const bool cached = iters <= EPT && (top_k > 0 || top_p < 1.0f);
     unsigned ck[EPT];
     u64 cm[EPT];
@@ -280,19 +386,19 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
     for (int e = 0; e < EPT; ++e) {
         ck[e] = 0; cm[e] = 0;
         const int i = e * THREADS + tid;
-        if (cached && i < n) { const float y = Y(i); ck[e] = ordered_key(y); cm[e] = mass_of(y, ymax); }
+        if (cached && i < n_cur) { const float y = Y(i); ck[e] = ordered_key(y); cm[e] = mass_of(y, ymax); }
     }
     auto for_all = [&](bool need_mass, auto&& body) {               // body(token present, key, mass)
         if (cached) {
 #pragma unroll
             for (int e = 0; e < EPT; ++e)
-                if (e < iters) body(e * THREADS + tid < n, ck[e], cm[e]);
+                if (e < iters) body(e * THREADS + tid < n_cur, ck[e], cm[e]);
         } else {
-            for (int i0 = 0; i0 < n; i0 += THREADS) {
+            for (int i0 = 0; i0 < n_cur; i0 += THREADS) {
                 const int i = i0 + tid;
                 unsigned key = 0; u64 mass = 0;
-                if (i < n) { const float y = Y(i); key = ordered_key(y); if (need_mass) mass = mass_of(y, ymax); }
-                body(i < n, key, mass);
+                if (i < n_cur) { const float y = Y(i); key = ordered_key(y); if (need_mass) mass = mass_of(y, ymax); }
+                body(i < n_cur, key, mass);
             }
         }
     };
@@ -327,7 +433,7 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
         u64 z = 0;
         for_all(true, [&](bool there, unsigned key, u64 mass) { if (there && key >= cut_key) z += mass; });
         z = block_sum_u64(z, s_u64);
-        if (C > 1) z = sum_u64(z, nullptr);
+        if (C > 1 && !solo) z = sum_u64(z, nullptr);
         const u64 limit = (u64)((double)top_p * (double)z);
         unsigned prefix = 0; u64 acc = 0;
         for (int shift = 24; shift >= 0; shift -= 8) {
@@ -355,8 +461,8 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
     // slice (an odd number of them, so the threads of a warp read different banks of the staged row); a slice that
     // is not staged is walked by warps instead, 32 consecutive tokens at a time, so its loads coalesce.
     const bool by_thread = staged != 0;
-    const int chunk = by_thread ? (((n + THREADS - 1) / THREADS) | 1) : ((((n + THREADS / 32 - 1) / (THREADS / 32)) + 31) & ~31);
-    const int i0 = min(n, (by_thread ? tid : warp) * chunk), i1 = min(n, i0 + chunk);
+    const int chunk = by_thread ? (((n_cur + THREADS - 1) / THREADS) | 1) : ((((n_cur + THREADS / 32 - 1) / (THREADS / 32)) + 31) & ~31);
+    const int i0 = min(n_cur, (by_thread ? tid : warp) * chunk), i1 = min(n_cur, i0 + chunk);
     u64 local = 0;
     if (by_thread) {
         for (int i = i0; i < i1; ++i) {
@@ -395,10 +501,10 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
     incl += warp ? s_warp[warp - 1] : 0;
     const u64 mine = s_warp[THREADS / 32 - 1];                        // kept mass of this CTA's slice
     u64 parts[C];
-    const u64 total = C > 1 ? sum_u64(mine, parts) : mine;
+    const u64 total = (C > 1 && !solo) ? sum_u64(mine, parts) : mine;
     u64 below = 0;                                                    // kept mass of the slices before this one
 #pragma unroll
-    for (int k = 0; k < C; ++k) if (C > 1 && k < (int)rank) below += parts[k];
+    for (int k = 0; k < C; ++k) if (C > 1 && !solo && k < (int)rank) below += parts[k];
     unsigned rnd[4];
     philox4x32_10(draws, 0u, 0u, 0u, seed_lo, seed_hi, rnd);
     const double u = (double)(rnd[0] >> 8) * (1.0 / 16777216.0);
@@ -415,7 +521,7 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
                 const float y = Y(i);
                 if (ordered_key(y) >= cut_key) {
                     c += mass_of(y, ymax);
-                    if (target < c) { s_found = v0 + i; break; }
+                    if (target < c) { s_found = TOK(i); break; }
                 }
             }
         } else {
@@ -433,7 +539,7 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
                 }
                 const bool hit = m > 0 && target >= c + sc - m && target < c + sc;
                 const unsigned where = __ballot_sync(0xffffffffu, hit);
-                if (where) { if (hit) s_found = v0 + j; break; }
+                if (where) { if (hit) s_found = TOK(j); break; }
                 c += __shfl_sync(0xffffffffu, sc, 31);
             }
         }
@@ -445,9 +551,18 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
     }
     if (probs_out) {
         const double inv = total ? 1.0 / (double)total : 0.0;
-        for (int i = tid; i < n; i += THREADS) {
-            const float y = Y(i);
-            probs_out[(size_t)r * V + v0 + i] = ordered_key(y) >= cut_key ? (float)((double)mass_of(y, ymax) * inv) : 0.f;
+        if (listed) {                                                 // this CTA is the only one left: the whole row is its to write
+            for (int i = tid; i < V; i += THREADS) probs_out[(size_t)r * V + i] = 0.f;
+            __syncthreads();
+            for (int i = tid; i < n_cur; i += THREADS) {
+                const float y = Y(i);
+                if (ordered_key(y) >= cut_key) probs_out[(size_t)r * V + TOK(i)] = (float)((double)mass_of(y, ymax) * inv);
+            }
+        } else {
+            for (int i = tid; i < n; i += THREADS) {
+                const float y = Y0(i);
+                probs_out[(size_t)r * V + v0 + i] = ordered_key(y) >= cut_key ? (float)((double)mass_of(y, ymax) * inv) : 0.f;
+            }
         }
     }
 }
@@ -459,7 +574,9 @@ int launch(const float* logits, int R, int V, const int* slot_ids, int* state, i
     int slice = (V + C - 1) / C;
     slice = (slice + 3) & ~3;                                         // slices start on 16-byte boundaries of a row that does
     const int staged = slice <= STAGE_FLOATS;
-    const size_t smem = staged ? (size_t)slice * sizeof(float) : 0;
+    // the staged slice, and room for the short list that may take its place (8 bytes an entry)
+    const size_t smem = staged ? std::max((size_t)slice * sizeof(float), (size_t)32768) : 0;
+    const int list_cap = (int)(smem / 8);
     auto k = sample_kernel<C>;
     static bool allowed = false;
     if (!allowed) {
@@ -467,8 +584,8 @@ int launch(const float* logits, int R, int V, const int* slot_ids, int* state, i
             TTIE_FAIL("sample: %d bytes of shared memory refused", STAGE_FLOATS * 4);
         allowed = true;
     }
-    if (C == 1) TTIE_LAUNCH(k, R, THREADS, smem, s, logits, V, slice, slot_ids, state, out, probs_out, staged);
-    else TTIE_LAUNCH_CLUSTER(k, R * C, THREADS, smem, s, dim3(C, 1, 1), logits, V, slice, slot_ids, state, out, probs_out, staged);
+    if (C == 1) TTIE_LAUNCH(k, R, THREADS, smem, s, logits, V, slice, slot_ids, state, out, probs_out, staged, list_cap);
+    else TTIE_LAUNCH_CLUSTER(k, R * C, THREADS, smem, s, dim3(C, 1, 1), logits, V, slice, slot_ids, state, out, probs_out, staged, list_cap);
     TTIE_CHECK_LAUNCH("sample");
     return 0;
 }
