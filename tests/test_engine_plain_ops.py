@@ -127,3 +127,33 @@ def test_mixed_step_is_packed_in_two_classes():
     # a step of one kind is one class: the step itself
     only = packer.pack(entries[1::2])
     assert only.seq_classes is None and len(only.classes()) == 1 and only.classes()[0].tok_hi == 2
+
+
+def test_requests_added_between_steps():
+    """``add_request`` between calls of ``step`` until ``has_unfinished`` says no, on a pool that throws a request out on
+    the way: every request's greedy tokens equal plain greedy decoding."""
+    from tiny_transformer_inference_engine_b200 import SamplingParams
+    cfg = TINY_A
+    eng, w = make(cfg, SEEDS["A"], 4, 12)
+    g = torch.Generator().manual_seed(3)
+    reqs = [(torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist(), new) for n, new in ((9, 12), (17, 10), (3, 14), (20, 8), (5, 5))]
+    arrive = [0, 0, 2, 3, 9]
+    assert not eng.has_unfinished()
+    out, ids, nxt, step = {}, {}, 0, 0
+    while nxt < len(reqs) or eng.has_unfinished():
+        while nxt < len(reqs) and arrive[nxt] <= step:
+            rid = eng.add_request(reqs[nxt][0], SamplingParams(max_new_tokens=reqs[nxt][1], greedy=True, ignore_eos=True))
+            ids[rid], out[nxt] = nxt, []
+            nxt += 1
+        for rid, tok, _ in eng.step():
+            out[ids[rid]].append(tok)
+        step += 1
+        assert step < 500
+    assert eng.stats()["preemptions"] > 0 and eng.stats()["finished"] == len(reqs)
+    eng.manager.check()
+    assert eng.manager.num_free_pages == eng.manager.num_usable_pages
+    for i, (prompt, new) in enumerate(reqs):
+        toks = list(prompt)
+        for _ in range(new):
+            toks.append(int(torch.argmax(plain_forward(cfg, w, toks)[-1])))
+        assert out[i] == toks[len(prompt):], i

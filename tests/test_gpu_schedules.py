@@ -105,6 +105,42 @@ def test_preemption_by_recompute_on_the_gpu():
     assert eng.manager.num_free_pages == eng.manager.num_usable_pages
 
 
+def test_requests_arriving_between_steps_with_everything_switched_on():
+    """The continuous loop as a caller drives it: ``add_request`` between calls of ``step`` until ``has_unfinished`` says
+    no, with captured decode steps, repeated layouts replayed, the next step launched ahead of the read and a pool that
+    forces a request out now and then.  Twenty requests arrive at random steps; every one's greedy tokens equal plain
+    greedy decoding (float32), and the pool is whole at the end."""
+    import random
+    cfg = TINY_B
+    rng = random.Random(11)
+    g = torch.Generator().manual_seed(11)
+    reqs, arrive, t = [], [], 0
+    for i in range(20):
+        n = rng.choice([1, 2, 3, 7, 16, 17, 33, 40, 64, 71])
+        reqs.append((torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist(), rng.randint(1, 24)))
+        arrive.append(t)
+        t += rng.choice([0, 0, 1, 2, 5, 9])
+    eng, w = make_engine(cfg, SEEDS["B"], PAGE["B"], 18, "float32", max_seqs=4, budget=24, graphs=True, cudagraph_batch_sizes=[1, 2, 4])
+    assert eng.engine_config.pipelined_decode and eng.engine_config.capture_repeated_steps
+    out, ids, nxt, step = {}, {}, 0, 0
+    while nxt < len(reqs) or eng.has_unfinished():
+        while nxt < len(reqs) and arrive[nxt] <= step:
+            rid = eng.add_request(reqs[nxt][0], SamplingParams(max_new_tokens=reqs[nxt][1], greedy=True, ignore_eos=True))
+            ids[rid], out[nxt] = nxt, []
+            nxt += 1
+        if eng.has_unfinished():
+            for rid, tok, _ in eng.step():
+                out[ids[rid]].append(tok)
+        step += 1
+        assert step < 5000
+    st = eng.stats()
+    assert st["preemptions"] > 0 and st["step_graph_replays"] > 0 and st["finished"] == 20
+    eng.manager.check()
+    assert eng.manager.num_free_pages == eng.manager.num_usable_pages
+    for i, (prompt, n) in enumerate(reqs):
+        assert out[i] == plain_greedy(cfg, w, prompt, n), i
+
+
 # ------------------------------------------------------------------------------------------ graphs, sampler in the graph, pipelining
 @pytest.mark.parametrize("pipelined", [True, False])
 def test_captured_pipelined_decode_in_bfloat16_against_the_plain_model(pipelined):

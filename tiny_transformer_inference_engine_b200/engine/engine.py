@@ -115,6 +115,11 @@ class Engine:
         self._requests[rid] = self.scheduler.waiting[-1]
         return rid
 
+    def has_unfinished(self) -> bool:
+        """Whether a call of ``step`` still has something to do: requests waiting or running, or a launched step whose
+        tokens the host has not read yet."""
+        return self._inflight is not None or self.scheduler.has_work
+
     @torch.no_grad()
     def step(self) -> List[Tuple[int, int, bool]]:
         """One scheduler step: plan, run the batch, sample on the device, read the tokens.
