@@ -148,30 +148,38 @@ struct AttnTcParams {
     int num_seqs, Hq, Hkv;
     float scale_log2; int window;
     int row_tiles;
+    int q_rows;                                                  // rows of the query tile that are staged (a multiple of 32 that covers every request's rows)
     int num_splits, split_len;                                   // keys per CTA along grid y (a multiple of 128); 1: no split
     float* ws_o; float* ws_ml;                                   // partial results [row][split][D] and [row][split][2] (max in natural log, sum)
 };
-
-// Barrier slots
-enum { KF = 0, KE = 2, VF = 4, VE = 6, SF = 8, SE = 10, OF = 12, OE = 14, PF = 16, XB = 17, XL = 19, NBARS = 20 };
 
 constexpr int NP = 4;                                            // softmax threads per query row
 constexpr int NTHREADS = 64 + NP * 128;
 
 // AHEAD: the copy producer looks pages up one tile ahead (prompt portions); otherwise as it goes (decode steps).
-template <int D, bool AHEAD>
+// NST: stages of the key ring and of the value ring.  A decode step's CTA is bound by how many bytes it has in flight
+// (it walks its keys once, each tile's copy is asked for when its stage comes free), and it has few query rows: only
+// `q_rows` of the tile's 128 rows are staged, which leaves room for a third stage at head size 128 and a fourth at 64.
+// The product still reads 128 rows; what it finds past `q_rows` belongs to the next block or to the ring, gives score
+// rows that nobody reads, and costs nothing (rows of a product do not mix).
+template <int D, bool AHEAD, int NST>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
+    // barrier slots: key / value stages full and empty, score and output buffers full and empty, P written, exchanges
+    constexpr int KF = 0, KE = NST, VF = 2 * NST, VE = 3 * NST, SF = 4 * NST, SE = SF + 2, OF = SE + 2, OE = OF + 2, PF = OE + 2,
+                  XB = PF + 1, XL = XB + 2, NBARS = XL + 1;
     constexpr int CB = D / 64;                                   // 64-column blocks of the head dimension
-    constexpr uint32_t QBLK = BM * 128, KVBLK = BN * 128;        // bytes of one 64-column block
-    constexpr uint32_t Q_BYTES = CB * QBLK, KV_BYTES = CB * KVBLK;
+    constexpr uint32_t KVBLK = BN * 128;                         // bytes of one 64-column block of a key / value tile
+    constexpr uint32_t KV_BYTES = CB * KVBLK;
+    const uint32_t QBLK = (uint32_t)p.q_rows * 128;              // ... of the staged query rows
+    const uint32_t Q_BYTES = CB * QBLK;
     constexpr uint32_t TMEM_COLS = 512;                          // 2 x 128 (S) + 2 x D (O_tile), rounded to a power of two
     constexpr uint32_t S_COL = 0, O_COL = 256;
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = smem;
-    unsigned char* Ks = Qs + Q_BYTES;                            // [2 stages]
-    unsigned char* Vs = Ks + 2 * KV_BYTES;                       // [2 stages]
+    unsigned char* Ks = Qs + Q_BYTES;                            // [NST stages]
+    unsigned char* Vs = Ks + NST * KV_BYTES;                     // [NST stages]
     __shared__ __align__(8) unsigned long long bars[NBARS];
     __shared__ uint32_t tmem_slot;
     __shared__ float xch[2][NP][BM];                              // row maxima of the column parts, by tile parity
@@ -245,7 +253,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     } else {
         // queries of the tile -> shared memory in the K-major swizzled operand layout
-        for (int c = threadIdx.x - 64; c < BM * (D / 8); c += blockDim.x - 64) {
+        for (int c = threadIdx.x - 64; c < p.q_rows * (D / 8); c += blockDim.x - 64) {
             const int r = c / (D / 8), chunk = c - r * (D / 8);      // chunk: 8 bfloat16 = 16 bytes
             const int row = row0 + r;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -283,8 +291,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         int y_cur = box_row(0);
         for (int j = 0; j < ntiles; ++j) {
             const int y_next = box_row(j + 1);
-            const int st = j & 1;
-            const uint32_t par = ((j >> 1) & 1) ^ 1;
+            const int st = j % NST;
+            const uint32_t par = ((j / NST) & 1) ^ 1;
             int ok = 1;
             if (lane == 0) ok = mbar_wait_relaxed(BAR(KE + st), par, 1);
             if (!__shfl_sync(0xffffffffu, ok, 0)) break;
@@ -343,8 +351,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             const int box_rows = ps < BN ? ps : BN;
             const int* table = p.block_table + (size_t)seq * p.table_width;
             for (int j = 2; j < ntiles; ++j) {
-                const int st = j & 1;
-                const uint32_t par = ((j >> 1) & 1) ^ 1;
+                const int st = j % NST;
+                const uint32_t par = ((j / NST) & 1) ^ 1;
                 const int key0 = (t_begin + j) * BN;
                 if (!mbar_wait(BAR(KE + st), par, 1)) break;
                 mbar_expect_tx(BAR(KF + st), KV_BYTES);
@@ -382,8 +390,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             for (int cb = 0; cb < CB; ++cb) q_lo[cb] = desc_lo(smem_u32(Qs + cb * QBLK), 16);
             const uint32_t ks_lo = desc_lo(smem_u32(Ks), 16), vs_lo = desc_lo(smem_u32(Vs), KVBLK);
             auto issue_s = [&](int j) -> bool {
-                const int st = j & 1, sb = j & 1;
-                if (!mbar_wait(BAR(KF + st), (j >> 1) & 1, 3)) return false;
+                const int st = j % NST, sb = j & 1;
+                if (!mbar_wait(BAR(KF + st), (j / NST) & 1, 3)) return false;
                 if (!mbar_wait(BAR(SE + sb), ((j >> 1) & 1) ^ 1, 4)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t k_lo = ks_lo + (uint32_t)st * (KV_BYTES >> 4), d = tmem_base + S_COL + (uint32_t)sb * BN;
@@ -401,8 +409,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             bool ok = ntiles > 0 ? issue_s(0) : true;
             for (int j = 0; j < ntiles && ok; ++j) {
                 if (j + 1 < ntiles) { ok = issue_s(j + 1); if (!ok) break; }
-                const int st = j & 1, ob = j & 1;
-                if (!mbar_wait(BAR(VF + st), (j >> 1) & 1, 5)) { ok = false; break; }
+                const int st = j % NST, ob = j & 1;
+                if (!mbar_wait(BAR(VF + st), (j / NST) & 1, 5)) { ok = false; break; }
                 if (!mbar_wait(BAR(OE + ob), ((j >> 1) & 1) ^ 1, 6)) { ok = false; break; }
                 if (!mbar_wait(BAR(PF), j & 1, 7)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1034,18 +1042,20 @@ int encode_page_map(CUtensorMap* map, const void* base, long long rows, int D, i
     return 0;
 }
 
-template <int D, bool AHEAD>
+template <int D, bool AHEAD, int NST>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, cudaStream_t s) {
-    const size_t smem = (size_t)(D / 64) * BM * 128 + 4 * (size_t)(D / 64) * BN * 128 + 1024;
-    auto k = attn_tc_kernel<D, AHEAD>;
+    const size_t smem = (size_t)(D / 64) * p.q_rows * 128 + 2 * NST * (size_t)(D / 64) * BN * 128 + 1024;
+    const size_t most = (size_t)(D / 64) * (NST > 2 && D > 64 ? 64 : BM) * 128 + 2 * NST * (size_t)(D / 64) * BN * 128 + 1024;
+    auto k = attn_tc_kernel<D, AHEAD, NST>;
     static bool allowed[64] = {false};                           // the attribute is set once per device
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     if (!allowed[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
+        if (e != cudaSuccess) TTIE_FAIL("attention_tc: %zu bytes of shared memory refused: %s", most, cudaGetErrorString(e));
         allowed[dev] = true;
     }
+    if (smem > most) TTIE_FAIL("attention_tc: %d staged query rows with %d stages do not fit", p.q_rows, NST);
     k<<<dim3(p.num_seqs * p.Hkv * p.row_tiles, p.num_splits), NTHREADS, smem, s>>>(mk, mv, p);
     TTIE_CHECK_LAUNCH("attention_tc");
     return 0;
@@ -1143,10 +1153,13 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("attention_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;
-    const bool ahead = max_q_len * (Hq / Hkv) >= BM;             // full row tiles: a prompt portion
+    const int rows_most = max_q_len * (Hq / Hkv);
+    const bool ahead = rows_most >= BM;                          // full row tiles: a prompt portion
+    p.q_rows = ahead ? BM : 32 * ceil_div(rows_most, 32);
     const int rc = two_tiles ? (D == 64 ? launch_pp<64>(mk, mv, p, s) : D == 128 ? launch_pp<128>(mk, mv, p, s) : launch_pp<256>(mk, mv, p, s))
-                 : D == 64 ? (ahead ? launch<64, true>(mk, mv, p, s) : launch<64, false>(mk, mv, p, s))
-                           : (ahead ? launch<128, true>(mk, mv, p, s) : launch<128, false>(mk, mv, p, s));
+                 : D == 64 ? (ahead ? launch<64, true, 2>(mk, mv, p, s) : launch<64, false, 4>(mk, mv, p, s))
+                           : (ahead ? launch<128, true, 2>(mk, mv, p, s)
+                                    : p.q_rows <= 64 ? launch<128, false, 3>(mk, mv, p, s) : launch<128, false, 2>(mk, mv, p, s));
     if (rc) return rc;
     if (num_splits > 1) return attn_merge_bf16(p.ws_o, p.ws_ml, out, T * Hq, num_splits, D, s);
     return 0;
