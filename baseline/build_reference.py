@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Puts an unmodified copy of the reference under ``baseline/_ref`` and builds its CUDA extensions.
 
-    python baseline/build_reference.py [--source DIR] [--only NAME ...]
+    python baseline/build_reference.py --source DIR [--only NAME ...]
 
 The reference is a flat script tree without a root ``setup.py`` or ``pyproject.toml``, so pip cannot
 install it.  Each of its kernels has a ``setup.py`` of its own (kernels/pagedattn/setup.py,
@@ -45,12 +45,12 @@ def built(module: str, folder: str):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--source", default="/root/reference")
+    ap.add_argument("--source", default=os.environ.get("REFERENCE_DIR", ""), help="the reference's checkout (needed once, to make the copy)")
     ap.add_argument("--only", nargs="*", default=None)
     args = ap.parse_args()
     if not os.path.isdir(os.path.join(DEST, "kernels")):
-        if not os.path.isdir(args.source):
-            print(f"no reference tree at {args.source}", file=sys.stderr)
+        if not args.source or not os.path.isdir(args.source):
+            print(f"no reference tree at {args.source!r}: give --source DIR", file=sys.stderr)
             return 1
         shutil.copytree(args.source, DEST, dirs_exist_ok=True)
     env = dict(os.environ, TORCH_CUDA_ARCH_LIST="10.0", MAX_JOBS=os.environ.get("MAX_JOBS", "4"))
