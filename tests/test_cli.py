@@ -38,3 +38,30 @@ def test_cli_generates(tmp_path):
     lines = [json.loads(l) for l in p.stdout.strip().split("\n")]
     assert [l["prompt_ids"] for l in lines] == [[1, 2, 3], [9, 8, 7, 6, 5]]
     assert all(len(l["generated_ids"]) == 6 for l in lines)
+
+
+def test_text_prompts_need_the_tokenizer(monkeypatch, capsys):
+    """``--prompt`` is the reference's text option; without tiktoken's vocabulary it is refused with a message that names
+    the way out.  With a tokenizer the text is encoded before anything else is looked at."""
+    import types
+    broken = types.ModuleType("tiktoken")
+
+    def no_vocabulary(name):
+        raise OSError("no vocabulary file")
+
+    broken.get_encoding = no_vocabulary
+    monkeypatch.setitem(sys.modules, "tiktoken", broken)
+    with pytest.raises(SystemExit):
+        main(["--model", "m", "--prompt", "Once upon a time"])
+    err = capsys.readouterr().err
+    assert "--prompt needs tiktoken's gpt2 vocabulary" in err and "--prompt-ids" in err
+
+    seen = []
+    working = types.ModuleType("tiktoken")
+    working.get_encoding = lambda name: types.SimpleNamespace(encode_ordinary=lambda t: seen.append(t) or [1, 2, 3], decode=lambda ids: "")
+    monkeypatch.setitem(sys.modules, "tiktoken", working)
+    import torch
+    if not torch.cuda.is_available():
+        with pytest.raises(SystemExit):
+            main(["--model", "m", "--prompt", "Once upon a time"])
+        assert seen == ["Once upon a time"] and "CUDA is unavailable" in capsys.readouterr().err

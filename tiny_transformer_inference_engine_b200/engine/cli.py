@@ -4,9 +4,11 @@ Option names and meanings follow it where it has them: ``--tokens/--token`` (100
 ``--temperature`` (1.0), ``--top-k/--top_k`` (0 = off), ``--top-p/--top_p`` (1.0 = off),
 ``--device`` (auto), ``--num-gpu-blocks`` (256), ``--block-size`` (16), ``--prompts`` for several
 requests at once (its ``--serving`` path; here every run goes through the scheduler).  Where the
-reference takes a checkpoint file and text (``--ckpt``, ``--prompt``), this takes a model folder
-(``--model``, or ``--ckpt`` as an alias) and token ids (``--prompt-ids 1,2,3``, repeatable), because
-the reference's tokenizer file cannot be had offline.  ``--random-config`` makes a random-weights
+reference takes a checkpoint file (``--ckpt``), this takes a model folder (``--model``, or ``--ckpt``
+as an alias).  Prompts are token ids (``--prompt-ids 1,2,3``, repeatable) or, as in the reference,
+text (``--prompt "Once upon a time"``, repeatable), which is encoded and decoded with tiktoken's
+``gpt2`` vocabulary (inference.py:256-269) if that package and its vocabulary file are there; without
+them ``--prompt`` is refused with a message and token ids remain.  ``--random-config`` makes a random-weights
 model from a config.json and ``--seed``.  Its backend, attention-type and quantization options have
 no counterpart (one kernel path, one architecture, no quantized weights).
 """
@@ -25,6 +27,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prompt-ids", "--prompts", dest="prompt_ids", action="append", default=[],
                     help="comma-separated token ids; give it several times for several requests")
     ap.add_argument("--prompt-ids-file", help="JSON file with a list of token-id lists")
+    ap.add_argument("--prompt", dest="prompt_text", action="append", default=[],
+                    help="a text prompt (tiktoken's gpt2 vocabulary, as the reference); may be given several times")
     ap.add_argument("--tokens", "--token", dest="tokens", type=int, default=100)
     ap.add_argument("--temperature", type=float, default=1.0)
     ap.add_argument("--top-k", "--top_k", dest="top_k", type=int, default=0)
@@ -58,8 +62,19 @@ def main(argv=None) -> int:
     if args.prompt_ids_file:
         with open(args.prompt_ids_file) as f:
             prompts.extend([int(t) for t in p] for p in json.load(f))
+    texts = [None] * len(prompts)
+    tokenizer = None
+    if args.prompt_text:
+        try:
+            import tiktoken
+            tokenizer = tiktoken.get_encoding("gpt2")                              # inference.py:256
+        except Exception as e:                                                     # noqa: BLE001 - not installed, or no vocabulary file offline
+            ap.error(f"--prompt needs tiktoken's gpt2 vocabulary ({type(e).__name__}: {e}); give --prompt-ids instead")
+        for t in args.prompt_text:
+            prompts.append(list(tokenizer.encode_ordinary(t)))                     # inference.py:262
+            texts.append(t)
     if not prompts:
-        ap.error("give at least one --prompt-ids")
+        ap.error("give at least one --prompt-ids or --prompt")
 
     import torch
     device = args.device
@@ -83,8 +98,11 @@ def main(argv=None) -> int:
     params = [SamplingParams(max_new_tokens=args.tokens, temperature=args.temperature, top_k=args.top_k,
                              top_p=args.top_p, greedy=args.greedy, seed=args.seed + i, ignore_eos=args.ignore_eos)
               for i in range(len(prompts))]
-    for prompt, out in zip(prompts, engine.generate(prompts, params)):
-        print(json.dumps({"prompt_ids": prompt, "generated_ids": out}))
+    for prompt, text, out in zip(prompts, texts, engine.generate(prompts, params)):
+        if text is None:
+            print(json.dumps({"prompt_ids": prompt, "generated_ids": out}))
+        else:
+            print(text + tokenizer.decode(out))                                    # inference.py:269
     return 0
 
 
