@@ -145,3 +145,48 @@ def test_missing_extension_fails_loudly():
         pytest.skip("a GPU is present")
     with pytest.raises(KernelError, match="no CPU path"):
         get_ops("cuda:0")
+
+
+def test_reference_checkpoint_is_converted_to_a_model_folder(tmp_path):
+    """A file saved the way the reference saves its checkpoints (inference.py:16-29,87: ``model_config``, ``model`` with
+    the compiled-model prefix on some keys) becomes config.json + model.safetensors; the engine loads the folder and its
+    logits are the plain model's for the same tensors.  The feed-forward width comes from the tensors, the rotary base and
+    the norms' eps are the values the reference fixes in code."""
+    from plain_model import plain_forward
+    from plain_ops import PlainOps
+    from tiny_configs import TINY_B, SEEDS
+    from tiny_transformer_inference_engine_b200 import Engine, EngineConfig, CacheConfig, SchedulerConfig
+    from tiny_transformer_inference_engine_b200.weights import convert_checkpoint, CheckpointError
+    from tiny_transformer_inference_engine_b200.weights.convert import main as convert_main
+    cfg = dict(TINY_B, rope_theta=10000.0, rms_norm_eps=1e-5)
+    w = random_tensors(ModelConfig.from_dict(cfg), SEEDS["B"], perturb_norms=True)
+    saved_cfg = {k: cfg[k] for k in ("vocab_size", "d_model", "num_layers", "num_heads", "num_kv_heads", "max_seq_len", "bias")}
+    saved_cfg.update(causal=True, dropout=0.0, eos_token_id=7, rope_theta=123.0, rms_norm_eps=0.5)   # declared, never used by its layers
+    state = {("_orig_mod." + k if i % 2 else k): v for i, (k, v) in enumerate(w.items())}
+    path = str(tmp_path / "ckpt_step1.pt")
+    torch.save({"model_config": saved_cfg, "model": state, "train_config": {"attn_type": "mqa"}, "step": 1}, path)
+    folder = str(tmp_path / "model")
+    assert convert_main([path, folder]) == 0
+    mc = ModelConfig.from_json(folder)
+    assert (mc.hidden_size, mc.rope_theta, mc.rms_norm_eps, mc.eos_token_id, mc.architecture) == (cfg["hidden_size"], 10000.0, 1e-5, 7, "mqa_gpt")
+    ec = EngineConfig(dtype="float32", device="cpu", use_cuda_graphs=False, cache=CacheConfig(block_size=8, num_gpu_blocks=20),
+                      sched=SchedulerConfig(max_num_seqs=2, max_num_batched_tokens=64))
+    eng = Engine.from_folder(folder, ec, ops=PlainOps())
+    from tiny_transformer_inference_engine_b200 import StepEntry
+    toks = [5, 900, 17, 3, 250, 1, 77]
+    eng.manager.admit("a")
+    eng.manager.extend("a", 0, len(toks))
+    got = eng.stepper.step([StepEntry("a", 0, toks, list(range(len(toks))))])
+    want = plain_forward(cfg, w, toks)
+    assert (got.cpu() - want).abs().max() < 1e-5 * want.abs().max()
+    # what cannot be converted says why
+    torch.save({"model": state}, path)
+    with pytest.raises(CheckpointError, match="missing model_config"):
+        convert_checkpoint(path, folder)
+    torch.save({"model_config": saved_cfg, "model": state, "quant_metadata": {"lm_head.weight": {}}}, path)
+    with pytest.raises(CheckpointError, match="quantized"):
+        convert_checkpoint(path, folder)
+    torch.save({"model_config": saved_cfg, "model": {k: v for k, v in state.items() if "gate_proj" not in k}}, path)
+    with pytest.raises(CheckpointError, match="gate_proj"):
+        convert_checkpoint(path, folder)
+    assert convert_main([str(tmp_path / "nothing.pt"), folder]) == 1
