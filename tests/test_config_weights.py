@@ -179,6 +179,11 @@ def test_reference_checkpoint_is_converted_to_a_model_folder(tmp_path):
     got = eng.stepper.step([StepEntry("a", 0, toks, list(range(len(toks))))])
     want = plain_forward(cfg, w, toks)
     assert (got.cpu() - want).abs().max() < 1e-5 * want.abs().max()
+    # the file itself is accepted where a folder is
+    eng2 = Engine.from_checkpoint(path, ec, ops=PlainOps())
+    eng2.manager.admit("a")
+    eng2.manager.extend("a", 0, len(toks))
+    assert torch.equal(eng2.stepper.step([StepEntry("a", 0, toks, list(range(len(toks))))]), got)
     # what cannot be converted says why
     torch.save({"model": state}, path)
     with pytest.raises(CheckpointError, match="missing model_config"):

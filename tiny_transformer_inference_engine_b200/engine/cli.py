@@ -5,7 +5,7 @@ Option names and meanings follow it where it has them: ``--tokens/--token`` (100
 ``--device`` (auto), ``--num-gpu-blocks`` (256), ``--block-size`` (16), ``--prompts`` for several
 requests at once (its ``--serving`` path; here every run goes through the scheduler).  Where the
 reference takes a checkpoint file (``--ckpt``), this takes a model folder (``--model``, or ``--ckpt``
-as an alias).  Prompts are token ids (``--prompt-ids 1,2,3``, repeatable) or, as in the reference,
+as an alias) or such a file, which is converted on the way in (``weights/convert.py``).  Prompts are token ids (``--prompt-ids 1,2,3``, repeatable) or, as in the reference,
 text (``--prompt "Once upon a time"``, repeatable), which is encoded and decoded with tiktoken's
 ``gpt2`` vocabulary (inference.py:256-269) if that package and its vocabulary file are there; without
 them ``--prompt`` is refused with a message and token ids remain.  ``--random-config`` makes a random-weights
@@ -21,7 +21,7 @@ import sys
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="tiny_transformer_inference_engine_b200", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--model", "--ckpt", dest="model", help="folder with config.json and *.safetensors")
+    ap.add_argument("--model", "--ckpt", dest="model", help="folder with config.json and *.safetensors, or a checkpoint file of the reference")
     ap.add_argument("--random-config", help="config.json for a model with random weights (see --seed)")
     ap.add_argument("--seed", type=int, default=0, help="seed of the random weights and of sampling")
     ap.add_argument("--prompt-ids", "--prompts", dest="prompt_ids", action="append", default=[],
@@ -92,7 +92,8 @@ def main(argv=None) -> int:
                       sched=SchedulerConfig(max_num_seqs=args.max_num_seqs,
                                             max_num_batched_tokens=args.max_num_batched_tokens))
     if args.model:
-        engine = Engine.from_folder(args.model, ec)
+        import os
+        engine = Engine.from_checkpoint(args.model, ec) if os.path.isfile(args.model) else Engine.from_folder(args.model, ec)
     else:
         engine = Engine.from_random(args.random_config, args.seed, ec)
     params = [SamplingParams(max_new_tokens=args.tokens, temperature=args.temperature, top_k=args.top_k,

@@ -97,6 +97,20 @@ class Engine:
         return cls(ModelConfig.from_json(folder), folder, _engine_config(engine_config, opts), ops)
 
     @classmethod
+    def from_checkpoint(cls, ckpt_path: str, engine_config: Optional[EngineConfig] = None, ops=None, **opts) -> "Engine":
+        """From a checkpoint file of the reference (inference.py:68-87): converted into a temporary model folder
+        (``weights/convert.py``), loaded from there, and the folder removed."""
+        import shutil
+        import tempfile
+        from ..weights.convert import convert_checkpoint
+        folder = tempfile.mkdtemp(prefix="ttie_model_")
+        try:
+            convert_checkpoint(ckpt_path, folder)
+            return cls.from_folder(folder, engine_config, ops, **opts)
+        finally:
+            shutil.rmtree(folder, ignore_errors=True)
+
+    @classmethod
     def from_random(cls, config: Union[ModelConfig, dict, str], seed: int = 0,
                     engine_config: Optional[EngineConfig] = None, ops=None, **opts) -> "Engine":
         if isinstance(config, str):
@@ -258,7 +272,10 @@ def _engine_config(engine_config: Optional[EngineConfig], opts: dict) -> EngineC
 
 # ------------------------------------------------------------------- the reference's names
 def load_model(path: str, device: str = "cuda:0", **opts) -> Engine:
-    """``inference.py:68`` takes a checkpoint file; this takes a model folder."""
+    """``inference.py:68`` takes a checkpoint file; this takes a model folder, or such a file."""
+    import os
+    if os.path.isfile(path):
+        return Engine.from_checkpoint(path, device=device, **opts)
     return Engine.from_folder(path, device=device, **opts)
 
 
