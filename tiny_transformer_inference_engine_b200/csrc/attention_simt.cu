@@ -189,12 +189,16 @@ paged_attn_simt_kernel(const AttnParams p) {
 
 // out[row] = sum_s exp(m_s - M) O_s / sum_s exp(m_s - M) l_s over the splits of the row.
 // One block per row: the first warp turns the (max, sum) pairs into one weight per split (kept in
-// shared memory), then every thread owns output columns and adds the splits' partial outputs with
-// independent loads.  The order of the additions is fixed.
+// shared memory); then the block's MERGE_GROUPS groups of threads each take every MERGE_GROUPS-th split - a thread
+// owns output columns and adds its splits' partial outputs with independent loads, so a row of a hundred splits costs
+// a few memory latencies, not a dozen - and the groups' sums are added in group order.  The order of the additions
+// is fixed.
+constexpr int MERGE_GROUPS = 4;
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, T* __restrict__ out,
                                   int num_splits, int D) {
-    extern __shared__ float wgt[];                                  // [num_splits]
+    extern __shared__ float wgt[];                                  // [num_splits], then the groups' sums [MERGE_GROUPS][D]
+    float* part = wgt + num_splits;
     TTIE_PDL_ENTRY();
     const size_t row = blockIdx.x;
     const float* ml = ws_ml + row * num_splits * 2;
@@ -219,10 +223,18 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
     }
     __syncthreads();
     const float* o = ws_o + row * num_splits * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const int cols = blockDim.x / MERGE_GROUPS, g = threadIdx.x / cols, c = threadIdx.x - g * cols;
+    for (int d = c; d < D; d += cols) {
         float acc = 0.f;
 #pragma unroll 8
-        for (int s = 0; s < num_splits; ++s) acc = fmaf(wgt[s], o[(size_t)s * D + d], acc);
+        for (int s = g; s < num_splits; s += MERGE_GROUPS) acc = fmaf(wgt[s], o[(size_t)s * D + d], acc);
+        part[g * D + d] = acc;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = part[d];
+#pragma unroll
+        for (int k = 1; k < MERGE_GROUPS; ++k) acc += part[k * D + d];
         out[row * D + d] = from_f32<T>(acc);
     }
 }
@@ -272,7 +284,8 @@ int attn_merge_bf16(const float* ws_o, const float* ws_ml, void* out, int rows, 
     } else if (num_splits <= 32) {
         TTIE_LAUNCH((attn_merge_small_kernel<__nv_bfloat16, 32>), grid, 128, 0, s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
     } else {
-        TTIE_LAUNCH(attn_merge_kernel<__nv_bfloat16>, rows, D >= 128 ? 128 : 64, num_splits * sizeof(float), s, ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
+        TTIE_LAUNCH(attn_merge_kernel<__nv_bfloat16>, rows, MERGE_GROUPS * (D >= 128 ? 128 : 64), (num_splits + MERGE_GROUPS * D) * sizeof(float), s,
+                    ws_o, ws_ml, (__nv_bfloat16*)out, num_splits, D);
     }
     TTIE_CHECK_LAUNCH("attention merge");
     return 0;
@@ -289,7 +302,8 @@ int launch(const AttnParams& p, int T_tokens, cudaStream_t s) {
     k<<<grid, WARPS * 32, smem, s>>>(p);
     TTIE_CHECK_LAUNCH("paged_attention");
     if (p.num_splits > 1) {
-        attn_merge_kernel<T><<<T_tokens * p.Hq, p.D >= 128 ? 128 : 64, p.num_splits * sizeof(float), s>>>(p.ws_o, p.ws_ml, (T*)p.out, p.num_splits, p.D);
+        attn_merge_kernel<T><<<T_tokens * p.Hq, MERGE_GROUPS * (p.D >= 128 ? 128 : 64), (p.num_splits + MERGE_GROUPS * p.D) * sizeof(float), s>>>(
+            p.ws_o, p.ws_ml, (T*)p.out, p.num_splits, p.D);
         TTIE_CHECK_LAUNCH("attention merge");
     }
     return 0;
