@@ -69,8 +69,13 @@ def test_add_rmsnorm(ops, dtype, wdtype, T, d, eps):
     assert rel(out.float().cpu(), exp.float()) < (1e-5 if dtype == "float32" else 8e-3)
 
 
-@pytest.mark.parametrize("M,N,K,bias", [(1, 7, 5, False), (33, 515, 96, True), (130, 64, 1000, False), (5, 200, 4544, True)])
+@pytest.mark.parametrize("M,N,K,bias", [(1, 7, 5, False), (33, 515, 96, True), (130, 64, 1000, False), (5, 200, 4544, True),
+                                        (16, 515, 96, True), (2, 50257, 512, False), (9, 33, 1000, True), (1, 3, 4, False), (17, 40, 64, False),
+                                        (32, 130, 512, True), (33, 130, 512, True)])
 def test_gemm_f32_is_true_32_bit(ops, M, N, K, bias):
+    """Both forms of the float32 product: up to 32 rows with aligned operands stream the weights (a warp per four weight
+    rows; 17 to 32 rows in two launches), everything else takes the 64 x 64 tile - including the strided, misaligned
+    view below."""
     g = torch.Generator().manual_seed(2)
     x, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
     b = torch.randn(N, generator=g) if bias else None

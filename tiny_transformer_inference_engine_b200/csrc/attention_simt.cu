@@ -34,10 +34,18 @@ struct AttnParams {
     float* ws_o; float* ws_ml;     // [T*Hq, num_splits, D] and [T*Hq, num_splits, 2]
 };
 
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
 template <typename T, int DPL>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attn_simt_kernel(const AttnParams p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int D = p.D, G = p.Hq / p.Hkv, KS = D + 4;
     float* Qs = smem;                       // [ROWS][D]
     float* Ks = Qs + ROWS * D;              // [BK][D+4]
@@ -98,17 +106,22 @@ paged_attn_simt_kernel(const AttnParams p) {
 
         for (int kt = k_lo; kt < k_hi; kt += BK) {
             __syncthreads();
-            for (int idx = threadIdx.x; idx < BK * D; idx += blockDim.x) {
-                const int j = idx / D, d = idx - j * D;
+            // four consecutive elements of a key and of a value per step (head sizes are multiples of 4): one page look-up
+            // and one 16-byte (float32) or 8-byte (bfloat16) load of each
+            const int D4 = D >> 2;
+            for (int idx = threadIdx.x; idx < BK * D4; idx += blockDim.x) {
+                const int j = idx / D4, d = (idx - j * D4) << 2;
                 const int key = kt + j;
-                float kval = 0.f, vval = 0.f;
+                float4 kval = make_float4(0.f, 0.f, 0.f, 0.f), vval = kval;
                 if (key < k_hi) {
-                    const int page = table[key / p.page_size];
-                    const int off = key - (key / p.page_size) * p.page_size;
+                    const int pg = key / p.page_size;
+                    const int page = table[pg];
+                    const int off = key - pg * p.page_size;
                     const size_t src = (((size_t)page * p.Hkv + kvh) * p.page_size + off) * D + d;
-                    kval = to_f32<T>(kp[src]); vval = to_f32<T>(vp[src]);
+                    kval = load4(kp + src); vval = load4(vp + src);
                 }
-                Ks[j * KS + d] = kval; Vs[j * KS + d] = vval;
+                *reinterpret_cast<float4*>(Ks + j * KS + d) = kval;
+                *reinterpret_cast<float4*>(Vs + j * KS + d) = vval;
             }
             __syncthreads();
 
