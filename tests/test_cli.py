@@ -65,3 +65,18 @@ def test_text_prompts_need_the_tokenizer(monkeypatch, capsys):
         with pytest.raises(SystemExit):
             main(["--model", "m", "--prompt", "Once upon a time"])
         assert seen == ["Once upon a time"] and "CUDA is unavailable" in capsys.readouterr().err
+
+
+@pytest.mark.gpu
+def test_ranges_around_the_operations_change_nothing(tmp_path):
+    """``TTIE_NVTX=1`` wraps every operation of the kernel library in a profiler range of its name; the tokens are the same."""
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(TINY_A))
+    cmd = [sys.executable, "-m", "tiny_transformer_inference_engine_b200", "--random-config", str(cfg), "--seed", "4",
+           "--prompt-ids", "1,2,3", "--tokens", "6", "--temperature", "0.9", "--top-k", "20", "--dtype", "float32", "--num-gpu-blocks", "16", "--ignore-eos"]
+    outs = []
+    for flag in ("0", "1"):
+        p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600, env=dict(os.environ, TTIE_NVTX=flag))
+        assert p.returncode == 0, p.stderr[-2000:]
+        outs.append(json.loads(p.stdout.strip())["generated_ids"])
+    assert outs[0] == outs[1] and len(outs[0]) == 6

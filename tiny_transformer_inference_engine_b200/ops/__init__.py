@@ -106,6 +106,8 @@ class CudaOps:
         self._product_choice = {}               # (N, K, row bucket) -> "skinny" | "library" for 9..64 rows (tune_products)
         self.product_timings = {}               # what tune_products measured: (N, K, rows) -> {"library": ms, "skinny": ms}
         self.lib.ttie_attn_tc_supported.restype = _c_int
+        if os.environ.get("TTIE_NVTX", "0") not in ("", "0"):
+            self._wrap_in_ranges()
         self._tc_pinned = torch.zeros(2, dtype=torch.int32).pin_memory()       # failure codes of the tcgen05 kernels, written by the device
         self._tc_words = self._tc_pinned.numpy()
         for i, name in enumerate(("ttie_gemm_tc_set_mirror", "ttie_attn_tc_set_mirror")):
@@ -117,6 +119,28 @@ class CudaOps:
             getattr(self.lib, name).restype = _c_int
 
     # ------------------------------------------------------------------ helpers
+    _RANGED = ("embed", "add_rmsnorm", "rmsnorm_rows", "linear", "linear_swiglu", "swiglu", "rope_table", "rope_store",
+               "paged_attention", "sample")
+
+    def _wrap_in_ranges(self):
+        """With ``TTIE_NVTX=1`` in the environment every operation below opens an NVTX range of its own name around its
+        launches, so a timeline of a step reads op by op (the reference marks the same places with
+        ``torch.profiler.record_function`` behind its ``PROFILE_REGIONS`` flag, models/mqa.py:14-18).  Off by
+        default: the step's host time is too short to spend on it unasked."""
+        push, pop = torch.cuda.nvtx.range_push, torch.cuda.nvtx.range_pop
+
+        def ranged(name, fn):
+            def call(*args, **kwargs):
+                push(name)
+                try:
+                    return fn(*args, **kwargs)
+                finally:
+                    pop()
+            return call
+
+        for name in self._RANGED:
+            setattr(self, name, ranged(name, getattr(self, name)))
+
     def _check(self, rc: int, what: str):
         if rc != 0:
             raise KernelError(f"{what}: {self.lib.ttie_last_error().decode()}")
