@@ -278,8 +278,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
     if (warp == 0 && AHEAD) {
         // Prompt portions.  The whole warp walks the tiles: lane b looks up the page of box b (a
-        // tile is 128 / box_rows boxes) one tile ahead, so the table's latency hides behind the waits; lane 0
-        // waits for the stages and issues the copies.
+        // tile is 128 / box_rows boxes) one tile ahead, so the table's latency hides behind the waits, and issues
+        // that box's copies; lane 0 waits for the stages.
         const int ps = p.page_size;
         const int box_rows = ps < BN ? ps : BN, nboxes = BN / box_rows;
         const int* table = p.block_table + (size_t)seq * p.table_width;
@@ -302,86 +302,79 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             if (lane == 0) ok = mbar_wait_relaxed(BAR(KE + st), par, 1);
             if (!__shfl_sync(0xffffffffu, ok, 0)) break;
             if (lane == 0) mbar_expect_tx(BAR(KF + st), KV_BYTES);
-            for (int b = 0; b < nboxes; ++b) {
-                const int y = __shfl_sync(0xffffffffu, y_cur, b);
-                if (lane == 0) {
+            __syncwarp();
+            if (lane < nboxes) {
 #pragma unroll
-                    for (int cb = 0; cb < CB; ++cb)
-                        tma_load_2d(smem_u32(Ks + st * KV_BYTES + cb * KVBLK + b * box_rows * 128), &tmK, BAR(KF + st), cb * 64, y);
-                }
+                for (int cb = 0; cb < CB; ++cb)
+                    tma_load_2d(smem_u32(Ks + st * KV_BYTES + cb * KVBLK + lane * box_rows * 128), &tmK, BAR(KF + st), cb * 64, y_cur);
             }
             if (lane == 0) ok = mbar_wait_relaxed(BAR(VE + st), par, 2);
             if (!__shfl_sync(0xffffffffu, ok, 0)) break;
             if (lane == 0) mbar_expect_tx(BAR(VF + st), KV_BYTES);
-            for (int b = 0; b < nboxes; ++b) {
-                const int y = __shfl_sync(0xffffffffu, y_cur, b);
-                if (lane == 0) {
+            __syncwarp();
+            if (lane < nboxes) {
 #pragma unroll
-                    for (int cb = 0; cb < CB; ++cb)
-                        tma_load_2d(smem_u32(Vs + st * KV_BYTES + cb * KVBLK + b * box_rows * 128), &tmV, BAR(VF + st), cb * 64, y);
-                }
+                for (int cb = 0; cb < CB; ++cb)
+                    tma_load_2d(smem_u32(Vs + st * KV_BYTES + cb * KVBLK + lane * box_rows * 128), &tmV, BAR(VF + st), cb * 64, y_cur);
             }
             y_cur = y_next;
         }
     } else if (warp == 0 && !AHEAD) {
-        // Few rows (decode steps, where the softmax threads set the pace): one thread looks pages up as it goes,
-        // which spaces the copies out; measured faster there than asking for both stages at once.
+        // Few rows (decode steps).  Lane b owns box b of a tile (a tile is 128 / box_rows boxes, 16 of them with 8-key
+        // pages): it looks the box's page up - one coalesced read of the table for the whole tile, ahead of the wait for
+        // the stage - and issues the box's copies itself, for the keys and then, from the same look-up, for the values.
+        // (One thread that looked up and issued box after box took 7,400 clocks per 128-key tile with 16-key pages.)
+        const int ps = p.page_size;
+        const int box_rows = ps < BN ? ps : BN, nboxes = BN / box_rows;
+        const int* table = p.block_table + (size_t)seq * p.table_width;
+        auto box_row = [&](int j) -> int {                      // first row of this lane's box of tile j in the page matrix
+            int y = 0;
+            if (lane < nboxes && j < ntiles) {
+                const int key = (t_begin + j) * BN + lane * box_rows;
+                const int pg = key / ps;
+                const int page = pg < p.table_width ? table[pg] : 0;
+                y = (page * p.Hkv + kvh) * ps + (key - pg * ps);
+            }
+            return y;
+        };
         {
             // the first two tiles (both stages are free): their pages were looked up while the queries were staged
-            const int ps0 = p.page_size;
-            const int box_rows0 = ps0 < BN ? ps0 : BN, nboxes0 = BN / box_rows0;
+            // (lane = tile * boxes + box)
+            const int jt = lane / nboxes, bx = lane - jt * nboxes;
             for (int j = 0; j < 2 && j < ntiles; ++j) {
-                if (lane == 0) mbar_expect_tx(BAR(KF + j), KV_BYTES);
-                for (int b = 0; b < nboxes0; ++b) {
-                    const int yy = __shfl_sync(0xffffffffu, y_first, j * nboxes0 + b);
-                    if (lane == 0) {
+                if (lane == 0) { mbar_expect_tx(BAR(KF + j), KV_BYTES); mbar_expect_tx(BAR(VF + j), KV_BYTES); }
+                __syncwarp();
+                if (jt == j) {
 #pragma unroll
-                        for (int cb = 0; cb < CB; ++cb)
-                            tma_load_2d(smem_u32(Ks + j * KV_BYTES + cb * KVBLK + b * box_rows0 * 128), &tmK, BAR(KF + j), cb * 64, yy);
-                    }
-                }
-                if (lane == 0) mbar_expect_tx(BAR(VF + j), KV_BYTES);
-                for (int b = 0; b < nboxes0; ++b) {
-                    const int yy = __shfl_sync(0xffffffffu, y_first, j * nboxes0 + b);
-                    if (lane == 0) {
+                    for (int cb = 0; cb < CB; ++cb)
+                        tma_load_2d(smem_u32(Ks + j * KV_BYTES + cb * KVBLK + bx * box_rows * 128), &tmK, BAR(KF + j), cb * 64, y_first);
 #pragma unroll
-                        for (int cb = 0; cb < CB; ++cb)
-                            tma_load_2d(smem_u32(Vs + j * KV_BYTES + cb * KVBLK + b * box_rows0 * 128), &tmV, BAR(VF + j), cb * 64, yy);
-                    }
+                    for (int cb = 0; cb < CB; ++cb)
+                        tma_load_2d(smem_u32(Vs + j * KV_BYTES + cb * KVBLK + bx * box_rows * 128), &tmV, BAR(VF + j), cb * 64, y_first);
                 }
             }
         }
-        if (lane == 0) {
-            const int ps = p.page_size;
-            const int box_rows = ps < BN ? ps : BN;
-            const int* table = p.block_table + (size_t)seq * p.table_width;
-            for (int j = 2; j < ntiles; ++j) {
-                const int st = j % NST;
-                const uint32_t par = ((j / NST) & 1) ^ 1;
-                const int key0 = (t_begin + j) * BN;
-                if (!mbar_wait(BAR(KE + st), par, 1)) break;
-                mbar_expect_tx(BAR(KF + st), KV_BYTES);
-                for (int kk = 0; kk < BN; kk += box_rows) {
-                    const int key = key0 + kk;
-                    const int pg = key / ps;
-                    const int page = pg < p.table_width ? table[pg] : 0;
-                    const int y = (page * p.Hkv + kvh) * ps + (key - pg * ps);
+        int y_cur = box_row(2);
+        for (int j = 2; j < ntiles; ++j) {
+            const int y_next = box_row(j + 1);
+            const int st = j % NST;
+            const uint32_t par = ((j / NST) & 1) ^ 1;
+            int ok = 1;
+            if (lane == 0) { ok = mbar_wait(BAR(KE + st), par, 1); if (ok) mbar_expect_tx(BAR(KF + st), KV_BYTES); }
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            if (lane < nboxes) {
 #pragma unroll
-                    for (int cb = 0; cb < CB; ++cb)
-                        tma_load_2d(smem_u32(Ks + st * KV_BYTES + cb * KVBLK + kk * 128), &tmK, BAR(KF + st), cb * 64, y);
-                }
-                if (!mbar_wait(BAR(VE + st), par, 2)) break;
-                mbar_expect_tx(BAR(VF + st), KV_BYTES);
-                for (int kk = 0; kk < BN; kk += box_rows) {
-                    const int key = key0 + kk;
-                    const int pg = key / ps;
-                    const int page = pg < p.table_width ? table[pg] : 0;
-                    const int y = (page * p.Hkv + kvh) * ps + (key - pg * ps);
-#pragma unroll
-                    for (int cb = 0; cb < CB; ++cb)
-                        tma_load_2d(smem_u32(Vs + st * KV_BYTES + cb * KVBLK + kk * 128), &tmV, BAR(VF + st), cb * 64, y);
-                }
+                for (int cb = 0; cb < CB; ++cb)
+                    tma_load_2d(smem_u32(Ks + st * KV_BYTES + cb * KVBLK + lane * box_rows * 128), &tmK, BAR(KF + st), cb * 64, y_cur);
             }
+            if (lane == 0) { ok = mbar_wait(BAR(VE + st), par, 2); if (ok) mbar_expect_tx(BAR(VF + st), KV_BYTES); }
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            if (lane < nboxes) {
+#pragma unroll
+                for (int cb = 0; cb < CB; ++cb)
+                    tma_load_2d(smem_u32(Vs + st * KV_BYTES + cb * KVBLK + lane * box_rows * 128), &tmV, BAR(VF + st), cb * 64, y_cur);
+            }
+            y_cur = y_next;
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -883,8 +876,8 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory");
         if (warp == 12) {
             // ------------------------------------------------------------ copy producer: K0 K1 V0 K2 V1 K3 ... through the ring.
-            // Lane x looks up the page of box x of a tile (a tile is 64 / box_rows boxes) ahead of its use; lane 0 waits
-            // for the stage and issues the copies.
+            // Lane x looks up the page of box x of a tile (a tile is 64 / box_rows boxes) ahead of its use and issues that
+            // box's copies; lane 0 waits for the stage.
             const int ps = p.page_size;
             const int box_rows = ps < BNK ? ps : BNK, nboxes = BNK / box_rows;
             const int* table = p.block_table + (size_t)seq * p.table_width;
@@ -905,13 +898,11 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 if (lane == 0) ok = mbar_wait_relaxed(BAR(PP_EMPTY + st), ((it / NSD) & 1) ^ 1, code);
                 if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
                 if (lane == 0) mbar_expect_tx(BAR(PP_FULL + st), KV_BYTES);
-                for (int x = 0; x < nboxes; ++x) {
-                    const int y = __shfl_sync(0xffffffffu, y_lane, x);
-                    if (lane == 0) {
+                __syncwarp();
+                if (lane < nboxes) {                                // every lane issues the copies of its own box
 #pragma unroll
-                        for (int cb = 0; cb < CB; ++cb)
-                            tma_load_2d(smem_u32(ring + st * KV_BYTES + cb * KVBLK + x * box_rows * 128), map, BAR(PP_FULL + st), cb * 64, y);
-                    }
+                    for (int cb = 0; cb < CB; ++cb)
+                        tma_load_2d(smem_u32(ring + st * KV_BYTES + cb * KVBLK + lane * box_rows * 128), map, BAR(PP_FULL + st), cb * 64, y_lane);
                 }
                 ++it;
                 return true;
