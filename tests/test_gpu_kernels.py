@@ -321,6 +321,32 @@ def test_refuses_sizes_it_cannot_take(ops):
                                     torch.zeros(1, 2, dtype=torch.float32, device=DEV))
 
 
+def test_a_block_table_that_cannot_cover_the_keys_is_refused(ops):
+    q = torch.zeros(1, 4 * 64, dtype=torch.bfloat16, device=DEV)
+    pages = torch.zeros(4, 1, 16, 64, dtype=torch.bfloat16, device=DEV)
+    table = torch.ones(1, 2, dtype=torch.int32, device=DEV)                 # two pages of 16 keys
+    qsl = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    lens = torch.tensor([40], dtype=torch.int32, device=DEV)
+    from tiny_transformer_inference_engine_b200.ops import KernelError
+    with pytest.raises(KernelError, match="cannot cover 40 keys"):
+        ops.paged_attention(q, 4, 1, 64, pages, pages, table, 16, qsl, lens, 1, 1, 40, 0.125, 0, torch.empty_like(q))
+
+
+def test_many_requests_with_grouped_kv_heads_are_cut_into_pieces(ops):
+    """Decode steps whose (request, kv head) pairs alone fill the GPU: the tile loop is planned as CTAs of at
+    least 512 keys (2,000 to 4,000 of them), and the pieces merge to the float32 reference."""
+    assert ops.attention_plan(torch.bfloat16, 64, 32, 8, 128, 1, 4096, 64) == ("mma", 8, 512)
+    assert ops.attention_plan(torch.bfloat16, 32, 32, 8, 128, 1, 4096, 64) == ("mma", 8, 512)
+    assert ops.attention_plan(torch.bfloat16, 128, 32, 8, 128, 1, 2048, 64) == ("mma", 4, 512)
+    assert ops.attention_plan(torch.bfloat16, 64, 16, 16, 64, 1, 4096, 64) == ("mma", 4, 1024)
+    assert ops.attention_plan(torch.bfloat16, 512, 32, 8, 128, 1, 4096, 64) == ("mma", 1, 0)        # 4,096 pairs: enough as they are
+    seqs = [(1500 - 37 * i, 1) for i in range(24)]
+    plan = ops.attention_plan(torch.bfloat16, len(seqs), 32, 8, 128, 1, 1500, 64)
+    assert plan == ("mma", 2, 768)
+    out, exp, _, _ = attention_case(ops, "bfloat16", 32, 8, 128, 64, seqs, plan=plan)
+    assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
+
+
 # ------------------------------------------------------------------------------------------ sampling
 def sampler_state(rows):
     st = torch.zeros(len(rows), 8, dtype=torch.int32)

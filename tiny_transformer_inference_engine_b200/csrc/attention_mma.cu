@@ -131,7 +131,7 @@ paged_attn_mma_kernel(const MmaParams p) {
             long long off = -1;
             if (key < k_hi) {
                 const int pg = key / p.page_size;
-                const int page = table[pg];
+                const int page = pg < p.table_width ? table[pg] : 0;             // (a table that is too short: the scratch page, not a wild read)
                 off = (((long long)page * p.Hkv + kvh) * p.page_size + (key - pg * p.page_size)) * D;
             }
             rowoff[stage * BN + j] = off;
@@ -437,7 +437,7 @@ paged_attn_cluster_kernel(const MmaParams p) {
             off[i] = NO_ROW;
             if (key < k_hi) {
                 const int pg = key / p.page_size;
-                const int page = pages ? pages[i] : table[pg];
+                const int page = pages ? pages[i] : (pg < p.table_width ? table[pg] : 0);
                 off[i] = ((unsigned)page * (unsigned)p.Hkv + (unsigned)kvh) * (unsigned)p.page_size + (unsigned)(key - pg * p.page_size);
             }
         }

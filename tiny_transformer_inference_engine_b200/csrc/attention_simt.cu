@@ -115,7 +115,7 @@ paged_attn_simt_kernel(const AttnParams p) {
                 float4 kval = make_float4(0.f, 0.f, 0.f, 0.f), vval = kval;
                 if (key < k_hi) {
                     const int pg = key / p.page_size;
-                    const int page = table[pg];
+                    const int page = pg < p.table_width ? table[pg] : 0;         // (a table that is too short: the scratch page, not a wild read)
                     const int off = key - pg * p.page_size;
                     const size_t src = (((size_t)page * p.Hkv + kvh) * p.page_size + off) * D + d;
                     kval = load4(kp + src); vval = load4(vp + src);
