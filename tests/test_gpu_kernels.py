@@ -502,6 +502,29 @@ def test_skinny_gemm_all_epilogues(ops, M, N, K):
     ops.skinny_max_rows = 8
 
 
+def test_swiglu_product_for_few_rows_is_chosen_by_measurement(ops):
+    """Up to 8 rows the gate/up product carries SwiGLU in its epilogue or runs K-split-free and hands over to the
+    activation kernel, whichever measured faster for the shape at its first use; both give the reference's values."""
+    g = torch.Generator().manual_seed(5)
+    for F, K in ((1024, 8192), (2752, 1024)):
+        x = torch.randn(8, K, generator=g).bfloat16()
+        w = (torch.randn(2 * F, K, generator=g) * 0.02).bfloat16()
+        gu = x.double() @ w.double().T
+        ref = gu[:, :F] * torch.sigmoid(gu[:, :F]) * gu[:, F:]
+        xd, wd = x.to(DEV), w.to(DEV)
+        ops._swiglu_choice.pop((F, K, "few"), None)
+        act = ops.linear_swiglu(xd, wd, None, F)
+        took = ops.product_timings[("swiglu", F, K, "few")]
+        assert set(took) == {"fused", "unfused"} and ops._swiglu_choice[(F, K, "few")] == (took["fused"] <= 1.03 * took["unfused"])
+        assert rel(act.float().cpu(), ref) < 1.2e-2
+        for forced in (True, False):                                   # both forms, whatever was measured
+            ops._swiglu_choice[(F, K, "few")] = forced
+            assert rel(ops.linear_swiglu(xd, wd, None, F).float().cpu(), ref) < 1.2e-2
+        del ops._swiglu_choice[(F, K, "few")]
+    # 64 CTAs of 512 KB each against a product cut over K: the fused form loses by far on such a shape
+    assert ops.product_timings[("swiglu", 1024, 8192, "few")]["unfused"] < ops.product_timings[("swiglu", 1024, 8192, "few")]["fused"]
+
+
 def test_partial_sums_feed_norm_and_rope(ops):
     g = torch.Generator().manual_seed(7)
     S, T, d = 3, 5, 200

@@ -368,16 +368,58 @@ class CudaOps:
         """silu(x @ Wg.T) * (x @ Wu.T) with w_gu = [Wg; Wu] ([2*hidden, K]) -> [M, hidden]."""
         M, K = x.shape
         act = torch.empty((M, hidden), dtype=x.dtype, device=x.device)
-        if self._skinny_ok(x, w_gu):
-            self._check(self.lib.ttie_skinny_gemm(_ptr(x), x.stride(0), _ptr(w_gu), w_gu.stride(0), _ptr(b_gu), _ptr(act),
-                                                  hidden, M, hidden, K, math.ceil(K / 128) * 128, 2, hidden,
-                                                  self._stream(x)), "skinny_gemm_swiglu")
-            self.launches += 1
-            return act
+        if self._skinny_ok(x, w_gu) and self._fused_few_rows_wins(x, w_gu, b_gu, hidden):
+            return self._linear_swiglu_skinny(x, w_gu, b_gu, hidden, act)
         if M >= 1024 and x.dtype == torch.bfloat16 and self._skinny_shape_ok(x, w_gu) and self._fused_swiglu_wins(x, w_gu, b_gu, hidden):
             return self.linear_swiglu_tc_pair(x, w_gu, b_gu, hidden)
         self.swiglu(self.linear(x, w_gu, b_gu), act)
         return act
+
+    def _linear_swiglu_skinny(self, x, w_gu, b_gu, hidden, act):
+        M, K = x.shape
+        self._check(self.lib.ttie_skinny_gemm(_ptr(x), x.stride(0), _ptr(w_gu), w_gu.stride(0), _ptr(b_gu), _ptr(act),
+                                              hidden, M, hidden, K, math.ceil(K / 128) * 128, 2, hidden,
+                                              self._stream(x)), "skinny_gemm_swiglu")
+        self.launches += 1
+        return act
+
+    def _graph_time(self, fn, iters=8) -> float:
+        """Milliseconds of one replay of a graph of ``iters`` calls of ``fn`` (after two plain calls)."""
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                fn()
+        g.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize(self.device)
+        return a.elapsed_time(b)
+
+    def _fused_few_rows_wins(self, x, w_gu, b_gu, hidden) -> bool:
+        """Up to 8 rows: whether the weight-streaming product with SwiGLU in its epilogue beats the same product without
+        it followed by the activation kernel.  The fused form cannot cut K over CTAs (the activation needs whole sums),
+        so it has hidden / 16 CTAs: at the Llama-2-7B widths (688 CTAs) it is 8 % ahead, at a feed-forward width of
+        2,048 to 4,096 behind a model width of 4,096 to 8,192 it is 15-40 % behind.  Measured per shape the first time
+        it is met outside a graph capture (a step that meets a new batch bucket runs plainly once before it is
+        captured), as a replayed graph of eight launches each."""
+        key = (hidden, x.shape[1], "few")
+        choice = self._swiglu_choice.get(key)
+        if choice is None:
+            if torch.cuda.is_current_stream_capturing():
+                return True
+            launches = self.launches
+            act = torch.empty((x.shape[0], hidden), dtype=x.dtype, device=x.device)
+            took = {"fused": self._graph_time(lambda: self._linear_swiglu_skinny(x, w_gu, b_gu, hidden, act)),
+                    "unfused": self._graph_time(lambda: self.swiglu(self.linear(x, w_gu, b_gu), act))}
+            self.launches = launches
+            choice = self._swiglu_choice[key] = took["fused"] <= 1.03 * took["unfused"]
+            self.product_timings[("swiglu",) + key] = took
+        return choice
 
     def _fused_swiglu_wins(self, x, w_gu, b_gu, hidden) -> bool:
         """Whether, for portions of this many rows, the gate/up product with SwiGLU in its epilogue (this package's
