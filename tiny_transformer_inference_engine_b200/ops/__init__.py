@@ -102,7 +102,7 @@ class CudaOps:
         self.attn_tc_min_split = 256            # keys per CTA from which the tcgen05 kernel splits a decode step's key range
         self.attn_tcpp_min_split = 1024         # keys per CTA below which a prompt portion's key range is not cut
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
-        self.skinny_max_rows = 8                # rows up to which the weight-streaming product always replaces the library's
+        self.skinny_max_rows = 8                # rows up to which the weight-streaming product is the rule (tune_products may hand a shape to the library)
         self._swiglu_choice = {}                # (F, K, row bucket) -> True where the fused tcgen05 gate/up + SwiGLU kernel measured faster
         self._product_choice = {}               # (N, K, row bucket) -> "skinny" | "library" for 9..64 rows (tune_products)
         self.product_timings = {}               # what tune_products measured: (N, K, rows) -> {"library": ms, "skinny": ms}
@@ -217,6 +217,8 @@ class CudaOps:
         M = x.shape[0]
         if M > self.skinny_max_rows and not (M <= 64 and self._product_choice.get((w.shape[0], w.shape[1], _row_bucket(M))) == "skinny"):
             return False
+        if M <= self.skinny_max_rows and self._product_choice.get((w.shape[0], w.shape[1], 8)) == "library":
+            return False
         return (x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
                 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
@@ -226,13 +228,15 @@ class CudaOps:
         [2048, 16384] it leaves half of the memory bandwidth unused).  So each distinct bfloat16 matrix shape of a
         model is timed once per row bucket (16, 32, 64) with both, as a replayed graph of ``iters`` launches
         that rotate over the model's matrices of that shape, and the faster one is remembered.  Small matrices
-        (under 4 Mi elements) are left to the library."""
+        (under 4 Mi elements) are left to the library.  Up to 8 rows the weight-streaming product is the rule and
+        is ahead on most shapes, by up to 3x on narrow deep ones; the same measurement at 8 rows hands a shape to
+        the library where that is more than 5 % faster (measured: [10240, 8192] and [8192, 28672] by 9-10 %)."""
         groups, launches = {}, self.launches
         for w in weights:
             if w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1 and w.shape[0] * w.shape[1] >= (4 << 20):
                 groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
         for (N, K), ws in groups.items():
-            for M in (16, 32, 64):
+            for M in (8, 16, 32, 64):
                 if (N, K, M) in self._product_choice:
                     continue
                 x = torch.randn(M, K, device=self.device).to(torch.bfloat16)
@@ -257,7 +261,10 @@ class CudaOps:
                     torch.cuda.synchronize(self.device)
                     took[kind] = a.elapsed_time(b)
                     del g
-                self._product_choice[(N, K, M)] = "skinny" if took["skinny"] < 0.97 * took["library"] else "library"
+                if M == 8:      # up to 8 rows the weight-streaming product is the rule; the library takes a shape only where it is clearly ahead
+                    self._product_choice[(N, K, M)] = "library" if took["library"] < 0.95 * took["skinny"] else "skinny"
+                else:
+                    self._product_choice[(N, K, M)] = "skinny" if took["skinny"] < 0.97 * took["library"] else "library"
                 self.product_timings[(N, K, M)] = took
         self.launches = launches
 
