@@ -622,12 +622,17 @@ def test_tcgen05_splits_one_key_decides(ops, kpos):
 
 
 def test_decode_form_is_planned(ops):
-    """Decode steps of the bfloat16 path take the decode form while a warp has one key tile to walk; longer
-    contexts take the tile loop with splits, prompt portions the tcgen05 kernel or the tile loop."""
-    kernel, C, split_len = ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 2048, 64)
+    """Decode steps of the bfloat16 path take the tcgen05 kernel with the key range cut over CTAs where a request brings
+    16 rows or more per kv head at head size 64 or 128; with fewer rows or another head size the decode form while a
+    warp has one key tile to walk, and the tile loop with splits beyond; prompt portions the tcgen05 kernels or the tile loop."""
+    kernel, n, split_len = ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 2048, 64)
+    assert kernel == "tc" and n * split_len >= 2048 and 8 * n <= 148
+    assert ops.attention_plan(torch.bfloat16, 64, 32, 1, 128, 1, 256, 64) == ("tc", 1, 0)
+    kernel, C, split_len = ops.attention_plan(torch.bfloat16, 8, 8, 1, 128, 1, 2048, 64)          # 8 rows per request
     assert kernel == "mma_c4" and C * split_len >= 2048 and C & (C - 1) == 0 and split_len <= 256
+    assert ops.attention_plan(torch.bfloat16, 8, 32, 1, 96, 1, 2048, 64)[0] == "mma_c4"           # a head size the tcgen05 kernel does not take
     assert ops.attention_plan(torch.bfloat16, 3, 4, 2, 64, 1, 100, 16)[0] == "mma_c2"
-    assert ops.attention_plan(torch.bfloat16, 64, 32, 1, 128, 1, 256, 64) == ("mma_c4", 1, 256)
+    assert ops.attention_plan(torch.bfloat16, 64, 8, 1, 128, 1, 256, 64) == ("mma_c4", 1, 256)
     kernel, n, split_len = ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 32768, 64)
     assert kernel == "tc" and n * split_len >= 32768 and split_len % 128 == 0 and 8 * n <= 148
     assert ops.attention_plan(torch.bfloat16, 8, 32, 1, 96, 1, 32768, 64)[0] == "mma"       # a head size the tcgen05 kernel does not take

@@ -95,8 +95,9 @@ paged_attn_mma_kernel(const MmaParams p) {
     int k_hi = ctx + tok_hi + 1;
     int k_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
     if (p.num_splits > 1) {
-        k_lo = max(k_lo, split * p.split_len);
-        k_hi = min(k_hi, (split + 1) * p.split_len);
+        const int piece = piece_len(kv_len, p.num_splits, p.split_len, BN);
+        k_lo = max(k_lo, split * piece);
+        k_hi = min(k_hi, (split + 1) * piece);
     }
     k_lo = k_lo / BN * BN;                                                          // tiles start on multiples of BN
 

@@ -199,8 +199,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
     const int split = blockIdx.y;
     if (p.num_splits > 1) {                                      // splits start on tile boundaries
-        key_lo = max(key_lo, split * p.split_len);
-        key_hi = min(key_hi, (split + 1) * p.split_len);
+        const int piece = piece_len(kv_len, p.num_splits, p.split_len, BN);
+        key_lo = max(key_lo, split * piece);
+        key_hi = min(key_hi, (split + 1) * piece);
     }
     const int t_begin = key_lo / BN, t_end = (key_hi + BN - 1) / BN;
     const int ntiles = t_end - t_begin;
@@ -657,8 +658,9 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
     const int split = blockIdx.y;
     if (p.num_splits > 1) {
-        key_lo = max(key_lo, split * p.split_len);
-        key_hi = min(key_hi, (split + 1) * p.split_len);
+        const int piece = piece_len(kv_len, p.num_splits, p.split_len, BN);
+        key_lo = max(key_lo, split * piece);
+        key_hi = min(key_hi, (split + 1) * piece);
     }
     const int t_begin = key_lo / BNK, t_end = (key_hi + BNK - 1) / BNK;
     const int nsteps = t_end - t_begin;

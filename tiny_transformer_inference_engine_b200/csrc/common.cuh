@@ -28,6 +28,15 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // first statement of a kernel: wait for the predecessor's results, then let the successor be scheduled
 #define TTIE_PDL_ENTRY() do { ::ttie::pdl_wait(); ::ttie::pdl_launch_dependents(); } while (0)
 
+// Keys per piece for a request of kv_len keys, in a step that was planned as num_splits pieces of split_len keys for its
+// longest request (or for the longest a captured graph may meet): an even share of the request's own keys, rounded up
+// to the kernel's tile, never more than planned.  So every request spreads over all the CTAs it was given, whatever its
+// length, and a graph planned for 8,192 keys does not walk a 4,096-key request with half of its CTAs.
+__device__ __forceinline__ int piece_len(int kv_len, int num_splits, int split_len, int granule) {
+    const int share = ((kv_len + num_splits - 1) / num_splits + granule - 1) / granule * granule;
+    return min(split_len, max(share, granule));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
