@@ -628,6 +628,8 @@ def test_decode_form_is_planned(ops):
     kernel, n, split_len = ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 2048, 64)
     assert kernel == "tc" and n * split_len >= 2048 and 8 * n <= 148
     assert ops.attention_plan(torch.bfloat16, 64, 32, 1, 128, 1, 256, 64) == ("tc", 1, 0)
+    assert ops.attention_plan(torch.bfloat16, 256, 32, 1, 128, 1, 4096, 64) == ("tc", 1, 0)       # more requests than SMs: uncut, wave after wave
+    assert ops.attention_plan(torch.bfloat16, 512, 32, 1, 128, 1, 512, 64)[0] == "mma"            # ... unless the requests are short
     kernel, C, split_len = ops.attention_plan(torch.bfloat16, 8, 8, 1, 128, 1, 2048, 64)          # 8 rows per request
     assert kernel == "mma_c4" and C * split_len >= 2048 and C & (C - 1) == 0 and split_len <= 256
     assert ops.attention_plan(torch.bfloat16, 8, 32, 1, 96, 1, 2048, 64)[0] == "mma_c4"           # a head size the tcgen05 kernel does not take

@@ -577,13 +577,17 @@ class CudaOps:
         """The tcgen05 kernel for steps with few query rows per request and contexts too long for the decode
         form: one wave of CTAs (the kernel takes a whole SM), each walking at least 256 keys; the merge
         kernel adds the pieces.  None where the head or page size is not the kernel's, the rows exceed one
-        128-row tile or fill less than an eighth of it (the mma.sync kernel's 16-row tiles waste less there), or
-        the requests alone fill the GPU."""
+        128-row tile or fill less than an eighth of it (the mma.sync kernel's 16-row tiles waste less there).  With more
+        requests than SMs it runs uncut."""
         rows = max_q_len * (num_heads // num_kv_heads)
         base = num_seqs * num_kv_heads
-        if (page_size is None or rows > 128 or rows < 16 or base > self.num_sms or head_dim > 128
+        if (page_size is None or rows > 128 or rows < 16 or head_dim > 128
                 or not self.lib.ttie_attn_tc_supported(head_dim, page_size)):
             return None
+        if base > self.num_sms:
+            # more requests than SMs: one CTA per request, wave after wave, while a request has a thousand keys or more
+            # (256 requests at 4,096 keys: 105 us against 143 for the tile loop in 8 pieces; at 512 keys the tile loop is ahead)
+            return ("tc", 1, 0) if max_kv_len >= 1024 else None
         n = max(1, min(self.num_sms // base, math.ceil(max_kv_len / self.attn_tc_min_split)))
         split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
         n = math.ceil(max_kv_len / split_len)
