@@ -321,6 +321,32 @@ def test_refuses_sizes_it_cannot_take(ops):
                                     torch.zeros(1, 2, dtype=torch.float32, device=DEV))
 
 
+def test_split_decode_attention_in_many_waves_never_waits_in_vain(ops):
+    """600 CTAs of six key tiles each, launch after launch: a CTA that starts while the memory system is busy gets its
+    value tiles late, and the softmax threads then finish two tiles before the issuing thread has looked at the first.
+    With one barrier for "P is written" that looked like no arrival at all and the wait ran out (a second later, with a
+    wrong result); the barrier exists per score buffer now.  No wait may run out in 1,500 launches."""
+    B, ctx, Hq, D, page = 100, 4096, 32, 128, 64
+    pages = ctx // page
+    g = torch.Generator().manual_seed(1)
+    kp = torch.randn(B * pages + 1, 1, page, D, generator=g).bfloat16().to(DEV)
+    vp = torch.randn(B * pages + 1, 1, page, D, generator=g).bfloat16().to(DEV)
+    table = (torch.arange(B * pages, dtype=torch.int32) + 1).view(B, pages).to(DEV)
+    q = torch.randn(B, Hq * D, generator=g).bfloat16().to(DEV)
+    qsl = torch.arange(B + 1, dtype=torch.int32).to(DEV)
+    lens = torch.full((B,), ctx, dtype=torch.int32).to(DEV)
+    out = torch.empty_like(q)
+    for i in range(1500):
+        ops.paged_attention(q, Hq, 1, D, kp, vp, table, page, qsl, lens, B, 1, ctx, 1 / math.sqrt(D), 0, out, plan=("tc", 6, 768))
+    torch.cuda.synchronize()
+    assert ops.tc_error() == 0
+    r = 7                                                            # one request against the float32 formula
+    k = kp[1 + r * pages:1 + (r + 1) * pages, 0].reshape(ctx, D).float()
+    v = vp[1 + r * pages:1 + (r + 1) * pages, 0].reshape(ctx, D).float()
+    p = torch.softmax(q[r].view(Hq, D).float() @ k.T / math.sqrt(D), dim=-1)
+    assert rel(out[r].view(Hq, D).float().cpu(), (p @ v).cpu()) < TOL["bfloat16"]
+
+
 def test_a_block_table_that_cannot_cover_the_keys_is_refused(ops):
     q = torch.zeros(1, 4 * 64, dtype=torch.bfloat16, device=DEV)
     pages = torch.zeros(4, 1, 16, 64, dtype=torch.bfloat16, device=DEV)

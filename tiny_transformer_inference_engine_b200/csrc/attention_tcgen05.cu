@@ -165,9 +165,13 @@ constexpr int NTHREADS = 64 + NP * 128;
 template <int D, bool AHEAD, int NST>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
-    // barrier slots: key / value stages full and empty, score and output buffers full and empty, P written, exchanges
+    // barrier slots: key / value stages full and empty, score and output buffers full and empty, P written, exchanges.
+    // Every barrier that counts thread arrivals exists twice, by tile parity: the softmax threads write P of tile j + 1
+    // (into the other score buffer) before they wait for the product of tile j, so they can arrive for two tiles in a
+    // row while the issuing thread still waits for a late value tile - on a single barrier two completed phases look
+    // like none, and that wait ran out (seen once in several thousand launches of 600 CTAs).
     constexpr int KF = 0, KE = NST, VF = 2 * NST, VE = 3 * NST, SF = 4 * NST, SE = SF + 2, OF = SE + 2, OE = OF + 2, PF = OE + 2,
-                  XB = PF + 1, XL = XB + 2, NBARS = XL + 1;
+                  XB = PF + 2, XL = XB + 2, NBARS = XL + 1;
     constexpr int CB = D / 64;                                   // 64-column blocks of the head dimension
     constexpr uint32_t KVBLK = BN * 128;                         // bytes of one 64-column block of a key / value tile
     constexpr uint32_t KV_BYTES = CB * KVBLK;
@@ -207,7 +211,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const int ntiles = t_end - t_begin;
     const int rows_here = min(BM, nrows - row0);
     if (ntiles <= 0) {
-        // (only with splits) no key of this split is visible: an empty partial result, nothing allocated
+        // (only with splits) no key of this split is visible: an empty partial result, nothing allocated.  The scratch
+        // memory may still be read by the merge kernel of the launch before this one: wait for it first.
+        pdl_wait();
         for (int e = threadIdx.x; e < rows_here * D; e += blockDim.x) {
             const int r = e / D, row = row0 + r;
             const int tok = row / G, g = row - tok * G;
@@ -232,7 +238,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (warp == 1) {
         if (lane == 0) {
             for (int i = 0; i < NBARS; ++i) {
-                const bool many = (i >= OE && i < OE + 2) || i == PF || i >= XB;      // arrivals of the softmax threads; the rest: one commit or copy
+                const bool many = (i >= OE && i < OE + 2) || (i >= PF && i < PF + 2) || i >= XB;      // arrivals of the softmax threads; the rest: one commit or copy
                 mbar_init(BAR(i), many ? softmax_threads : 1u);
             }
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -411,7 +417,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 const int st = j % NST, ob = j & 1;
                 if (!mbar_wait(BAR(VF + st), (j / NST) & 1, 5)) { ok = false; break; }
                 if (!mbar_wait(BAR(OE + ob), ((j >> 1) & 1) ^ 1, 6)) { ok = false; break; }
-                if (!mbar_wait(BAR(PF), j & 1, 7)) { ok = false; break; }
+                if (!mbar_wait(BAR(PF + (j & 1)), (j >> 1) & 1, 7)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_lo = vs_lo + (uint32_t)st * (KV_BYTES >> 4), o_tmem = tmem_base + O_COL + (uint32_t)ob * D;
                 const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)(j & 1) * BN;     // P sits where the tile's scores sat
@@ -501,7 +507,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
                 m_run = m_new;
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(BAR(PF));                                   // P is in tensor memory
+                mbar_arrive(BAR(PF + sb));                              // P is in tensor memory
                 // rescale what has been summed so far to the new maximum
                 if (alpha != 1.f) {
 #pragma unroll
@@ -665,7 +671,9 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     const int t_begin = key_lo / BNK, t_end = (key_hi + BNK - 1) / BNK;
     const int nsteps = t_end - t_begin;
     if (nsteps <= 0) {
-        // (only with splits) no key of this split is visible: an empty partial result, nothing allocated
+        // (only with splits) no key of this split is visible: an empty partial result, nothing allocated.  The scratch
+        // memory may still be read by the merge kernel of the launch before this one: wait for it first.
+        pdl_wait();
         for (int e = threadIdx.x; e < rows_here * D; e += blockDim.x) {
             const int r = e / D, row = row0 + r;
             const int tok = row / G, g = row - tok * G;
