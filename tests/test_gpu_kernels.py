@@ -461,6 +461,50 @@ def test_sampling_after_a_top_k_cut(ops, V, ctas):
     assert int((probs[4] > 0).sum()) > V // 5 and int((probs[5] > 0).sum()) > V // 3 - 1     # the equal values stayed together
 
 
+@pytest.mark.parametrize("V,ctas", [(515, 1), (32000, 0), (32000, 1), (65024, 2), (256000, 0)])
+def test_sampling_with_top_p_alone(ops, V, ctas):
+    """Top-p without a top-k: peaked rows, where the tokens of 1/1,024 of the mass or more reach past the cut and the
+    kernel leaves the row for them; flat rows, where they do not and the whole row is walked; a row whose listed tokens
+    hold just about top_p of the mass; a row of equal values; a row with one token of nearly all the mass.  Kept sets,
+    probabilities and draws as the plain sampler's, and the same token whatever the number of CTAs."""
+    g = torch.Generator().manual_seed(V + 2)
+    R = 8
+    logits = torch.randn(R, V, generator=g)
+    logits[0] *= 8.0                                               # peaked
+    logits[1] *= 5.0
+    logits[2] *= 0.5                                               # flat: nearly every token is needed
+    logits[3] *= 3.0                                               # in between (the outcome depends on V)
+    logits[4] = 1.25                                               # all equal: stay together
+    logits[5, 7 % V] = 40.0                                        # one token holds nearly everything
+    logits[6] *= 6.0
+    logits[6, 1::2] = logits[6, ::2][: logits[6, 1::2].numel()]    # equal pairs at every level
+    logits[7] *= 4.0
+    rows = [(21, 0, 0, 1.0, 0.9, 0), (22, 3, 0, 0.8, 0.95, 0), (23, 1, 0, 1.0, 0.9, 0), (24, 7, 0, 1.0, 0.92, 0),
+            (25, 2, 0, 1.0, 0.5, 0), (26, 4, 0, 1.0, 0.3, 0), (27, 5, V, 1.1, 0.7, 0), (28, 6, 0, 0.6, 0.999, 0)]
+    state = sampler_state(rows)
+    slot_ids = torch.arange(R, dtype=torch.int32)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    probs = torch.zeros(R, V, device=DEV)
+    ops.sample(logits.to(DEV), slot_ids.to(DEV), state.clone().to(DEV), out, probs_out=probs, ctas_per_row=ctas)
+    for other in (1, 4):
+        again = torch.empty(R, dtype=torch.int32, device=DEV)
+        ops.sample(logits.to(DEV), slot_ids.to(DEV), state.clone().to(DEV), again, ctas_per_row=other)
+        assert torch.equal(again, out)
+    out, probs = out.cpu(), probs.cpu()
+    for r, (seed, draws, top_k, temp, top_p, greedy) in enumerate(rows):
+        exp = PLAIN.filtered_probs(logits[r], temp, top_k, top_p).float()
+        assert torch.equal(probs[r] > 0, exp > 0), f"row {r}: kept sets differ ({int((probs[r] > 0).sum())} against {int((exp > 0).sum())})"
+        assert torch.allclose(probs[r], exp, atol=2e-6, rtol=1e-4)
+        u = uniform_from_state(seed & 0x7fffffff, seed >> 31, draws)
+        cdf = torch.cumsum(probs[r].double(), 0)
+        tok = int(out[r])
+        assert probs[r, tok] > 0
+        lo = cdf[tok - 1].item() if tok else 0.0
+        assert lo - 1e-5 <= u <= cdf[tok].item() + 1e-5, (r, u, lo, cdf[tok].item())
+    assert int((probs[4] > 0).sum()) == V and int((probs[5] > 0).sum()) == 1
+    assert int((probs[0] > 0).sum()) < 1024 < int((probs[2] > 0).sum()) or V < 2048     # a short nucleus and one no list can hold
+
+
 def test_sampling_skips_padding_rows(ops):
     """A row whose slot id is -1 (padding of a fixed-size batch) yields token 0 and touches no state."""
     V = 300

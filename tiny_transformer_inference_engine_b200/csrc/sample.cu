@@ -22,6 +22,7 @@ namespace {
 constexpr int THREADS = 1024;
 constexpr int LIST_TOP_K = 256;                                      // largest top-k for which the short list is tried
 constexpr int KEEP_CAP = 1024;                                       // tokens one CTA may hand in to the short list
+constexpr float LIST_TOP_P = 1024.f;                                 // top-p alone: the list takes tokens of 1 / 1024 of the row's mass or more
 typedef unsigned long long u64;
 
 __device__ __forceinline__ unsigned ordered_key(float x) {
@@ -156,6 +157,9 @@ __device__ __forceinline__ void all_gather(T* buf, int n, T v, unsigned rank) {
 // per CTA) are gathered in token order, handed to the first CTA of the cluster, and that CTA alone does the exact top-k
 // cut, top-p and the draw on the list (`list_cap` entries fit the shared memory that held its slice).  If the list would
 // overflow (thousands of equal values at the bound), every CTA goes on with its whole slice instead.
+// Top-p without a top-k leaves the row the same way when the distribution is peaked: the (at most 1,024) tokens that hold
+// 1 / 1,024 of the row's mass or more each are listed, and if together they hold more than top_p of the mass the cut lies
+// among them.  A flat row (the listed tokens hold too little) is walked whole as before.
 template <int C>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __restrict__ slot_ids, int* __restrict__ state,
@@ -291,6 +295,10 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
         return t;
     };
 
+    bool try_list = false, by_mass = false;
+    unsigned low_key = 0;                                             // the list takes every token at or above this key
+    u64 z_row = 0, limit_row = 0;                                     // top-p alone: the row's whole mass and top_p of it
+    bool have_z = false;
     if (staged && list_cap > 0 && top_k > 0 && top_k < V && top_k <= LIST_TOP_K) {
         // (a) the bound: the top_k-th largest of the threads' own maxima (a radix select over one key per thread)
         const unsigned tkey = ordered_key(my_best / temperature);
@@ -309,13 +317,29 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
             prefix = s_prefix; remaining = s_acc;
             __syncthreads();
         }
-        const unsigned low_key = prefix;
-        // (b) the tokens at or above it, in token order: a thread counts them in its run of consecutive tokens (an odd
-        // run length: different banks), a scan over the block gives each run its place
+        low_key = prefix; try_list = true;
+    } else if (staged && list_cap > 0 && top_p < 1.0f && !(top_k > 0 && top_k < V)) {
+        // (a') top-p without a top-k: at most LIST_TOP_P tokens hold 1 / LIST_TOP_P of the row's mass or more each.  If
+        // together they hold more than top_p of it, the cut lies among them and the rest of the row is not needed.
+        u64 zz = 0;
+        for (int i = tid; i < n; i += THREADS) zz += mass_of(s_row[i], ymax);
+        zz = block_sum_u64(zz, s_u64);
+        z_row = sum_u64(zz, nullptr); have_z = true;
+        limit_row = (u64)((double)top_p * (double)z_row);
+        low_key = ordered_key(ymax + logf((float)((double)z_row * (1.0 / 1099511627776.0) / LIST_TOP_P)));
+        try_list = true; by_mass = true;
+    }
+    if (try_list) {
+        // (b) the tokens at or above the bound, in token order: a thread counts them in its run of consecutive tokens (an
+        // odd run length: different banks), a scan over the block gives each run its place
         const int run = ((n + THREADS - 1) / THREADS) | 1;
         const int a = min(n, tid * run), b = min(n, a + run);
         int cnt = 0;
-        for (int i = a; i < b; ++i) cnt += ordered_key(s_row[i]) >= low_key ? 1 : 0;
+        u64 lm = 0;                                                   // (top-p alone) their mass
+        for (int i = a; i < b; ++i) {
+            const float y = s_row[i];
+            if (ordered_key(y) >= low_key) { ++cnt; if (by_mass) lm += mass_of(y, ymax); }
+        }
         int incl = cnt;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -358,6 +382,10 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
             fits = kept <= KEEP_CAP; total = kept;
         }
         fits = fits && total <= list_cap;
+        if (by_mass) {                                                // the list must reach past the cut
+            lm = block_sum_u64(lm, s_u64);
+            fits = sum_u64(lm, nullptr) > limit_row && fits;
+        }
         if (fits) {
             // (d) into the first CTA's list, slice after slice; the others are done
             for (int j = tid; j < kept; j += THREADS) {
@@ -430,10 +458,12 @@ sample_kernel(const float* __restrict__ logits, int V, int slice, const int* __r
 
     // 3. top-p threshold: the smallest key whose strictly-larger keys hold mass <= top_p * total
     if (top_p < 1.0f) {
-        u64 z = 0;
-        for_all(true, [&](bool there, unsigned key, u64 mass) { if (there && key >= cut_key) z += mass; });
-        z = block_sum_u64(z, s_u64);
-        if (C > 1 && !solo) z = sum_u64(z, nullptr);
+        u64 z = z_row;                                                // (known already if the short list was tried for top-p alone)
+        if (!have_z) {
+            for_all(true, [&](bool there, unsigned key, u64 mass) { if (there && key >= cut_key) z += mass; });
+            z = block_sum_u64(z, s_u64);
+            if (C > 1 && !solo) z = sum_u64(z, nullptr);
+        }
         const u64 limit = (u64)((double)top_p * (double)z);
         unsigned prefix = 0; u64 acc = 0;
         for (int shift = 24; shift >= 0; shift -= 8) {
