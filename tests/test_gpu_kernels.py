@@ -359,16 +359,18 @@ def test_a_block_table_that_cannot_cover_the_keys_is_refused(ops):
 
 
 def test_many_requests_with_grouped_kv_heads_are_cut_into_pieces(ops):
-    """Decode steps whose (request, kv head) pairs alone fill the GPU: the tile loop is planned as CTAs of at
-    least 512 keys (2,000 to 4,000 of them), and the pieces merge to the float32 reference."""
-    assert ops.attention_plan(torch.bfloat16, 64, 32, 8, 128, 1, 4096, 64) == ("mma", 8, 512)
-    assert ops.attention_plan(torch.bfloat16, 32, 32, 8, 128, 1, 4096, 64) == ("mma", 8, 512)
+    """Decode steps whose (request, kv head) pairs alone fill the GPU: the tile loop's key range is cut so that the CTAs
+    come in whole waves of what the GPU holds at once (5 per SM at head size 128), and the pieces merge to the float32
+    reference."""
+    assert ops.lib.ttie_attn_mma_ctas_per_sm(128, 1, 32, 8) == 5 and ops.num_sms == 148
+    assert ops.attention_plan(torch.bfloat16, 64, 32, 8, 128, 1, 4096, 64) == ("mma", 5, 832)       # 2,560 CTAs, not 512 of 4,096 keys
+    assert ops.attention_plan(torch.bfloat16, 32, 32, 8, 128, 1, 4096, 64) == ("mma", 11, 384)      # 2,816 CTAs: 3.8 waves
+    assert ops.attention_plan(torch.bfloat16, 24, 32, 8, 128, 1, 2048, 64) == ("mma", 3, 704)       # 576 CTAs in one wave; 4 pieces would be 768
     assert ops.attention_plan(torch.bfloat16, 128, 32, 8, 128, 1, 2048, 64) == ("mma", 4, 512)
-    assert ops.attention_plan(torch.bfloat16, 64, 16, 16, 64, 1, 4096, 64) == ("mma", 4, 1024)
     assert ops.attention_plan(torch.bfloat16, 512, 32, 8, 128, 1, 4096, 64) == ("mma", 1, 0)        # 4,096 pairs: enough as they are
     seqs = [(1500 - 37 * i, 1) for i in range(24)]
     plan = ops.attention_plan(torch.bfloat16, len(seqs), 32, 8, 128, 1, 1500, 64)
-    assert plan == ("mma", 2, 768)
+    assert plan == ("mma", 3, 512)
     out, exp, _, _ = attention_case(ops, "bfloat16", 32, 8, 128, 64, seqs, plan=plan)
     assert torch.isfinite(out).all() and rel(out, exp) < TOL["bfloat16"]
 
@@ -700,10 +702,18 @@ def test_decode_form_is_planned(ops):
     assert ops.attention_plan(torch.bfloat16, 64, 32, 1, 128, 1, 256, 64) == ("tc", 1, 0)
     assert ops.attention_plan(torch.bfloat16, 256, 32, 1, 128, 1, 4096, 64) == ("tc", 1, 0)       # more requests than SMs: uncut, wave after wave
     assert ops.attention_plan(torch.bfloat16, 512, 32, 1, 128, 1, 512, 64)[0] == "mma"            # ... unless the requests are short
-    kernel, C, split_len = ops.attention_plan(torch.bfloat16, 8, 8, 1, 128, 1, 2048, 64)          # 8 rows per request
+    assert ops.attention_plan(torch.bfloat16, 8, 8, 1, 128, 1, 2048, 64) == ("tc", 16, 128)       # 8 rows per request: while the GPU is far from full
+    kernel, C, split_len = ops.attention_plan(torch.bfloat16, 8, 8, 1, 96, 1, 2048, 64)           # ... at a head size the tcgen05 kernel does not take
     assert kernel == "mma_c4" and C * split_len >= 2048 and C & (C - 1) == 0 and split_len <= 256
+    assert ops.attention_plan(torch.bfloat16, 96, 40, 2, 128, 1, 2048, 64)[0] == "mma"            # 20 rows per kv head, more CTAs than SMs
+    kernel, n, split_len = ops.attention_plan(torch.bfloat16, 24, 32, 8, 128, 1, 2048, 64)        # the tile loop's pieces fill whole waves of
+    per_sm = ops.lib.ttie_attn_mma_ctas_per_sm(128, 1, 32, 8)                                     # resident CTAs: not 769 CTAs for 740 places
+    assert kernel == "mma" and per_sm >= 4 and (24 * 8 * n) % (per_sm * 148) <= 0.9 * per_sm * 148 and n * split_len >= 2048
+    kernel, n, split_len = ops.attention_plan(torch.bfloat16, 96, 32, 1, 128, 1, 8192, 64)        # 96 CTAs would leave a third of the SMs idle
+    assert kernel == "tc" and n == 3
     assert ops.attention_plan(torch.bfloat16, 8, 32, 1, 96, 1, 2048, 64)[0] == "mma_c4"           # a head size the tcgen05 kernel does not take
-    assert ops.attention_plan(torch.bfloat16, 3, 4, 2, 64, 1, 100, 16)[0] == "mma_c2"
+    assert ops.attention_plan(torch.bfloat16, 3, 4, 2, 48, 1, 100, 16)[0] == "mma_c2"
+    assert ops.attention_plan(torch.bfloat16, 3, 4, 2, 64, 1, 100, 16) == ("tc", 1, 0)             # two rows per kv head, but the GPU is nearly empty
     assert ops.attention_plan(torch.bfloat16, 64, 8, 1, 128, 1, 256, 64) == ("mma_c4", 1, 256)
     kernel, n, split_len = ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 32768, 64)
     assert kernel == "tc" and n * split_len >= 32768 and split_len % 128 == 0 and 8 * n <= 148

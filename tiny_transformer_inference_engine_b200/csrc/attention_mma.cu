@@ -696,6 +696,20 @@ int launch(const MmaParams& p, cudaStream_t s) {
     return 0;
 }
 
+// CTAs of the tile loop that one SM holds at once (0 if the question fails)
+template <int D, int NWARPS>
+int resident_per_sm() {
+    constexpr int BM = NWARPS * 16, LDS = D + 8, STAGES = NWARPS >= 4 ? 2 : 1;
+    const size_t smem = ((size_t)BM * LDS + 2 * STAGES * (size_t)BN * LDS) * sizeof(__nv_bfloat16) + STAGES * BN * sizeof(long long);
+    auto k = paged_attn_mma_kernel<D, NWARPS, STAGES>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return 0; }
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, NWARPS * 32, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+template <int D>
+int resident_per_sm_of(int rows) { return rows <= 16 ? resident_per_sm<D, 1>() : rows <= 32 ? resident_per_sm<D, 2>() : resident_per_sm<D, 4>(); }
+
 template <int D>
 int pick_rows(const MmaParams& p, int rows_per_seq_max, cudaStream_t s, int* bm) {
     if (rows_per_seq_max <= 16) { *bm = 16; return launch<D, 1>(p, s); }
@@ -711,6 +725,22 @@ extern "C" int ttie_attn_mma_tile_rows(int max_q_len, int Hq, int Hkv) {
 }
 
 extern "C" int ttie_attn_mma_supported(int D) { return D % 16 == 0 && D >= 16 && D <= 128; }
+
+// CTAs of the tile loop that one SM holds at once, for this head size and row count per request and kv head.
+extern "C" int ttie_attn_mma_ctas_per_sm(int D, int max_q_len, int Hq, int Hkv) {
+    const int rows = max_q_len * (Hq / Hkv);
+    switch (D) {
+        case 16: return resident_per_sm_of<16>(rows);
+        case 32: return resident_per_sm_of<32>(rows);
+        case 48: return resident_per_sm_of<48>(rows);
+        case 64: return resident_per_sm_of<64>(rows);
+        case 80: return resident_per_sm_of<80>(rows);
+        case 96: return resident_per_sm_of<96>(rows);
+        case 112: return resident_per_sm_of<112>(rows);
+        case 128: return resident_per_sm_of<128>(rows);
+    }
+    return 0;
+}
 
 // The decode form tiles query rows (tokens x heads per kv head) by at most this many per cluster.
 extern "C" int ttie_attn_cluster_tile_rows(int max_q_len, int Hq, int Hkv) { return max_q_len * (Hq / Hkv) <= 16 ? 16 : CL_MAX_ROWS; }

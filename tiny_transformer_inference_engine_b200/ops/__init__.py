@@ -94,11 +94,11 @@ class CudaOps:
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None) or \
             (lambda index: torch.cuda.current_stream(index).cuda_stream)
         self.attn_target_ctas = 4 * self.num_sms  # decode tiles are small: four CTAs share an SM
-        self.attn_mma_target_ctas = 28 * self.num_sms   # CTAs the tile loop wants when the requests alone fill the GPU (measured: 2,000 to 4,000)
         self.attn_cluster_max_rows = 64         # query rows per request (tokens x heads per kv head) up to which the decode form runs
         self.attn_cluster_max_size = 8          # CTAs per cluster (16 is placed on fewer SMs at a time)
         self.attn_cluster_tiles_per_warp = 1    # ... and only while a warp walks at most this many 64-key tiles
         self._cluster_max = {}
+        self._mma_per_sm = {}
         self.attn_tc_min_split = 256            # keys per CTA from which the tcgen05 kernel splits a decode step's key range
         self.attn_tcpp_min_split = 1024         # keys per CTA below which a prompt portion's key range is not cut
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
@@ -116,7 +116,8 @@ class CudaOps:
             fn.argtypes, fn.restype = [_c_void], _c_int
             if fn(self._tc_pinned.data_ptr() + 4 * i):
                 raise KernelError(f"{name} failed")
-        for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows", "ttie_attn_cluster_tile_rows", "ttie_attn_cluster_active"):
+        for name in ("ttie_attn_mma_supported", "ttie_attn_mma_tile_rows", "ttie_attn_cluster_tile_rows", "ttie_attn_cluster_active",
+                     "ttie_attn_mma_ctas_per_sm"):
             getattr(self.lib, name).restype = _c_int
 
     # ------------------------------------------------------------------ helpers
@@ -542,15 +543,8 @@ class CudaOps:
             kernel, tile_rows, unit, min_len = "simt", 32, 32, 32      # (one 32-key tile per CTA where the GPU has room: 10.6 us
                                                                       # against 21 for 200 keys in two pieces of 128)
         base = num_seqs * num_kv_heads * math.ceil(rows / tile_rows)
-        if kernel == "mma" and rows <= 64 and self.num_sms <= base < self.attn_mma_target_ctas and max_kv_len >= 1024:
-            # few rows per request and kv head, many requests or kv heads (grouped kv heads at a large batch): the tile
-            # loop streams best as 2,000 to 4,000 CTAs of 512 keys or more - several resident per SM, and no long last wave
-            # (64 requests x 8 kv heads at 4,096 keys: 283 us uncut, 214 us in 8 pieces; 32 x 8: 242 -> 117 us in 8;
-            # 64 x 16 kv heads of 64: 248 -> 191 us in 4)
-            want = max(1, min(self.attn_mma_target_ctas // base, max_kv_len // 512))
-            split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
-            num_splits = math.ceil(max_kv_len / split_len)
-            return (kernel, num_splits, split_len) if num_splits > 1 else (kernel, 1, 0)
+        if kernel == "mma" and rows <= 64:      # (one row tile per request and kv head: decoded tokens and the like)
+            return self._mma_split_plan(base, head_dim, max_q_len, num_heads, num_kv_heads, max_kv_len)
         if base >= self.num_sms or max_kv_len <= min_len:
             return kernel, 1, 0
         # as many splits as fit one wave of resident CTAs, none shorter than min_len keys
@@ -558,6 +552,42 @@ class CudaOps:
         split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
         num_splits = math.ceil(max_kv_len / split_len)
         return (kernel, num_splits, split_len) if num_splits > 1 else (kernel, 1, 0)
+
+    def _mma_split_plan(self, base, head_dim, max_q_len, num_heads, num_kv_heads, max_kv_len):
+        """Pieces of the key range for the mma.sync tile loop, by a cost model fitted to measurements (head size 128,
+        16-row tiles, 8 to 200 requests on 2 and 8 kv heads, 300 to 8,192 keys).  An SM holds a handful of the kernel's
+        CTAs (5 at head size 128) and all of them together stream at a fixed rate, so the CTAs run in waves of
+        ``resident``: a wave costs about 4.3 us and 74 ns per key of its pieces (58 ns when the wave fills less than a
+        third of the GPU: a CTA alone on its SM runs faster), and 769 CTAs take as long as 1,480.  From three waves on the
+        waves blur and the cost is proportional to the CTAs.  Merging costs 2 us.  Against picking the pieces by a fixed
+        target of CTAs this is 16 % faster on average over those measurements and up to 70 % (24 requests x 8 kv heads at
+        300 keys: 12.5 us in 3 pieces against 19.7 uncut; at 2,048 keys 54.6 against 71.4)."""
+        key = (head_dim, max_q_len * (num_heads // num_kv_heads) <= 16, max_q_len * (num_heads // num_kv_heads) <= 32)
+        per_sm = self._mma_per_sm.get(key)
+        if per_sm is None:
+            per_sm = self._mma_per_sm[key] = max(1, self.lib.ttie_attn_mma_ctas_per_sm(head_dim, max_q_len, num_heads, num_kv_heads))
+        resident = per_sm * self.num_sms
+        full_key = 0.0743 * (head_dim + 8) / 136
+
+        def per_key(fill):
+            return full_key * (0.78 + max(0.0, min(fill, 0.86) - 0.3) * 0.4)
+
+        best, best_cost = ("mma", 1, 0), None
+        for want in range(1, min(128, math.ceil(max_kv_len / 64)) + 1):
+            split_len = math.ceil(math.ceil(max_kv_len / want) / 64) * 64
+            n = math.ceil(max_kv_len / split_len)
+            if n != want:
+                continue
+            ctas, keys = base * n, min(split_len, max_kv_len)
+            if ctas >= 3 * resident:
+                cost = ctas / resident * (4.3 + keys * full_key)
+            else:
+                whole, rest = divmod(ctas, resident)
+                cost = whole * (4.3 + keys * full_key) + ((4.3 + keys * per_key(rest / resident)) if rest else 0.0)
+            cost += 2.0 if n > 1 else 0.0
+            if best_cost is None or cost < best_cost - 1e-9:
+                best, best_cost = (("mma", n, split_len) if n > 1 else ("mma", 1, 0)), cost
+        return best
 
     def _tc_wide_plan(self, num_seqs, num_kv_heads, rows, max_kv_len):
         """Head size 256: every step takes the prompt-portion tcgen05 kernel with one 128-row tile per CTA.  Where
@@ -574,24 +604,44 @@ class CudaOps:
         return ("tcpp", n, split_len) if n > 1 else ("tcpp", 1, 0)
 
     def _tc_split_plan(self, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size):
-        """The tcgen05 kernel for steps with few query rows per request and contexts too long for the decode
-        form: one wave of CTAs (the kernel takes a whole SM), each walking at least 256 keys; the merge
-        kernel adds the pieces.  None where the head or page size is not the kernel's, the rows exceed one
-        128-row tile or fill less than an eighth of it (the mma.sync kernel's 16-row tiles waste less there).  With more
-        requests than SMs it runs uncut."""
+        """The tcgen05 kernel for steps with few query rows per request: the key range of every request is cut into
+        pieces, one CTA each (the kernel takes a whole SM), and the merge kernel adds the pieces.  None where the head
+        or page size is not the kernel's, the rows exceed one 128-row tile, or there are so few rows per kv head and so
+        many requests that the mma.sync kernel's 16-row tiles waste less."""
         rows = max_q_len * (num_heads // num_kv_heads)
         base = num_seqs * num_kv_heads
-        if (page_size is None or rows > 128 or rows < 16 or head_dim > 128
+        if (page_size is None or rows > 128 or head_dim > 128
                 or not self.lib.ttie_attn_tc_supported(head_dim, page_size)):
             return None
-        if base > self.num_sms:
-            # more requests than SMs: one CTA per request, wave after wave, while a request has a thousand keys or more
-            # (256 requests at 4,096 keys: 105 us against 143 for the tile loop in 8 pieces; at 512 keys the tile loop is ahead)
-            return ("tc", 1, 0) if max_kv_len >= 1024 else None
-        n = max(1, min(self.num_sms // base, math.ceil(max_kv_len / self.attn_tc_min_split)))
-        split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
-        n = math.ceil(max_kv_len / split_len)
-        return ("tc", n, split_len) if n > 1 else ("tc", 1, 0)
+        # 16 rows or fewer fill an eighth of the kernel's row tile: it still wins while the GPU is far from full (2 requests
+        # x 8 kv heads at 300 keys: 8.0 us against 10.0 for the decode form), the tile loop's 16-row CTAs win beyond (32
+        # requests x 2 kv heads at 2,048 keys: 19.6 us against 22.9)
+        if rows <= 16 and (base > 32 or base * max_kv_len > (32768 if rows == 16 else 16384)):
+            return None
+        if rows < 32 and base > self.num_sms:
+            return None              # (40 heads on 2 kv heads, 96 requests at 2,048 keys: 72.7 us uncut against 56.8 for the tile loop)
+        if base > self.num_sms and max_kv_len < 1024:
+            return None              # more requests than SMs with short contexts: the tile loop is ahead (measured at 512 keys)
+        # The number of pieces by a cost model fitted to measurements (32 heads of 128 and 71 heads of 64 on one kv head, 2
+        # to 200 requests, 300 to 8,192 keys).  CTAs run in waves of one per SM; a wave costs about 3.5 us to set up and
+        # finish and 12.5 ns per key (more with more than 64 query rows); the launch costs 2 us, merging the pieces 2
+        # (4 with more than 32 pieces, which the general merge kernel adds up).  So few requests get pieces down to 128
+        # keys (2 requests at 1,024 keys: 7.7 us in 8 pieces against 8.9 in 4), and where the requests alone leave the
+        # last wave half empty the key range is cut although every SM has a CTA already (96 requests at 8,192 keys: 81 us
+        # in 3 pieces against 99 uncut; 200 requests: 165 in 2 against 194) - but into pieces of 1,280 keys at least:
+        # shorter ones in several waves lose (200 requests at 1,024 keys: 43.6 us in 2 pieces against 34.8 uncut).
+        per_key = 0.0125 * (1.15 if rows > 64 else 1.0)
+        best, best_cost = ("tc", 1, 0), None
+        for want in range(1, min(256, math.ceil(max_kv_len / 128)) + 1):
+            split_len = math.ceil(math.ceil(max_kv_len / want) / 128) * 128
+            n = math.ceil(max_kv_len / split_len)
+            if n != want or (n > 1 and base * n > self.num_sms and split_len < 1280):
+                continue                                             # (the same cut as a smaller count; short pieces in several waves)
+            cost = (math.ceil(base * n / self.num_sms) * (3.5 + min(split_len, max_kv_len) * per_key) + 2.0
+                    + (0.0 if n == 1 else 2.0 if n <= 32 else 4.0))
+            if best_cost is None or cost < best_cost - 1e-9:
+                best, best_cost = (("tc", n, split_len) if n > 1 else ("tc", 1, 0)), cost
+        return best
 
     def _clusters_active(self, head_dim, max_q_len, num_heads, num_kv_heads, groups, size):
         key = (head_dim, max_q_len * (num_heads // num_kv_heads) <= 16, groups, size)
