@@ -694,9 +694,10 @@ def test_tcgen05_splits_one_key_decides(ops, kpos):
 
 
 def test_decode_form_is_planned(ops):
-    """Decode steps of the bfloat16 path take the tcgen05 kernel with the key range cut over CTAs where a request brings
-    16 rows or more per kv head at head size 64 or 128; with fewer rows or another head size the decode form while a
-    warp has one key tile to walk, and the tile loop with splits beyond; prompt portions the tcgen05 kernels or the tile loop."""
+    """Decode steps of the bfloat16 path take the tcgen05 kernel with the key range cut over CTAs at head size 64 or 128
+    where a request brings 32 rows or more per kv head, or fewer on a nearly empty GPU; otherwise, and at another head size,
+    the decode form while a warp has one key tile to walk, and the tile loop with splits beyond; prompt portions the tcgen05
+    kernels or the tile loop."""
     kernel, n, split_len = ops.attention_plan(torch.bfloat16, 8, 32, 1, 128, 1, 2048, 64)
     assert kernel == "tc" and n * split_len >= 2048 and 8 * n <= 148
     assert ops.attention_plan(torch.bfloat16, 64, 32, 1, 128, 1, 256, 64) == ("tc", 1, 0)
