@@ -99,7 +99,6 @@ class CudaOps:
         self.attn_cluster_tiles_per_warp = 1    # ... and only while a warp walks at most this many 64-key tiles
         self._cluster_max = {}
         self._mma_per_sm = {}
-        self.attn_tc_min_split = 256            # keys per CTA from which the tcgen05 kernel splits a decode step's key range
         self.attn_tcpp_min_split = 1024         # keys per CTA below which a prompt portion's key range is not cut
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product is the rule (tune_products may hand a shape to the library)
@@ -590,14 +589,17 @@ class CudaOps:
         return best
 
     def _tc_wide_plan(self, num_seqs, num_kv_heads, rows, max_kv_len):
-        """Head size 256: every step takes the prompt-portion tcgen05 kernel with one 128-row tile per CTA.  Where
-        the row tiles fill less than half of the GPU the key range is cut over CTAs as well: into pieces of at least
-        256 keys for steps of few rows (decoded tokens), of at least 1,024 keys for portions."""
+        """Head size 256: every step takes the prompt-portion tcgen05 kernel with one 128-row tile per CTA.  Steps of few
+        rows (decoded tokens) have their key range cut by the cost model of the one-tile decode kernel, at 20 ns per key
+        (8 heads on one kv head, 2 requests at 1,024 keys: 9.3 us in 8 pieces of 128 against 11.5 in 4; 96 requests at
+        8,192 keys: 132 us in 3 pieces against 153 uncut).  Portions are cut where their row tiles fill less than half of
+        the GPU, into pieces of at least 1,024 keys."""
         base = num_seqs * num_kv_heads * math.ceil(rows / 128)
+        if rows <= 128:
+            return self._one_per_sm_pieces("tcpp", base, max_kv_len, 0.020, waves_min_keys=640)
         if base > self.num_sms // 2:
             return "tcpp", 1, 0
-        shortest = self.attn_tc_min_split if rows <= 128 else self.attn_tcpp_min_split
-        n = max(1, min(self.num_sms // base, max_kv_len // shortest))
+        n = max(1, min(self.num_sms // base, max_kv_len // self.attn_tcpp_min_split))
         if n > 1:
             split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
             n = math.ceil(max_kv_len / split_len)
@@ -625,22 +627,27 @@ class CudaOps:
         # The number of pieces by a cost model fitted to measurements (32 heads of 128 and 71 heads of 64 on one kv head, 2
         # to 200 requests, 300 to 8,192 keys).  CTAs run in waves of one per SM; a wave costs about 3.5 us to set up and
         # finish and 12.5 ns per key (more with more than 64 query rows); the launch costs 2 us, merging the pieces 2
-        # (4 with more than 32 pieces, which the general merge kernel adds up).  So few requests get pieces down to 128
+        # (5.5 with more than 32 pieces, which the general merge kernel adds up).  So few requests get pieces down to 128
         # keys (2 requests at 1,024 keys: 7.7 us in 8 pieces against 8.9 in 4), and where the requests alone leave the
         # last wave half empty the key range is cut although every SM has a CTA already (96 requests at 8,192 keys: 81 us
         # in 3 pieces against 99 uncut; 200 requests: 165 in 2 against 194) - but into pieces of 1,280 keys at least:
         # shorter ones in several waves lose (200 requests at 1,024 keys: 43.6 us in 2 pieces against 34.8 uncut).
-        per_key = 0.0125 * (1.15 if rows > 64 else 1.0)
-        best, best_cost = ("tc", 1, 0), None
+        return self._one_per_sm_pieces("tc", base, max_kv_len, 0.0125 * (1.15 if rows > 64 else 1.0))
+
+    def _one_per_sm_pieces(self, kernel, base, max_kv_len, per_key, waves_min_keys=1280):
+        """The cheapest cut of ``max_kv_len`` keys into pieces of a multiple of 128 keys for a kernel that runs one CTA per
+        SM, ``base`` CTAs per piece: waves of ``num_sms`` CTAs at 3.5 us + ``per_key`` us per key of a piece, 2 us for the
+        launch, 2 for merging (5.5 with more than 32 pieces); pieces that run in several waves hold ``waves_min_keys`` or more."""
+        best, best_cost = (kernel, 1, 0), None
         for want in range(1, min(256, math.ceil(max_kv_len / 128)) + 1):
             split_len = math.ceil(math.ceil(max_kv_len / want) / 128) * 128
             n = math.ceil(max_kv_len / split_len)
-            if n != want or (n > 1 and base * n > self.num_sms and split_len < 1280):
+            if n != want or (n > 1 and base * n > self.num_sms and split_len < waves_min_keys):
                 continue                                             # (the same cut as a smaller count; short pieces in several waves)
             cost = (math.ceil(base * n / self.num_sms) * (3.5 + min(split_len, max_kv_len) * per_key) + 2.0
-                    + (0.0 if n == 1 else 2.0 if n <= 32 else 4.0))
+                    + (0.0 if n == 1 else 2.0 if n <= 32 else 5.5))
             if best_cost is None or cost < best_cost - 1e-9:
-                best, best_cost = (("tc", n, split_len) if n > 1 else ("tc", 1, 0)), cost
+                best, best_cost = ((kernel, n, split_len) if n > 1 else (kernel, 1, 0)), cost
         return best
 
     def _clusters_active(self, head_dim, max_q_len, num_heads, num_kv_heads, groups, size):
