@@ -29,19 +29,21 @@ def plain_greedy(cfg, w, prompt, n):
 
 # ------------------------------------------------------------------------------------------ long prompts
 LONG = {
-    # 8 heads of 128 on one kv head; 64 heads of 64 on two
+    # 8 and 16 heads of 128 on one kv head; 64 heads of 64 on two
     "h128": dict(architecture="mqa_gpt", vocab_size=160, d_model=1024, num_layers=2, num_heads=8, num_kv_heads=1,
                  hidden_size=192, max_seq_len=2688, rope_theta=10000.0, rms_norm_eps=1e-5, bias=False, dtype="float32"),
+    "h128w": dict(architecture="mqa_gpt", vocab_size=150, d_model=2048, num_layers=1, num_heads=16, num_kv_heads=1,
+                  hidden_size=128, max_seq_len=2688, rope_theta=10000.0, rms_norm_eps=1e-5, bias=False, dtype="float32"),
     "h64": dict(architecture="mqa_gpt", vocab_size=130, d_model=4096, num_layers=1, num_heads=64, num_kv_heads=2,
                 hidden_size=64, max_seq_len=2688, rope_theta=50000.0, rms_norm_eps=1e-6, bias=False, dtype="float32"),
 }
 
 
-@pytest.mark.parametrize("name,page", [("h128", 64), ("h128", 16), ("h64", 64)])
-def test_long_prompts_reach_the_two_tile_kernel(name, page):
-    """A 2,048-token portion (the two-tile kernel), a 512-token portion behind it (the same kernel with its key
-    range cut over CTAs, then the merge), the rest, decoded tokens beside another request's portion, and a
-    prompt taken whole: bfloat16 logits at every position against the plain model."""
+@pytest.mark.parametrize("name,page", [("h128", 64), ("h128", 16), ("h128w", 64), ("h64", 64)])
+def test_long_prompts_reach_the_tensor_core_kernels(name, page):
+    """A 2,048-token portion (the two-tile kernel where its row tiles fill half of the GPU, else the one-tile kernel), a
+    512-token portion behind it (its key range cut over CTAs, then the merge), the rest, decoded tokens beside another
+    request's portion, and a prompt taken whole: bfloat16 logits at every position against the plain model."""
     cfg = LONG[name]
     g = torch.Generator().manual_seed(5)
     a = torch.randint(0, cfg["vocab_size"], (2640,), generator=g).tolist()
@@ -72,9 +74,13 @@ def test_long_prompts_reach_the_two_tile_kernel(name, page):
         eng.ops.attention_plan = inner
     assert eng.ops.tc_error() == 0
     kinds = {(k, n > 1) for k, n, _ in plans}
-    # portions whose key range is cut over CTAs (with 8 heads even the 2,048-token one: its row tiles fill less than
-    # half of the GPU); with 64 heads the long portions run uncut
-    assert ("tcpp", True) in kinds and (name != "h64" or ("tcpp", False) in kinds), kinds
+    # with 8 heads the row tiles of a portion fill less than half of the GPU: the one-tile kernel takes the long portion
+    # uncut and the shorter ones behind it with their key range cut over CTAs; with 64 heads the long portions run uncut
+    # on the two-tile kernel
+    if name in ("h64", "h128w"):
+        assert ("tcpp", False) in kinds, kinds
+    else:
+        assert ("tc", False) in kinds and (("tc", True) in kinds or ("tcpp", True) in kinds), kinds
     exp = {"a": plain_forward(cfg, w, a), "b": plain_forward(cfg, w, b)}
     exp["c"] = exp["b"]
     bad = tu.first_wrong(got, exp, TOL["bfloat16"])

@@ -514,18 +514,31 @@ class CudaOps:
             return self._tc_wide_plan(num_seqs, num_kv_heads, rows, max_kv_len)
         if (dtype == torch.bfloat16 and page_size is not None and rows >= self.attn_tc_min_rows
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
-            # prompt portions: the tcgen05 kernel with two query tiles per CTA.  Where its CTAs fill less than half of
-            # the GPU, a short portion behind a long context has its key range cut as well, and a short portion
-            # without one goes to the one-tile kernel, which has twice the CTAs (measured at 512 tokens x 32 heads:
-            # 16.4 against 21.6 us; the last 512 of 8,192 tokens: 105 us cut in two, 147 us uncut)
+            # prompt portions: the tcgen05 kernel with two query tiles per CTA, uncut, where its CTAs fill half of the GPU
+            # or more.  Below that the choice is between that kernel and the one-tile kernel (twice the CTAs), each with the
+            # key range uncut or cut, by a cost model fitted to measurements (32 heads of 128; 1 to 8 portions of 128 to
+            # 2,048 tokens behind 2,048 to 32,768 keys): waves of one CTA per SM at 3.5 us and 12 ns (one tile) or 17 ns (two)
+            # per key, 2 us for the launch, and for cut ranges 3 us and the partial results' way through memory at 4 TB/s.
+            # (512 tokens alone: one tile uncut, 14.3 against 18.4 us; the last 512 of 8,192: two tiles in two pieces, 83
+            # against 103 one tile uncut and 134 two tiles uncut; the last 128 of 2,048: one tile in four pieces, 18.4
+            # against 30.4 two tiles in two.)
             base = num_seqs * num_kv_heads * math.ceil(rows / 256)
             if base > self.num_sms // 2:
                 return "tcpp", 1, 0
-            n = max(1, min(self.num_sms // base, max_kv_len // self.attn_tcpp_min_split))
-            if n > 1:
-                split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
-                n = math.ceil(max_kv_len / split_len)
-            return ("tcpp", n, split_len) if n > 1 else ("tc", 1, 0)
+            all_rows = num_seqs * num_kv_heads * rows
+            best, best_cost = ("tc", 1, 0), None
+            for kernel, tiles, per_key in (("tc", num_seqs * num_kv_heads * math.ceil(rows / 128), 0.012), ("tcpp", base, 0.017)):
+                for want in range(1, min(16, math.ceil(max_kv_len / 128)) + 1):
+                    split_len = math.ceil(math.ceil(max_kv_len / want) / 128) * 128
+                    n = math.ceil(max_kv_len / split_len)
+                    if n != want or (n > 1 and tiles * n > self.num_sms):
+                        continue                                     # (a cut range in several waves lost wherever it was measured)
+                    cost = math.ceil(tiles * n / self.num_sms) * (3.5 + min(split_len, max_kv_len) * per_key) + 2.0
+                    if n > 1:
+                        cost += 3.0 + all_rows * (n * (4 * head_dim + 8) + 2 * head_dim) / 4e6
+                    if best_cost is None or cost < best_cost - 1e-9:
+                        best, best_cost = ((kernel, n, split_len) if n > 1 else (kernel, 1, 0)), cost
+            return best
         if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
             # few rows per request: the tcgen05 kernel with the key range cut over CTAs where it applies (16 rows and more
             # per kv head, head size 64 or 128) - since it stages only the rows in use and sets itself up while its
