@@ -99,7 +99,6 @@ class CudaOps:
         self.attn_cluster_tiles_per_warp = 1    # ... and only while a warp walks at most this many 64-key tiles
         self._cluster_max = {}
         self._mma_per_sm = {}
-        self.attn_tcpp_min_split = 1024         # keys per CTA below which a prompt portion's key range is not cut
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product is the rule (tune_products may hand a shape to the library)
         self._swiglu_choice = {}                # (F, K, row bucket) -> True where the fused tcgen05 gate/up + SwiGLU kernel measured faster
@@ -511,7 +510,7 @@ class CudaOps:
         rows = max_q_len * G
         if (dtype == torch.bfloat16 and page_size is not None and head_dim > 128
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
-            return self._tc_wide_plan(num_seqs, num_kv_heads, rows, max_kv_len)
+            return self._tc_wide_plan(num_seqs, num_kv_heads, rows, max_kv_len, max_q_len)
         if (dtype == torch.bfloat16 and page_size is not None and rows >= self.attn_tc_min_rows
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
             # prompt portions: the tcgen05 kernel with two query tiles per CTA, uncut, where its CTAs fill half of the GPU
@@ -525,20 +524,9 @@ class CudaOps:
             base = num_seqs * num_kv_heads * math.ceil(rows / 256)
             if base > self.num_sms // 2:
                 return "tcpp", 1, 0
-            all_rows = num_seqs * num_kv_heads * rows
-            best, best_cost = ("tc", 1, 0), None
-            for kernel, tiles, per_key in (("tc", num_seqs * num_kv_heads * math.ceil(rows / 128), 0.012), ("tcpp", base, 0.017)):
-                for want in range(1, min(16, math.ceil(max_kv_len / 128)) + 1):
-                    split_len = math.ceil(math.ceil(max_kv_len / want) / 128) * 128
-                    n = math.ceil(max_kv_len / split_len)
-                    if n != want or (n > 1 and tiles * n > self.num_sms):
-                        continue                                     # (a cut range in several waves lost wherever it was measured)
-                    cost = math.ceil(tiles * n / self.num_sms) * (3.5 + min(split_len, max_kv_len) * per_key) + 2.0
-                    if n > 1:
-                        cost += 3.0 + all_rows * (n * (4 * head_dim + 8) + 2 * head_dim) / 4e6
-                    if best_cost is None or cost < best_cost - 1e-9:
-                        best, best_cost = ((kernel, n, split_len) if n > 1 else (kernel, 1, 0)), cost
-            return best
+            return self._portion_pieces(num_seqs * num_kv_heads * rows, head_dim, max_kv_len,
+                                        (("tc", num_seqs * num_kv_heads * math.ceil(rows / 128), 0.012), ("tcpp", base, 0.017)),
+                                        max_kv_len >= 2 * max_q_len)
         if dtype == torch.bfloat16 and self.lib.ttie_attn_mma_supported(head_dim):
             # few rows per request: the tcgen05 kernel with the key range cut over CTAs where it applies (16 rows and more
             # per kv head, head size 64 or 128) - since it stages only the rows in use and sets itself up while its
@@ -564,6 +552,25 @@ class CudaOps:
         split_len = math.ceil(math.ceil(max_kv_len / want) / unit) * unit
         num_splits = math.ceil(max_kv_len / split_len)
         return (kernel, num_splits, split_len) if num_splits > 1 else (kernel, 1, 0)
+
+    def _portion_pieces(self, all_rows, head_dim, max_kv_len, kernels, may_cut):
+        """The cheapest of ``kernels`` (name, CTAs per piece, us per key) and cuts of the key range for prompt portions whose
+        CTAs fill less than half of the GPU: one wave of CTAs at 3.5 us + the keys of a piece, 2 us for the launch, and for
+        a cut range 3 us and the partial results' way through memory at 4 TB/s.  A cut range stays within one wave; a
+        portion that is most of its own context (``may_cut`` false) is not cut: behind the diagonal a piece has no work."""
+        best, best_cost = (kernels[0][0], 1, 0), None
+        for kernel, tiles, per_key in kernels:
+            for want in range(1, (min(16, math.ceil(max_kv_len / 128)) if may_cut else 1) + 1):
+                split_len = math.ceil(math.ceil(max_kv_len / want) / 128) * 128
+                n = math.ceil(max_kv_len / split_len)
+                if n != want or (n > 1 and tiles * n > self.num_sms):
+                    continue                                         # (a cut range in several waves lost wherever it was measured)
+                cost = math.ceil(tiles / self.num_sms) * (3.5 + min(split_len, max_kv_len) * per_key) + 2.0
+                if n > 1:
+                    cost += 3.0 + all_rows * (n * (4 * head_dim + 8) + 2 * head_dim) / 4e6
+                if best_cost is None or cost < best_cost - 1e-9:
+                    best, best_cost = ((kernel, n, split_len) if n > 1 else (kernel, 1, 0)), cost
+        return best
 
     def _mma_split_plan(self, base, head_dim, max_q_len, num_heads, num_kv_heads, max_kv_len):
         """Pieces of the key range for the mma.sync tile loop, by a cost model fitted to measurements (head size 128,
@@ -601,22 +608,19 @@ class CudaOps:
                 best, best_cost = (("mma", n, split_len) if n > 1 else ("mma", 1, 0)), cost
         return best
 
-    def _tc_wide_plan(self, num_seqs, num_kv_heads, rows, max_kv_len):
+    def _tc_wide_plan(self, num_seqs, num_kv_heads, rows, max_kv_len, max_q_len):
         """Head size 256: every step takes the prompt-portion tcgen05 kernel with one 128-row tile per CTA.  Steps of few
         rows (decoded tokens) have their key range cut by the cost model of the one-tile decode kernel, at 20 ns per key
         (8 heads on one kv head, 2 requests at 1,024 keys: 9.3 us in 8 pieces of 128 against 11.5 in 4; 96 requests at
-        8,192 keys: 132 us in 3 pieces against 153 uncut).  Portions are cut where their row tiles fill less than half of
-        the GPU, into pieces of at least 1,024 keys."""
+        8,192 keys: 132 us in 3 pieces against 153 uncut).  Portions whose row tiles fill less than half of the GPU are cut
+        by the portions' cost model at 21 ns per key (512 tokens behind 2,048 keys: 25.5 us in 4 pieces against 33.0 in 2)."""
         base = num_seqs * num_kv_heads * math.ceil(rows / 128)
         if rows <= 128:
             return self._one_per_sm_pieces("tcpp", base, max_kv_len, 0.020, waves_min_keys=640)
         if base > self.num_sms // 2:
             return "tcpp", 1, 0
-        n = max(1, min(self.num_sms // base, max_kv_len // self.attn_tcpp_min_split))
-        if n > 1:
-            split_len = math.ceil(math.ceil(max_kv_len / n) / 128) * 128
-            n = math.ceil(max_kv_len / split_len)
-        return ("tcpp", n, split_len) if n > 1 else ("tcpp", 1, 0)
+        return self._portion_pieces(num_seqs * num_kv_heads * rows, 256, max_kv_len, (("tcpp", base, 0.021),),
+                                    max_kv_len >= 2 * max_q_len)
 
     def _tc_split_plan(self, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size):
         """The tcgen05 kernel for steps with few query rows per request: the key range of every request is cut into
