@@ -99,6 +99,7 @@ class CudaOps:
         self.attn_cluster_tiles_per_warp = 1    # ... and only while a warp walks at most this many 64-key tiles
         self._cluster_max = {}
         self._mma_per_sm = {}
+        self._plans = {}
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product is the rule (tune_products may hand a shape to the library)
         self._swiglu_choice = {}                # (F, K, row bucket) -> True where the fused tcgen05 gate/up + SwiGLU kernel measured faster
@@ -505,7 +506,17 @@ class CudaOps:
         """Which attention kernel runs and how the key range is split: (kernel, num_splits,
         split_len).  bfloat16 with a head size that is a multiple of 16 up to 128, or 256, runs
         on tensor cores; everything else runs the general float32-arithmetic kernel.  The key
-        range is split only when the query rows alone cannot fill the GPU."""
+        range is split only when the query rows alone cannot fill the GPU.  Every layer of a step
+        asks the same question, so the answers are kept."""
+        key = (dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
+        plan = self._plans.get(key)
+        if plan is None:
+            if len(self._plans) >= 4096:
+                self._plans.clear()
+            plan = self._plans[key] = self._attention_plan(*key)
+        return plan
+
+    def _attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size):
         G = num_heads // num_kv_heads
         rows = max_q_len * G
         if (dtype == torch.bfloat16 and page_size is not None and head_dim > 128
