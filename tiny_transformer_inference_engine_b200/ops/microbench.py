@@ -235,7 +235,7 @@ def attention(ops, a):
             planned = ops.attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx, page)
             keep = ops._cluster_plan, ops._tc_split_plan
             ops._cluster_plan = ops._tc_split_plan = lambda *x: None
-            loop = ops.attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx, page)
+            loop = ops._attention_plan(torch.bfloat16, B, Hq, Hkv, D, 1, ctx, page)        # (not the kept answer)
             ops._cluster_plan, ops._tc_split_plan = keep
             for plan in (planned, loop):
                 us = timeit(lambda i: ops.paged_attention(q, Hq, Hkv, D, kp, vp, table, page, qsl, sl, B, 1, ctx, 1 / math.sqrt(D), 0, o, plan=plan))
