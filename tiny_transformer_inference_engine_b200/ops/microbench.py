@@ -111,10 +111,10 @@ def decode(ops, a):
     resid, part, w = torch.randn(B, d, device=DEV), torch.randn(4, B, d, device=DEV), torch.ones(d, device=DEV)
     out = torch.empty(B, d, device=DEV, dtype=torch.bfloat16)
     line("residual add (4 partial sums) + RMSNorm", timeit(lambda i: ops.add_rmsnorm(resid, part, w, 1e-5, out)), bytes_=B * d * (4 * 5 + 4 + 2))
-    nb = B * (ctx // page) + 1
+    nb = B * -(-ctx // page) + 1                                     # pages of whole requests, and the scratch page
     kp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
     vp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
-    table = (torch.arange(B * (ctx // page), device=DEV, dtype=torch.int32) + 1).view(B, -1)
+    table = (torch.arange(B * -(-ctx // page), device=DEV, dtype=torch.int32) + 1).view(B, -1)
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
     tseq = torch.arange(B, dtype=torch.int32, device=DEV)
     inv = (1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))).to(DEV)
@@ -224,10 +224,10 @@ def attention(ops, a):
     contexts = [int(v) for v in a.attn_contexts.split(",")] if a.attn_contexts else [512, 2048, a.ctx, 4 * a.ctx]
     for B in batches:
         for ctx in contexts:
-            nb = B * (ctx // page) + 1
+            nb = B * -(-ctx // page) + 1
             kp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
             vp = torch.randn(nb, Hkv, page, D, device=DEV).bfloat16()
-            table = (torch.arange(B * (ctx // page), device=DEV, dtype=torch.int32) + 1).view(B, -1)
+            table = (torch.arange(B * -(-ctx // page), device=DEV, dtype=torch.int32) + 1).view(B, -1)
             q = torch.randn(B, Hq * D, device=DEV).bfloat16()
             qsl = torch.arange(B + 1, dtype=torch.int32, device=DEV)
             sl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
