@@ -41,13 +41,17 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, int EPI, int U>
+// SETS: sets of 16 weight rows per CTA for the plain epilogues.  Every set is multiplied with the same activation
+// fragments, so the activations - which every CTA fetches for itself, through the caches - cost half as much per weight
+// byte with two sets (SwiGLU has always had two: its gate rows and its up rows).
+template <int MT, int EPI, int U, int SETS>
 __global__ void __launch_bounds__(128)
 skinny_gemm_kernel(const SkinnyParams p) {
-    constexpr int NSET = EPI == 2 ? 2 : 1;                       // SwiGLU streams two row sets
+    constexpr int NSET = EPI == 2 ? 2 : SETS;                    // SwiGLU streams two row sets: gate and up
     __shared__ float red[4][NSET][MT][32][4];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, q = lane & 3;
-    const int n0 = blockIdx.x * 16;
+    const int n0 = blockIdx.x * 16 * (EPI == 2 ? 1 : SETS);
+    const int set_stride = EPI == 2 ? p.up_offset : 16;           // rows from one set to the next
     const int split = blockIdx.y;
     const int kq = p.kslice / 4;
     const int k_begin = split * p.kslice + warp * kq;
@@ -59,13 +63,16 @@ skinny_gemm_kernel(const SkinnyParams p) {
 #pragma unroll
         for (int j = 0; j < MT; ++j) { acc[s][j][0] = acc[s][j][1] = acc[s][j][2] = acc[s][j][3] = 0.f; }
 
-    const bool row_a = n0 + r < p.N, row_b = n0 + r + 8 < p.N;
+    // (SwiGLU: N counts the gate rows, and an up row exists wherever its gate row does)
+    bool row_a[NSET], row_b[NSET];
     const __nv_bfloat16* wrow[NSET][2];
 #pragma unroll
     for (int s = 0; s < NSET; ++s) {
-        const long long base = (long long)(n0 + r + s * p.up_offset);
-        wrow[s][0] = p.w + (row_a ? base : 0) * p.ldw;
-        wrow[s][1] = p.w + (row_b ? base + 8 : 0) * p.ldw;
+        const int in_n = n0 + r + (EPI == 2 ? 0 : s * 16);
+        row_a[s] = in_n < p.N; row_b[s] = in_n + 8 < p.N;
+        const long long base = (long long)(n0 + r + s * set_stride);
+        wrow[s][0] = p.w + (row_a[s] ? base : 0) * p.ldw;
+        wrow[s][1] = p.w + (row_b[s] ? base + 8 : 0) * p.ldw;
     }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
@@ -81,8 +88,8 @@ skinny_gemm_kernel(const SkinnyParams p) {
             const bool ok = kk < k_end;
 #pragma unroll
             for (int s = 0; s < NSET; ++s) {
-                wv[u][s][0] = (ok && row_a) ? ld_stream(wrow[s][0] + kk) : zero;
-                wv[u][s][1] = (ok && row_b) ? ld_stream(wrow[s][1] + kk) : zero;
+                wv[u][s][0] = (ok && row_a[s]) ? ld_stream(wrow[s][0] + kk) : zero;
+                wv[u][s][1] = (ok && row_b[s]) ? ld_stream(wrow[s][1] + kk) : zero;
             }
         }
     };
@@ -132,7 +139,6 @@ skinny_gemm_kernel(const SkinnyParams p) {
             for (int c = 0; c < 4; ++c) red[warp][s][j][lane][c] = acc[s][j][c];
     __syncthreads();
     const int c = warp;                                         // thread (lane, c) finishes accumulator element c of `lane`
-    const int row = n0 + r + 8 * (c >> 1);
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
         const int m = 8 * j + 2 * q + (c & 1);
@@ -140,40 +146,58 @@ skinny_gemm_kernel(const SkinnyParams p) {
 #pragma unroll
         for (int s = 0; s < NSET; ++s)
             v[s] = ((red[0][s][j][lane][c] + red[1][s][j][lane][c]) + red[2][s][j][lane][c]) + red[3][s][j][lane][c];
-        if (row >= p.N || m >= p.M) continue;
-        if (EPI == 0) {
-            const float b = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
-            reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)m * p.ldo + row] = __float2bfloat16_rn(v[0] + b);
-        } else if (EPI == 1) {
-            reinterpret_cast<float*>(p.out)[((long long)split * p.M + m) * p.ldo + row] = v[0];
-        } else if (EPI == 2) {
+        if (m >= p.M) continue;
+        if (EPI == 2) {
+            const int row = n0 + r + 8 * (c >> 1);
+            if (row >= p.N) continue;
             const float g = v[0] + (p.bias ? __bfloat162float(p.bias[row]) : 0.f);
             const float u = v[NSET - 1] + (p.bias ? __bfloat162float(p.bias[row + p.up_offset]) : 0.f);
             reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)m * p.ldo + row] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
-        } else {
-            const float b = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
-            reinterpret_cast<float*>(p.out)[(long long)m * p.ldo + row] = v[0] + b;
+            continue;
+        }
+#pragma unroll
+        for (int s = 0; s < NSET; ++s) {
+            const int row = n0 + 16 * s + r + 8 * (c >> 1);
+            if (row >= p.N) continue;
+            if (EPI == 0) {
+                const float b = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+                reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)m * p.ldo + row] = __float2bfloat16_rn(v[s] + b);
+            } else if (EPI == 1) {
+                reinterpret_cast<float*>(p.out)[((long long)split * p.M + m) * p.ldo + row] = v[s];
+            } else {
+                const float b = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+                reinterpret_cast<float*>(p.out)[(long long)m * p.ldo + row] = v[s] + b;
+            }
         }
     }
 }
 
-template <int MT, int EPI, int U>
+template <int MT, int EPI, int U, int SETS>
 int launch(const SkinnyParams& p, int splits, cudaStream_t s) {
-    dim3 grid(ceil_div(p.N, 16), splits);
-    TTIE_LAUNCH((skinny_gemm_kernel<MT, EPI, U>), grid, 128, 0, s, p);
+    dim3 grid(ceil_div(p.N, 16 * (EPI == 2 ? 1 : SETS)), splits);
+    TTIE_LAUNCH((skinny_gemm_kernel<MT, EPI, U, SETS>), grid, 128, 0, s, p);
     TTIE_CHECK_LAUNCH("skinny_gemm");
     return 0;
 }
 
 template <int EPI>
 int dispatch(const SkinnyParams& p, int splits, int unroll, cudaStream_t s) {
+    // unroll: low four bits 0 (chosen here), 2 or 4; + 16 asks for two row sets per CTA (plain epilogues)
+    const bool two = EPI != 2 && (unroll & 16);
+    unroll &= 15;
     const int mt = ceil_div(p.M, 8);
     // a product that is not split over CTAs streams best with deep unrolling, a split one with more CTAs per SM
     const bool deep = EPI != 2 && (unroll ? unroll >= 4 : splits == 1);
-    if (mt <= 1) return deep ? launch<1, EPI, 4>(p, splits, s) : launch<1, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
-    if (mt <= 2) return launch<2, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
-    if (mt <= 4) return launch<4, EPI, (EPI == 2 ? 1 : 2)>(p, splits, s);
-    return launch<8, EPI, 1>(p, splits, s);
+    if (two) {
+        if (mt <= 1) return deep ? launch<1, EPI, 2, 2>(p, splits, s) : launch<1, EPI, 1, 2>(p, splits, s);
+        if (mt <= 2) return launch<2, EPI, 1, 2>(p, splits, s);
+        if (mt <= 4) return launch<4, EPI, 1, 2>(p, splits, s);
+        return launch<8, EPI, 1, 1>(p, splits, s);
+    }
+    if (mt <= 1) return deep ? launch<1, EPI, 4, 1>(p, splits, s) : launch<1, EPI, (EPI == 2 ? 1 : 2), 1>(p, splits, s);
+    if (mt <= 2) return launch<2, EPI, (EPI == 2 ? 1 : 2), 1>(p, splits, s);
+    if (mt <= 4) return launch<4, EPI, (EPI == 2 ? 1 : 2), 1>(p, splits, s);
+    return launch<8, EPI, 1, 1>(p, splits, s);
 }
 }  // namespace
 
@@ -189,7 +213,8 @@ extern "C" int ttie_skinny_gemm(const void* x, long long ldx, const void* w, lon
                                 long long ldo, int M, int N, int K, int kslice, int epilogue, int up_offset, void* stream) {
     return ttie_skinny_gemm_tuned(x, ldx, w, ldw, bias, out, ldo, M, N, K, kslice, epilogue, up_offset, 0, stream);
 }
-// unroll: 0 = chosen from kslice; 2 or 4 = 32-key blocks per register buffer (rows <= 8 only).
+// unroll: 0 = chosen from kslice; 2 or 4 = 32-key blocks per register buffer (rows <= 8 only); + 16 = two sets of 16
+// weight rows per CTA (plain epilogues; halves the 32-key blocks per buffer).
 extern "C" int ttie_skinny_gemm_tuned(const void* x, long long ldx, const void* w, long long ldw, const void* bias, void* out,
                                       long long ldo, int M, int N, int K, int kslice, int epilogue, int up_offset, int unroll,
                                       void* stream) {

@@ -35,6 +35,8 @@ _SIGNATURES = {
                             _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_skinny_gemm": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_void],
+    "ttie_skinny_gemm_tuned": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
+                               _c_int, _c_int, _c_void],
     "ttie_swiglu": [_c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
     "ttie_rope_store": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void,
                         _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
@@ -104,6 +106,7 @@ class CudaOps:
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product is the rule (tune_products may hand a shape to the library)
         self._swiglu_choice = {}                # (F, K, row bucket) -> True where the fused tcgen05 gate/up + SwiGLU kernel measured faster
         self._product_choice = {}               # (N, K, row bucket) -> "skinny" | "library" for 9..64 rows (tune_products)
+        self._skinny_tuned = {}                 # (N, K, row bucket 8 | 16) -> (K range per CTA, form code) where tune_products found a faster form
         self.product_timings = {}               # what tune_products measured: (N, K, rows) -> {"library": ms, "skinny": ms}
         self.lib.ttie_attn_tc_supported.restype = _c_int
         if os.environ.get("TTIE_NVTX", "0") not in ("", "0"):
@@ -223,14 +226,17 @@ class CudaOps:
                 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
     def tune_products(self, weights, iters=8):
-        """For 9 to 64 rows neither this package's weight-streaming product nor the library's wins at every shape
-        (measured at the Llama-2-7B widths the library is ahead by 10-20 %; on a narrow, deep matrix such as
-        [2048, 16384] it leaves half of the memory bandwidth unused).  So each distinct bfloat16 matrix shape of a
-        model is timed once per row bucket (16, 32, 64) with both, as a replayed graph of ``iters`` launches
-        that rotate over the model's matrices of that shape, and the faster one is remembered.  Small matrices
-        (under 4 Mi elements) are left to the library.  Up to 8 rows the weight-streaming product is the rule and
-        is ahead on most shapes, by up to 3x on narrow deep ones; the same measurement at 8 rows hands a shape to
-        the library where that is more than 5 % faster (measured: [10240, 8192] and [8192, 28672] by 9-10 %)."""
+        """Which product serves each distinct bfloat16 matrix shape of a model at 8, 16, 32 and 64 rows, by measurement:
+        a replayed graph of ``iters`` launches that rotate over the model's matrices of that shape (so that the weights come
+        from HBM).  For 9 to 64 rows neither this package's weight-streaming product nor the library's wins at every
+        shape (at the Llama-2-7B widths the library is ahead by 10-20 % from 32 rows on; on a narrow, deep matrix such as
+        [2048, 16384] it leaves half of the memory bandwidth unused), and the faster one is remembered.  Up to 8 rows the
+        weight-streaming product is the rule and is ahead on most shapes, by up to 3x on narrow deep ones; a shape goes to
+        the library where that is more than 5 % faster (measured: [10240, 8192] and [8192, 28672] by 9-10 %).  At 8 and
+        16 rows the weight-streaming product's own form is measured too - K cut into 1 to 16 ranges over CTAs, one or two
+        sets of 16 weight rows per CTA - and a form that beats the rule of thumb (``_kslice``) by 3 % is kept: [4352, 4096]
+        at 8 rows takes 7.8 us in 6 ranges with two row sets against 9.1 in 8 ranges with one, [4544, 18176] 28.5 us in 6
+        ranges against 38.3 uncut.  Small matrices (under 4 Mi elements) are left alone."""
         groups, launches = {}, self.launches
         for w in weights:
             if w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1 and w.shape[0] * w.shape[1] >= (4 << 20):
@@ -242,25 +248,31 @@ class CudaOps:
                 x = torch.randn(M, K, device=self.device).to(torch.bfloat16)
                 if not self._skinny_shape_ok(x, ws[0]):
                     continue
-                took = {}
-                for kind in ("library", "skinny"):
+
+                def measure(kind, form=None):
                     self._product_choice[(N, K, M)] = kind
-                    fn = lambda i: self.linear(x, ws[i % len(ws)], None, partial_ok=True)
-                    for i in range(2):
-                        fn(i)
-                    torch.cuda.synchronize(self.device)
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g):
-                        for i in range(iters):
-                            fn(i)
-                    g.replay()
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                    g.replay()
-                    b.record()
-                    torch.cuda.synchronize(self.device)
-                    took[kind] = a.elapsed_time(b)
-                    del g
+                    self._skinny_tuned.pop((N, K, M), None)
+                    if form is not None:
+                        self._skinny_tuned[(N, K, M)] = form
+                    return self._graph_time_rotating(lambda i: self.linear(x, ws[i % len(ws)], None, partial_ok=True), iters)
+
+                took = {"library": measure("library"), "skinny": measure("skinny")}
+                form = None
+                if M <= 16:
+                    # up to 16 rows the weight-streaming product's own form is measured as well: one or two sets of 16 weight
+                    # rows per CTA, K cut into 1 to 16 ranges
+                    for code in (0, 16):
+                        for S in (1, 2, 3, 4, 6, 8, 12, 16):
+                            kslice = math.ceil(math.ceil(K / S) / 128) * 128
+                            if kslice < 256 or math.ceil(K / kslice) != S:
+                                continue
+                            t = measure("skinny", (kslice, code))
+                            if t < 0.97 * took["skinny"]:
+                                took["skinny"], form = t, (kslice, code)
+                self._skinny_tuned.pop((N, K, M), None)
+                if form is not None:
+                    self._skinny_tuned[(N, K, M)] = form
+                    took["skinny_form"] = {"k_ranges": math.ceil(K / form[0]), "row_sets": 2 if form[1] & 16 else 1}
                 if M == 8:      # up to 8 rows the weight-streaming product is the rule; the library takes a shape only where it is clearly ahead
                     self._product_choice[(N, K, M)] = "library" if took["library"] < 0.95 * took["skinny"] else "skinny"
                 else:
@@ -303,7 +315,9 @@ class CudaOps:
             self.launches += 1
             return out
         if self._skinny_ok(x, w):
-            kslice = self._kslice(N, K, partial_ok and bias is None and out_dtype is None)
+            may_split = partial_ok and bias is None and out_dtype is None
+            tuned = self._skinny_tuned.get((N, K, 8 if M <= 8 else 16)) if (may_split and M <= 16) else None
+            kslice, form = tuned if tuned is not None else (self._kslice(N, K, may_split), 0)
             S = math.ceil(K / kslice)
             if S > 1:
                 out, epi = torch.empty((S, M, N), dtype=torch.float32, device=x.device), 1
@@ -311,8 +325,8 @@ class CudaOps:
                 out, epi = torch.empty((M, N), dtype=torch.float32, device=x.device), 3
             else:
                 out, epi = torch.empty((M, N), dtype=torch.bfloat16, device=x.device), 0
-            self._check(self.lib.ttie_skinny_gemm(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), N,
-                                                  M, N, K, kslice, epi, 0, self._stream(x)), "skinny_gemm")
+            self._check(self.lib.ttie_skinny_gemm_tuned(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out), N,
+                                                        M, N, K, kslice, epi, 0, form, self._stream(x)), "skinny_gemm")
             self.launches += 1
             return out
         # bfloat16, many rows: the library product, 32-bit accumulation inside
@@ -389,6 +403,26 @@ class CudaOps:
                                               self._stream(x)), "skinny_gemm_swiglu")
         self.launches += 1
         return act
+
+    def _graph_time_rotating(self, fn, iters=8) -> float:
+        """Milliseconds of one replay of a graph of ``iters`` calls ``fn(i)`` (after two plain calls)."""
+        for i in range(2):
+            fn(i)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(i)
+        g.replay()
+        best = None
+        for _ in range(3):                                           # the least of three replays
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize(self.device)
+            best = a.elapsed_time(b) if best is None else min(best, a.elapsed_time(b))
+        return best
 
     def _graph_time(self, fn, iters=8) -> float:
         """Milliseconds of one replay of a graph of ``iters`` calls of ``fn`` (after two plain calls)."""

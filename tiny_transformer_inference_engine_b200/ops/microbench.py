@@ -302,10 +302,10 @@ def mixed(ops, a):
 
 
 def tune(ops, a):
-    """What ``CudaOps.tune_products`` measures at 16, 32 and 64 rows for the model's matrix shapes: the library's
-    product against this package's weight-streaming kernel (both rotate over several matrices of a shape)."""
+    """What ``CudaOps.tune_products`` measures at 8, 16, 32 and 64 rows for the model's matrix shapes: the library's
+    product against this package's weight-streaming kernel in its best form (both rotate over several matrices of a shape)."""
     d, F, V, Hq, Hkv, D = a.d_model, a.hidden, a.vocab, a.heads, a.kv_heads, a.d_model // a.heads
-    print("== products of 16 / 32 / 64 rows, us per launch: library | weight-streaming kernel -> choice")
+    print("== products of 8 / 16 / 32 / 64 rows, us per launch: library | weight-streaming kernel -> choice")
     weights = []
     for N, K in (((Hq + 2 * Hkv) * D, d), (d, Hq * D), (d, F), (V, d)):
         n = max(2, min(8, int(400e6 // (N * K * 2))))
@@ -315,7 +315,9 @@ def tune(ops, a):
     for (N, K, M), took in sorted(ops.product_timings.items(), key=lambda kv: str(kv[0])):
         if N == "swiglu":
             continue
-        print(f"[{N}, {K}] {M:3d} rows   {took['library'] * 1000 / 8:7.1f} | {took['skinny'] * 1000 / 8:7.1f}   -> {ops._product_choice[(N, K, M)]}", flush=True)
+        form = took.get("skinny_form")
+        print(f"[{N}, {K}] {M:3d} rows   {took['library'] * 1000 / 8:7.1f} | {took['skinny'] * 1000 / 8:7.1f}   -> {ops._product_choice[(N, K, M)]}"
+              + (f"   (K in {form['k_ranges']} ranges, {form['row_sets']} row set(s) per CTA)" if form else ""), flush=True)
 
 
 def main(argv=None):
