@@ -216,11 +216,15 @@ class CudaOps:
         self.launches += 1
 
     # ---- matrix products
-    def _skinny_ok(self, x, w):
+    def _skinny_ok(self, x, w, may_split=False):
+        """Whether the weight-streaming product takes this product.  ``may_split``: the caller accepts partial sums of a
+        K range cut over CTAs; the measured choice for such calls (which may rest on a cut form) is kept apart."""
         M = x.shape[0]
-        if M > self.skinny_max_rows and not (M <= 64 and self._product_choice.get((w.shape[0], w.shape[1], _row_bucket(M))) == "skinny"):
+        key = (w.shape[0], w.shape[1], 8 if M <= self.skinny_max_rows else _row_bucket(M)) + (("split",) if may_split else ())
+        choice = self._product_choice.get(key)
+        if M > self.skinny_max_rows and not (M <= 64 and choice == "skinny"):
             return False
-        if M <= self.skinny_max_rows and self._product_choice.get((w.shape[0], w.shape[1], 8)) == "library":
+        if M <= self.skinny_max_rows and choice == "library":
             return False
         return (x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
                 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
@@ -249,14 +253,19 @@ class CudaOps:
                 if not self._skinny_shape_ok(x, ws[0]):
                     continue
 
-                def measure(kind, form=None):
-                    self._product_choice[(N, K, M)] = kind
+                def measure(kind, form=None, partial_ok=True):
+                    self._product_choice[(N, K, M)] = self._product_choice[(N, K, M, "split")] = kind
                     self._skinny_tuned.pop((N, K, M), None)
                     if form is not None:
                         self._skinny_tuned[(N, K, M)] = form
-                    return self._graph_time_rotating(lambda i: self.linear(x, ws[i % len(ws)], None, partial_ok=True), iters)
+                    return self._graph_time_rotating(lambda i: self.linear(x, ws[i % len(ws)], None, partial_ok=partial_ok), iters)
 
-                took = {"library": measure("library"), "skinny": measure("skinny")}
+                def decide(skinny, library):
+                    if M == 8:  # up to 8 rows the weight-streaming product is the rule; the library takes a shape only where it is clearly ahead
+                        return "library" if library < 0.95 * skinny else "skinny"
+                    return "skinny" if skinny < 0.97 * library else "library"
+
+                took = {"library": measure("library"), "skinny_uncut": measure("skinny", partial_ok=False), "skinny": measure("skinny")}
                 form = None
                 if M <= 16:
                     # up to 16 rows the weight-streaming product's own form is measured as well: one or two sets of 16 weight
@@ -273,10 +282,9 @@ class CudaOps:
                 if form is not None:
                     self._skinny_tuned[(N, K, M)] = form
                     took["skinny_form"] = {"k_ranges": math.ceil(K / form[0]), "row_sets": 2 if form[1] & 16 else 1}
-                if M == 8:      # up to 8 rows the weight-streaming product is the rule; the library takes a shape only where it is clearly ahead
-                    self._product_choice[(N, K, M)] = "library" if took["library"] < 0.95 * took["skinny"] else "skinny"
-                else:
-                    self._product_choice[(N, K, M)] = "skinny" if took["skinny"] < 0.97 * took["library"] else "library"
+                # callers that take partial sums of a cut K range, and callers that want the whole sum
+                self._product_choice[(N, K, M, "split")] = decide(took["skinny"], took["library"])
+                self._product_choice[(N, K, M)] = decide(took["skinny_uncut"], took["library"])
                 self.product_timings[(N, K, M)] = took
         self.launches = launches
 
@@ -314,8 +322,8 @@ class CudaOps:
                                                w.stride(0), N, self._stream(x)), "gemm_f32")
             self.launches += 1
             return out
-        if self._skinny_ok(x, w):
-            may_split = partial_ok and bias is None and out_dtype is None
+        may_split = partial_ok and bias is None and out_dtype is None
+        if self._skinny_ok(x, w, may_split):
             tuned = self._skinny_tuned.get((N, K, 8 if M <= 8 else 16)) if (may_split and M <= 16) else None
             kslice, form = tuned if tuned is not None else (self._kslice(N, K, may_split), 0)
             S = math.ceil(K / kslice)

@@ -305,7 +305,7 @@ def tune(ops, a):
     """What ``CudaOps.tune_products`` measures at 8, 16, 32 and 64 rows for the model's matrix shapes: the library's
     product against this package's weight-streaming kernel in its best form (both rotate over several matrices of a shape)."""
     d, F, V, Hq, Hkv, D = a.d_model, a.hidden, a.vocab, a.heads, a.kv_heads, a.d_model // a.heads
-    print("== products of 8 / 16 / 32 / 64 rows, us per launch: library | weight-streaming kernel -> choice")
+    print("== products of 8 / 16 / 32 / 64 rows, us per launch: library | weight-streaming kernel -> choice for callers that take partial sums; for the others")
     weights = []
     for N, K in (((Hq + 2 * Hkv) * D, d), (d, Hq * D), (d, F), (V, d)):
         n = max(2, min(8, int(400e6 // (N * K * 2))))
@@ -316,8 +316,9 @@ def tune(ops, a):
         if N == "swiglu":
             continue
         form = took.get("skinny_form")
-        print(f"[{N}, {K}] {M:3d} rows   {took['library'] * 1000 / 8:7.1f} | {took['skinny'] * 1000 / 8:7.1f}   -> {ops._product_choice[(N, K, M)]}"
-              + (f"   (K in {form['k_ranges']} ranges, {form['row_sets']} row set(s) per CTA)" if form else ""), flush=True)
+        print(f"[{N}, {K}] {M:3d} rows   {took['library'] * 1000 / 8:7.1f} | {took['skinny'] * 1000 / 8:7.1f}   -> {ops._product_choice[(N, K, M, 'split')]}"
+              + (f"   (K in {form['k_ranges']} ranges, {form['row_sets']} row set(s) per CTA)" if form else "")
+              + f"; K uncut {took['skinny_uncut'] * 1000 / 8:7.1f} -> {ops._product_choice[(N, K, M)]}", flush=True)
 
 
 def main(argv=None):
