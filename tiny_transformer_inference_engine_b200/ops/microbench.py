@@ -102,9 +102,10 @@ def decode(ops, a):
     for name, N, K in (("qkv projection", (Hq + 2 * Hkv) * D, d), ("output projection", d, Hq * D), ("down projection", d, F),
                        ("lm_head", V, d)):
         ws = weights(N, K)
+        ops.tune_products(ws)                                        # as when a model is loaded: the product and its form by measurement
         xin = torch.randn(B, K, device=DEV).bfloat16()
         f32 = torch.float32 if name == "lm_head" else None
-        line(f"{name} (weight streaming)", timeit(lambda i: ops.linear(xin, ws[i % len(ws)], None, out_dtype=f32, partial_ok=f32 is None)),
+        line(f"{name}", timeit(lambda i: ops.linear(xin, ws[i % len(ws)], None, out_dtype=f32, partial_ok=f32 is None)),
              bytes_=N * K * 2)
     ws = weights(2 * F, d)
     line("gate/up projection + SwiGLU", timeit(lambda i: ops.linear_swiglu(x, ws[i % len(ws)], None, F)), bytes_=2 * F * d * 2)
