@@ -565,6 +565,20 @@ def test_skinny_gemm_all_epilogues(ops, M, N, K):
                                       M, N, K, kslice, 1, 0, torch.cuda.current_stream().cuda_stream)
         assert rc == 0
         assert rel(part.sum(0).cpu(), exp) < 1e-5
+    # two sets of 16 weight rows per CTA (the form the load-time measurement may pick): every epilogue, K whole and cut
+    stream = torch.cuda.current_stream().cuda_stream
+    for kslice in (-(-K // 128) * 128, 256):
+        S = -(-K // kslice)
+        part = torch.full((S, M, N), float("nan"), dtype=torch.float32, device=DEV)
+        assert ops.lib.ttie_skinny_gemm_tuned(xd.data_ptr(), xd.stride(0), wd.data_ptr(), wd.stride(0), None, part.data_ptr(), N,
+                                              M, N, K, kslice, 1, 0, 16, stream) == 0
+        assert rel(part.sum(0).cpu(), exp) < 1e-5
+    o16 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    for out, epi, tol in ((o16, 0, 8e-3), (o32, 3, 1e-5)):
+        assert ops.lib.ttie_skinny_gemm_tuned(xd.data_ptr(), xd.stride(0), wd.data_ptr(), wd.stride(0), bd.data_ptr(), out.data_ptr(), N,
+                                              M, N, K, -(-K // 128) * 128, epi, 0, 16 + 4, stream) == 0
+        assert rel(out.float().cpu(), exp + b.double()) < tol
     if N % 2 == 0:
         F = N // 2
         act = ops.linear_swiglu(xd, wd, bd, F)
@@ -572,6 +586,34 @@ def test_skinny_gemm_all_epilogues(ops, M, N, K):
         ref = gu[:, :F] * torch.sigmoid(gu[:, :F]) * gu[:, F:]
         assert rel(act.float().cpu(), ref) < 1.2e-2
     ops.skinny_max_rows = 8
+
+
+def test_weight_streaming_form_is_measured_at_load(ops):
+    """``tune_products`` on a shape of a model: the product for 8, 16, 32 and 64 rows and, at 8 and 16 rows, the form of this
+    package's kernel (K ranges over CTAs, one or two row sets per CTA) are chosen by measurement; a caller that takes
+    partial sums and one that wants whole sums are decided apart, and both get the right values."""
+    N, K = 2048, 8192
+    g = torch.Generator().manual_seed(3)
+    ws = [(torch.randn(N, K, generator=g) * 0.02).bfloat16().to(DEV) for _ in range(3)]
+    keep = dict(ops._product_choice), dict(ops._skinny_tuned)
+    try:
+        ops.tune_products(ws)
+        for M in (8, 16, 32, 64):
+            took = ops.product_timings[(N, K, M)]
+            assert took["library"] > 0 and took["skinny"] > 0 and took["skinny"] <= took["skinny_uncut"] * 1.05
+            assert ops._product_choice[(N, K, M)] in ("skinny", "library") and ops._product_choice[(N, K, M, "split")] in ("skinny", "library")
+        # a narrow deep matrix: this package's kernel with K cut over CTAs wins at 8 and 16 rows
+        assert ops._product_choice[(N, K, 8, "split")] == "skinny" and ops._product_choice[(N, K, 16, "split")] == "skinny"
+        for M in (3, 8, 13, 16, 40):
+            x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+            exp = x.double().cpu() @ ws[1].double().cpu().T
+            part = ops.linear(x, ws[1], None, partial_ok=True)
+            got = part.sum(0) if part.dim() == 3 else part.float()
+            assert rel(got.double().cpu(), exp) < (1e-5 if part.dim() == 3 else 8e-3)
+            assert rel(ops.linear(x, ws[1], None).double().cpu(), exp) < 8e-3
+    finally:
+        ops._product_choice.clear(); ops._product_choice.update(keep[0])
+        ops._skinny_tuned.clear(); ops._skinny_tuned.update(keep[1])
 
 
 def test_swiglu_product_for_few_rows_is_chosen_by_measurement(ops):
