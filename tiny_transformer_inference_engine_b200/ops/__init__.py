@@ -105,9 +105,9 @@ class CudaOps:
         self.attn_tc_min_rows = 256             # query rows per request from which the tcgen05 attention kernel is used
         self.skinny_max_rows = 8                # rows up to which the weight-streaming product is the rule (tune_products may hand a shape to the library)
         self._swiglu_choice = {}                # (F, K, row bucket) -> True where the fused tcgen05 gate/up + SwiGLU kernel measured faster
-        self._product_choice = {}               # (N, K, row bucket) -> "skinny" | "library" for 9..64 rows (tune_products)
+        self._product_choice = {}               # (N, K, row bucket[, "split"]) -> "skinny" | "library" (tune_products; "split": for callers that take partial sums)
         self._skinny_tuned = {}                 # (N, K, row bucket 8 | 16) -> (K range per CTA, form code) where tune_products found a faster form
-        self.product_timings = {}               # what tune_products measured: (N, K, rows) -> {"library": ms, "skinny": ms}
+        self.product_timings = {}               # what tune_products measured: (N, K, rows) -> {"library": ms, "skinny": ms (best form), "skinny_uncut": ms, ...}
         self.lib.ttie_attn_tc_supported.restype = _c_int
         if os.environ.get("TTIE_NVTX", "0") not in ("", "0"):
             self._wrap_in_ranges()
