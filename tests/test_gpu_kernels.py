@@ -46,7 +46,7 @@ def test_embed(ops, dtype, T, d, V):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,d,eps", [(1, 64, 1e-5), (19, 1000, 1e-6), (3, 4544, 1e-3), (2, 11008, 1e-5)])
+@pytest.mark.parametrize("T,d,eps", [(1, 64, 1e-5), (19, 1000, 1e-6), (3, 4544, 1e-3), (2, 11008, 1e-5), (64, 4096, 1e-5), (97, 2048, 1e-5)])
 def test_add_rmsnorm(ops, dtype, wdtype, T, d, eps):
     g = torch.Generator().manual_seed(1)
     resid = torch.randn(T, d, generator=g) * 3
